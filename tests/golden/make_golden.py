@@ -1,0 +1,174 @@
+"""Generate golden vectors for the ternary-E8 path FROM THE LIVE REFERENCE.
+
+Run once, in a container that has the reference checkout:
+
+    OJASX_DISABLE_UPDATE_CHECK=1 PYTHONDONTWRITEBYTECODE=1 \
+        python tests/golden/make_golden.py --ref /path/to/reference
+
+It imports the reference's ``ojasx2.math.lattice`` / ``ojasx2.streaming_e8``,
+feeds them inputs from the portable seeded generator in ``oracle/e8t_oracle.py``
+(so inputs can be regenerated anywhere without a library RNG) and stores the
+reference's outputs:
+
+* ``e8t_golden.npz``  - full arrays for small cases (packed bytes, fp16 scales,
+  fp32 decoded weights, fp32 linear outputs) and the reference's full
+  rank->coords table;
+* ``e8t_golden.json`` - case descriptions plus SHA-256 digests of the
+  reference's outputs for the large cases.
+
+Nothing here is read at test time except the two output files.
+"""
+
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import logging
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import e8t_oracle as O  # noqa: E402  (input generator only)
+
+
+def sha(a: np.ndarray) -> str:
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+# name, seed, rows, cols, sigma, dtype, group, store_full
+CASES = [
+    ("kat_64x128_f32", 1, 64, 128, 0.02, "f32", 32, True),
+    ("kat_256x4096_f16", 2, 256, 4096, 0.02, "f16", 32, False),
+    ("kat_128x14336_f32", 3, 128, 14336, 0.02, "f32", 32, False),
+    ("kat_96x8192_f16", 4, 96, 8192, 0.02, "f16", 32, False),
+    ("bf16_48x256", 5, 48, 256, 0.02, "bf16", 32, True),
+    ("unit_sigma_32x512", 6, 32, 512, 1.0, "f32", 32, True),
+    ("odd_7x13_g32", 7, 7, 13, 0.5, "f32", 32, True),
+    ("odd_5x19_g16", 8, 5, 19, 0.5, "f32", 16, True),
+    ("row_not_group_4x48_g32", 9, 4, 48, 0.1, "f32", 32, True),
+    ("group64_16x256", 10, 16, 256, 0.02, "f32", 64, True),
+    ("bad_group_8x64_g8", 11, 8, 64, 0.02, "f32", 8, True),      # coerced to 16 by the packer
+    ("single_group_1x32", 12, 1, 32, 3.0, "f32", 32, True),
+    ("llama_q_512x4096_bf16", 13, 512, 4096, 0.02, "bf16", 32, False),
+    ("big_values_16x128", 14, 16, 128, 1.0e4, "f32", 32, True),
+    ("tiny_values_16x128", 15, 16, 128, 1.0e-6, "f16", 32, True),   # fp16 denormals / zeros
+]
+
+
+def make_input(seed, rows, cols, sigma, dtype):
+    import torch
+    w = O.gen_normal(seed, rows * cols, sigma).reshape(rows, cols)
+    t = torch.from_numpy(w.copy())
+    if dtype == "f16":
+        t = t.half()
+    elif dtype == "bf16":
+        t = t.bfloat16()
+    return t
+
+
+def special_inputs():
+    """Hand-built edge inputs: all-zero groups, exact ties, half-way values, signed zeros."""
+    import torch
+    out = {}
+    z = torch.zeros(2, 64)
+    z[1, :32] = torch.linspace(-1, 1, 32)
+    out["zeros_and_ramp_2x64"] = (z, 32)
+    # values that sit exactly on rounding boundaries after division by the scale
+    t = torch.tensor([0.5, -0.5, 1.5, -1.5, 0.0, -0.0, 2.5, -2.5] * 4, dtype=torch.float32).reshape(1, 32)
+    out["halfway_1x32"] = (t, 32)
+    # identical magnitudes -> argmin ties (first index must win)
+    e = torch.full((1, 32), 0.3, dtype=torch.float32)
+    e[0, ::3] = -0.3
+    out["ties_1x32"] = (e, 32)
+    c = torch.ones(3, 32, dtype=torch.float32)
+    c[1] *= -1
+    c[2, 16:] = 0
+    out["constant_3x32"] = (c, 32)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    os.environ.setdefault("OJASX_DISABLE_UPDATE_CHECK", "1")
+    logging.disable(logging.CRITICAL)
+    sys.path.insert(0, args.ref)
+    import torch
+    import ojasx2.math.lattice as L
+    from ojasx2.streaming_e8 import pack_weight_rowwise
+
+    torch.set_num_threads(4)
+    arrays, meta = {}, {"cases": [], "special": [], "generator_check": {}}
+
+    x0 = O.gen_normal(1, 4, 1.0)
+    meta["generator_check"] = {"seed": 1, "first4": [float(v) for v in x0]}
+
+    r2c, raw2rank, _ = L._get_ternary_e8_luts()
+    arrays["rank_to_coords"] = r2c.numpy().astype(np.int8)
+    meta["rank_to_coords_sha256"] = sha(arrays["rank_to_coords"])
+    meta["raw_to_rank_sha256"] = sha(raw2rank.numpy().astype(np.int64))
+
+    for name, seed, rows, cols, sigma, dtype, group, full in CASES:
+        w = make_input(seed, rows, cols, sigma, dtype)
+        packed, scales, shape = L.TernaryE8LatticePacker.pack(w, group_size=group)
+        dec = L.TernaryE8LatticePacker.unpack(packed, scales, (rows, cols), dtype=torch.float32)
+        entry = dict(name=name, seed=seed, rows=rows, cols=cols, sigma=sigma, dtype=dtype, group=group,
+                     full=full, packed_len=int(packed.numel()), scales_len=int(scales.numel()),
+                     sha_input=sha(w.view(torch.int16).numpy() if dtype != "f32" else w.numpy()),
+                     sha_packed=sha(packed.numpy()), sha_scales=sha(scales.view(torch.int16).numpy()),
+                     sha_decoded=sha(dec.numpy()))
+        if group % 32 == 0 and cols % group == 0:
+            p2, s2 = pack_weight_rowwise(w, bitrate=1.5, group_size=group, row_block=5)
+            entry["rowwise_equal"] = bool(torch.equal(p2, packed) and torch.equal(s2, scales))
+        if cols % 32 == 0 and group == 32:
+            xb = torch.from_numpy(O.gen_normal(seed + 100, 4 * cols, 1.0).reshape(4, cols).copy()).bfloat16()
+            y = xb.float() @ dec.t()
+            y_ref = L._FusedE8GEMMFunction.apply(xb.float(), packed, scales, None, rows, cols, group, 1.5, False)
+            entry["y_norm"] = float(y.norm())
+            entry["y_head"] = [float(v) for v in y[0, :3]]
+            entry["ref_forward_matches_dequant_matmul"] = bool(torch.equal(y, y_ref))
+            if full:
+                arrays[name + "/y"] = y.numpy()
+        if full:
+            arrays[name + "/packed"] = packed.numpy()
+            arrays[name + "/scales"] = scales.view(torch.int16).numpy().view(np.uint16)
+            arrays[name + "/decoded"] = dec.numpy()
+        meta["cases"].append(entry)
+        print(name, entry["sha_packed"][:16], entry["sha_scales"][:16], entry["sha_decoded"][:16])
+
+    for name, (w, group) in special_inputs().items():
+        packed, scales, _ = L.TernaryE8LatticePacker.pack(w, group_size=group)
+        dec = L.TernaryE8LatticePacker.unpack(packed, scales, tuple(w.shape), dtype=torch.float32)
+        arrays["special/" + name + "/input"] = w.numpy()
+        arrays["special/" + name + "/packed"] = packed.numpy()
+        arrays["special/" + name + "/scales"] = scales.view(torch.int16).numpy().view(np.uint16)
+        arrays["special/" + name + "/decoded"] = dec.numpy()
+        meta["special"].append(dict(name=name, group=group, rows=int(w.shape[0]), cols=int(w.shape[1])))
+        print("special", name, sha(packed.numpy())[:16])
+
+    # decode of every code: all 3281 ranks (padded to an even count) with unit scales
+    ranks = np.arange(3282, dtype=np.int64) % 3281
+    packed_all = O.pack_codes(ranks)
+    sc = torch.ones(3282 * 8 // 32 + 1, dtype=torch.float16)[: (3282 * 8) // 32]
+    # 3282*8 = 26256 weights = 820.5 groups of 32 -> use group 16 (1641 groups)
+    sc16 = torch.ones(1641, dtype=torch.float16)
+    dec_all = L.TernaryE8LatticePacker.unpack(torch.from_numpy(packed_all), sc16, (3282, 8), dtype=torch.float32)
+    arrays["all_codes/packed"] = packed_all
+    arrays["all_codes/decoded"] = dec_all.numpy().astype(np.int8)
+    del sc
+
+    np.savez_compressed(os.path.join(HERE, "e8t_golden.npz"), **arrays)
+    with open(os.path.join(HERE, "e8t_golden.json"), "w") as f:
+        json.dump(meta, f, indent=1, sort_keys=True)
+    print("wrote", len(arrays), "arrays")
+
+
+if __name__ == "__main__":
+    main()
