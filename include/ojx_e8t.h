@@ -1,0 +1,147 @@
+/*
+ * ojx_e8t.h - C ABI of the B200 (sm_100a) ternary-E8 quantized-linear kernels.
+ *
+ * Packed format (identical to the reference's, so buffers are interchangeable):
+ *   codes   uint8[P*3/16]  every 3 bytes hold two 12-bit lattice ranks c0,c1 covering 16
+ *                          consecutive weights: b0=c0&0xFF, b1=(c0>>8)|((c1&0xF)<<4), b2=c1>>4
+ *   scales  fp16[P/g]      one RMS scale per group of g consecutive weights (g = 32 by default)
+ *   P = rows*cols rounded up to a multiple of g; weights are taken row-major.  When cols % g == 0
+ *   every row owns whole groups: row n starts at byte n*cols*3/16 and at scale n*cols/g.
+ *
+ * Conventions for every entry point
+ *   - returns an ojx_status (0 = ok, negative = error); never throws, never traps;
+ *   - never allocates device or host memory: every buffer, including scratch, is owned by the
+ *     caller (one documented exception below carries its own static scratch);
+ *   - asynchronous: work is enqueued on `stream` (a cudaStream_t passed as void*);
+ *   - all pointers are device pointers unless stated otherwise.
+ *
+ * The functions replace the following parts of the reference project (file:line inside it):
+ *   ojx_e8t_encode        TernaryE8LatticePacker.pack            ojasx2/math/lattice.py:338-384
+ *                         (and its row-block caller)             ojasx2/streaming_e8.py:112-159
+ *   ojx_e8t_decode        TernaryE8LatticePacker.unpack          ojasx2/math/lattice.py:386-419
+ *                         workspace reconstruction               ojasx2/math/lattice.py:62-84,412-416
+ *   ojx_e8t_gemv/_gemm    _FusedE8GEMMFunction.forward           ojasx2/math/lattice.py:551-640
+ *                         dispatch_tilelang_e8_gemm              ojasx2/tilelang_kernels.py:370-419
+ *                         _build_tl_ternary_e8_1_5bit_gemm       ojasx2/tilelang_kernels.py:277-363
+ *                         fused_ternary_e8_gemm_forward<T>       ojasx2/math/csrc/ojasx_math_core.hpp:580-634
+ *                         op schema fused_ternary_e8_gemm_fwd    ojasx2/math/csrc/ojasx_math_bindings.cpp:586-595
+ */
+#ifndef OJX_E8T_H
+#define OJX_E8T_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    OJX_OK = 0,
+    OJX_ERR_NULL = -1,        /* a required pointer is null */
+    OJX_ERR_SHAPE = -2,       /* sizes are zero/negative or violate the layout rules */
+    OJX_ERR_ALIGN = -3,       /* a pointer or row stride is not aligned as required */
+    OJX_ERR_DTYPE = -4,       /* unknown or unsupported element type */
+    OJX_ERR_ARCH = -5,        /* the current device is not sm_100 */
+    OJX_ERR_LAUNCH = -6,      /* the CUDA runtime rejected a launch or a set-up call */
+    OJX_ERR_TIMEOUT = -7,     /* a bounded device-side wait gave up (reported by ojx_e8t_gemm_status) */
+    OJX_ERR_WORKSPACE = -8,   /* scratch buffer missing or too small */
+    OJX_ERR_UNSUPPORTED = -9  /* valid request that this build does not implement */
+} ojx_status;
+
+typedef enum { OJX_F32 = 0, OJX_F16 = 1, OJX_BF16 = 2 } ojx_dtype;
+
+/* Library version: major*10000 + minor*100 + patch. */
+int32_t ojx_e8t_version(void);
+
+/* Static, human readable name of a status code. */
+const char* ojx_e8t_status_string(int32_t status);
+
+/*
+ * Encoder.  Replaces TernaryE8LatticePacker.pack (ojasx2/math/lattice.py:338-384); bit-exact.
+ *   w         [rows, cols] row-major, dtype w_dtype (fp32 / fp16 / bf16), any alignment of rows
+ *   group     scale group size; values that are not a positive multiple of 16 are replaced by 16,
+ *             exactly as the reference does (lattice.py:346-347)
+ *   packed_out uint8[P*3/16], scales_out fp16[P/g] with P = rows*cols padded up to g
+ */
+int32_t ojx_e8t_encode(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
+                       uint8_t* packed_out, uint16_t* scales_out, void* stream);
+
+/*
+ * Decoder.  Replaces TernaryE8LatticePacker.unpack (ojasx2/math/lattice.py:386-419).
+ * out[rows, cols] = coord * cast(scale): fp32 and fp16 outputs are exact; bf16 output multiplies
+ * by the bf16-rounded scale, as the reference does when asked for bf16.
+ */
+int32_t ojx_e8t_decode(const uint8_t* packed, const uint16_t* scales, int64_t rows, int64_t cols,
+                       int32_t group, int32_t out_dtype, void* out, void* stream);
+
+/*
+ * Decode-shape linear (small M): y[M, N] = x[M, K] . W^T (+ bias), W given packed.
+ * Replaces _FusedE8GEMMFunction.forward for small batches (ojasx2/math/lattice.py:551-640) and the
+ * reference's native fused kernel (ojasx_math_core.hpp:580-634).  fp32 accumulation.
+ *   x, y       row-major, dtypes x_dtype / y_dtype (bf16, fp16 or fp32)
+ *   bias       [N] in x_dtype, or null
+ *   group      must be 32 and K % 32 == 0 (every row owns whole groups)
+ *   workspace  scratch of at least ojx_e8t_gemv_workspace_bytes(M, N, K) bytes (may be null when
+ *              that function returns 0); contents need not be initialised
+ */
+size_t  ojx_e8t_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int32_t ojx_e8t_gemv(const void* x, int32_t x_dtype, int64_t M,
+                     const uint8_t* packed, const uint16_t* scales, const void* bias,
+                     int64_t N, int64_t K, int32_t group,
+                     void* y, int32_t y_dtype,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Several independent decode-shape linears in ONE launch (for example q/k/v, or gate/up, or a
+ * rotation of matrices in a benchmark).  `problems` is a DEVICE array of `count` descriptors;
+ * `total_tiles` is the sum over problems of ojx_e8t_gemv_tiles(N, K).  All problems share M,
+ * x_dtype and y_dtype; every K must be a multiple of 256.  Pass needs_reduce != 0 when any problem
+ * has ojx_e8t_gemv_kchunks(K) > 1 (its `partial` scratch is then summed by a second small kernel).  No counterpart in the reference, which runs one layer per call.
+ */
+typedef struct {
+    const void*     x;        /* [M, K] */
+    const uint8_t*  packed;   /* [N, K*3/16] */
+    const uint16_t* scales;   /* [N, K/32] */
+    const void*     bias;     /* [N] or null */
+    void*           y;        /* [M, N] */
+    float*          partial;  /* scratch [kchunks, M, N] fp32 when kchunks > 1, else null */
+    int32_t         N, K;
+    int32_t         tile_begin;   /* exclusive prefix sum of tiles over the problem list */
+    int32_t         reserved;
+} ojx_e8t_gemv_problem;
+
+int32_t ojx_e8t_gemv_tiles(int64_t N, int64_t K);
+int32_t ojx_e8t_gemv_kchunks(int64_t K);
+int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles,
+                             int64_t M, int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce, void* stream);
+
+/*
+ * Prefill-shape linear (large M) on the tcgen05 tensor cores.  Same contract as ojx_e8t_gemv;
+ * replaces the reference's TileLang builder (ojasx2/tilelang_kernels.py:277-363) and the
+ * unpack + F.linear path (lattice.py:613-624).  `workspace` holds TMA descriptors and a device
+ * status word; query its size with ojx_e8t_gemm_workspace_bytes.
+ * ojx_e8t_gemm_status reads back (synchronising the stream) whether any bounded wait inside the
+ * last gemm on that workspace expired.
+ */
+size_t  ojx_e8t_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int32_t ojx_e8t_gemm(const void* x, int32_t x_dtype, int64_t M,
+                     const uint8_t* packed, const uint16_t* scales, const void* bias,
+                     int64_t N, int64_t K, int32_t group,
+                     void* y, int32_t y_dtype,
+                     void* workspace, size_t workspace_bytes, void* stream);
+int32_t ojx_e8t_gemm_status(const void* workspace, void* stream);
+
+/*
+ * Seeded synthetic data, generated on the device: element i of stream `seed` is a sum of twelve
+ * 24-bit uniforms from splitmix64, scaled to ~N(0, sigma), then rounded to `dtype`.  Integer-exact,
+ * so host and device produce identical bits.  Used by the benchmark to fill 70B-shaped weights
+ * without a host copy.  No counterpart in the reference.
+ */
+int32_t ojx_e8t_generate(void* out, int32_t dtype, int64_t count, uint64_t seed, int64_t start,
+                         float sigma, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OJX_E8T_H */

@@ -1,0 +1,20 @@
+"""B200-native (sm_100a) implementation of the ternary-E8 quantized-linear path.
+
+Public names mirror the reference's ``ojasx3.lattice`` / ``ojasx2.streaming_e8`` /
+``ojasx3.hardware`` entry points for this path.  The package directory name contains hyphens, so
+import it with ``importlib.import_module("ojasx-open-source-cuda_b200")``.
+"""
+
+from . import _cabi, ops                                                     # noqa: F401
+from .lattice import (E8LatticeLinear, TernaryE8LatticePacker, _FusedE8GEMMFunction,   # noqa: F401
+                      _get_ternary_e8_luts, fwht_block32, pack_model_e8)
+from .streaming_e8 import (_copy_row_block_into_layer, _pack_row_block, _validate_row_layout,   # noqa: F401
+                           pack_weight_rowwise)
+from .hardware import dispatch_tilelang_e8_gemm, install_into_reference      # noqa: F401
+from .sharding import ColumnShardedLinear, shard_rows                        # noqa: F401
+
+__all__ = [
+    "E8LatticeLinear", "TernaryE8LatticePacker", "_FusedE8GEMMFunction", "pack_model_e8", "fwht_block32",
+    "pack_weight_rowwise", "dispatch_tilelang_e8_gemm", "install_into_reference", "ColumnShardedLinear",
+    "shard_rows", "ops",
+]

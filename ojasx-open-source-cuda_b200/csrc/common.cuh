@@ -1,0 +1,96 @@
+// Shared device/host helpers for the ternary-E8 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ojx_e8t.h"
+
+namespace ojx {
+
+constexpr int kNumPoints = 3281;
+
+// Device copies of the generated tables.  The whole library is one translation unit
+// (ojx_e8t.cu includes every kernel file), so file-scope statics are shared by all kernels.
+//   g_trit_nibbles[rank]  eight 4-bit fields, field i = coordinate i as {0: 0, 1: +1, 2: -1}
+//   g_raw_to_rank[raw]    base-3 raw value -> rank
+#define OJX_TABLE_QUAL static __device__
+#define OJX_TABLE_NAME(x) g_##x
+#include "e8t_tables.inc"
+#undef OJX_TABLE_QUAL
+#undef OJX_TABLE_NAME
+
+__host__ __device__ inline int effective_group(int group) {
+    // The reference replaces anything that is not a positive multiple of 16 by 16
+    // (ojasx2/math/lattice.py:346-347).
+    return (group <= 0 || group % 16 != 0) ? 16 : group;
+}
+
+inline int dtype_size(int dt) {
+    switch (dt) {
+        case OJX_F32: return 4;
+        case OJX_F16: return 2;
+        case OJX_BF16: return 2;
+        default: return 0;
+    }
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Two 12-bit ranks from one 3-byte triplet (ojasx2/math/lattice.py:397-405).
+__device__ __forceinline__ void triplet_to_codes(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t& c0, uint32_t& c1) {
+    c0 = b0 | ((b1 & 0x0Fu) << 8);
+    c1 = ((b1 >> 4) & 0x0Fu) | (b2 << 4);
+}
+
+// Coordinate i (-1, 0, +1) of a nibble-encoded trit vector.
+__device__ __forceinline__ int nibble_coord(uint32_t nib, int i) {
+    uint32_t f = (nib >> (4 * i)) & 0xFu;
+    return f == 0 ? 0 : (f == 1 ? 1 : -1);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// Validates the device once per process per device: kernels are built for sm_100a only.
+int check_arch();
+
+#define OJX_RETURN_IF(cond, code) do { if (cond) return (code); } while (0)
+
+inline int32_t launch_status() {
+    return cudaGetLastError() == cudaSuccess ? OJX_OK : OJX_ERR_LAUNCH;
+}
+
+// Entry points implemented in the individual .cu files (called by api.cu).
+int32_t encode_impl(const void* w, int w_dtype, int64_t rows, int64_t cols, int group,
+                    uint8_t* packed, uint16_t* scales, cudaStream_t s);
+int32_t decode_impl(const uint8_t* packed, const uint16_t* scales, int64_t rows, int64_t cols,
+                    int group, int out_dtype, void* out, cudaStream_t s);
+int32_t generate_impl(void* out, int dtype, int64_t count, uint64_t seed, int64_t start, float sigma,
+                      cudaStream_t s);
+size_t  gemv_workspace_bytes_impl(int64_t M, int64_t N, int64_t K);
+int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                  const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
+                  void* workspace, size_t workspace_bytes, cudaStream_t s);
+int32_t gemv_tiles_impl(int64_t N, int64_t K);
+int32_t gemv_kchunks_impl(int64_t K);
+int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
+                          int x_dtype, int y_dtype, int needs_reduce, cudaStream_t s);
+size_t  gemm_workspace_bytes_impl(int64_t M, int64_t N, int64_t K);
+int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                  const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
+                  void* workspace, size_t workspace_bytes, cudaStream_t s);
+int32_t gemm_status_impl(const void* workspace, cudaStream_t s);
+
+}  // namespace ojx

@@ -1,0 +1,90 @@
+// The whole library is this one translation unit: C ABI entry points (declared in
+// include/ojx_e8t.h) in front of the kernel files included below.  Built for sm_100a only.
+#include "common.cuh"
+#include "codec.cuh"
+#include "gemv.cuh"
+#include "gemm_tcgen05.cuh"
+
+namespace ojx {
+
+int check_arch() {
+    static int cached[64] = {0};          // 0 unknown, 1 ok, -1 wrong architecture
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return OJX_ERR_LAUNCH;
+    if (dev < 0 || dev >= 64) return OJX_ERR_ARCH;
+    if (cached[dev] == 0) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return OJX_ERR_LAUNCH;
+        cached[dev] = (major == 10) ? 1 : -1;
+    }
+    return cached[dev] == 1 ? OJX_OK : OJX_ERR_ARCH;
+}
+
+}  // namespace ojx
+
+extern "C" {
+
+int32_t ojx_e8t_version(void) { return 100; }
+
+const char* ojx_e8t_status_string(int32_t st) {
+    switch (st) {
+        case OJX_OK: return "OJX_OK";
+        case OJX_ERR_NULL: return "OJX_ERR_NULL";
+        case OJX_ERR_SHAPE: return "OJX_ERR_SHAPE";
+        case OJX_ERR_ALIGN: return "OJX_ERR_ALIGN";
+        case OJX_ERR_DTYPE: return "OJX_ERR_DTYPE";
+        case OJX_ERR_ARCH: return "OJX_ERR_ARCH";
+        case OJX_ERR_LAUNCH: return "OJX_ERR_LAUNCH";
+        case OJX_ERR_TIMEOUT: return "OJX_ERR_TIMEOUT";
+        case OJX_ERR_WORKSPACE: return "OJX_ERR_WORKSPACE";
+        case OJX_ERR_UNSUPPORTED: return "OJX_ERR_UNSUPPORTED";
+        default: return "OJX_ERR_UNKNOWN";
+    }
+}
+
+int32_t ojx_e8t_encode(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
+                       uint8_t* packed_out, uint16_t* scales_out, void* stream) {
+    return ojx::encode_impl(w, w_dtype, rows, cols, group, packed_out, scales_out, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_decode(const uint8_t* packed, const uint16_t* scales, int64_t rows, int64_t cols,
+                       int32_t group, int32_t out_dtype, void* out, void* stream) {
+    return ojx::decode_impl(packed, scales, rows, cols, group, out_dtype, out, (cudaStream_t)stream);
+}
+
+size_t ojx_e8t_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) { return ojx::gemv_workspace_bytes_impl(M, N, K); }
+
+int32_t ojx_e8t_gemv(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                     const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+    return ojx::gemv_impl(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, workspace, workspace_bytes,
+                          (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_gemv_tiles(int64_t N, int64_t K) { return ojx::gemv_tiles_impl(N, K); }
+int32_t ojx_e8t_gemv_kchunks(int64_t K) { return ojx::gemv_kchunks_impl(K); }
+
+int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles, int64_t M,
+                             int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce, void* stream) {
+    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, (cudaStream_t)stream);
+}
+
+size_t ojx_e8t_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) { return ojx::gemm_workspace_bytes_impl(M, N, K); }
+
+int32_t ojx_e8t_gemm(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                     const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+    return ojx::gemm_impl(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, workspace, workspace_bytes,
+                          (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_gemm_status(const void* workspace, void* stream) {
+    return ojx::gemm_status_impl(workspace, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_generate(void* out, int32_t dtype, int64_t count, uint64_t seed, int64_t start, float sigma,
+                         void* stream) {
+    return ojx::generate_impl(out, dtype, count, seed, start, sigma, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,236 @@
+"""Host-side mirror of the reference's ternary-E8 interface, backed by the sm_100a kernels.
+
+Same names, argument meaning and error behaviour as the reference module
+``ojasx2/math/lattice.py`` (re-exported there as ``ojasx3.lattice``), restricted to the
+1.5-bit ternary-E8 path:
+
+* :class:`TernaryE8LatticePacker`   (reference ``lattice.py:335-419``)
+* :class:`_FusedE8GEMMFunction`     (reference ``lattice.py:548-717``)
+* :class:`E8LatticeLinear`          (reference ``lattice.py:724-846``)
+* :func:`pack_model_e8`             (reference ``lattice.py:901-945``)
+* :func:`fwht_block32`              (reference ``lattice.py:91-102``)
+* :func:`_get_ternary_e8_luts`      (reference ``lattice.py:292-332``)
+
+Differences, all deliberate: tensors must live on a CUDA device (the kernels are the only
+implementation; nothing falls back to CPU or to PyTorch ops), other bit-rates raise
+``NotImplementedError``, and no dense weight matrix is ever materialised in the forward pass.
+"""
+
+from __future__ import annotations
+
+import copy
+import math
+from typing import Optional, Tuple, Union
+
+import torch
+import torch.nn as nn
+
+from . import ops
+
+_SUPPORTED_BITRATE = 1.5
+
+
+def _check_bitrate(bitrate: float) -> None:
+    if float(bitrate) != _SUPPORTED_BITRATE:
+        raise NotImplementedError(
+            f"bitrate={bitrate!r}: the B200 backend implements the 1.5-bit ternary-E8 path only")
+
+
+def fwht_block32(x: torch.Tensor) -> torch.Tensor:
+    """Normalised 32-point Walsh-Hadamard transform over consecutive blocks of the last dimension.
+
+    Same butterfly order and final scaling as the reference (``lattice.py:91-102``), so results are
+    bit-identical; tensors whose last dimension is not a multiple of 32 are returned unchanged.
+    """
+    if x.shape[-1] == 0 or x.shape[-1] % 32 != 0:
+        return x
+    h = x.reshape(-1, 32)
+    span = 1
+    while span < 32:
+        v = h.reshape(-1, 32 // (2 * span), 2, span)
+        a, b = v[:, :, 0, :], v[:, :, 1, :]
+        h = torch.stack([a + b, a - b], dim=2).reshape(-1, 32)
+        span *= 2
+    return (h * 0.1767766952966369).reshape(x.shape)
+
+
+_LUT_CACHE = {}
+
+
+def _get_ternary_e8_luts(device: Optional[Union[str, torch.device]] = None):
+    """``(rank_to_coords int8[3281,8], raw_to_rank int64[6561], powers int64[8])`` in the reference's
+    enumeration order (``lattice.py:305-321``).  The kernels carry their own compiled-in tables; this
+    function exists for callers that index the tables directly."""
+    dev = torch.device("cpu") if device is None else torch.device(device)
+    key = (dev.type, dev.index)
+    if key not in _LUT_CACHE:
+        raw = torch.arange(3 ** 8, dtype=torch.int64)
+        digits = torch.stack([(raw // 3 ** i) % 3 for i in range(8)], dim=1) - 1
+        valid = digits.sum(dim=1) % 2 == 0
+        raw_to_rank = torch.zeros(3 ** 8, dtype=torch.int64)
+        raw_to_rank[valid] = torch.arange(int(valid.sum()), dtype=torch.int64)
+        coords = digits[valid].to(torch.int8)
+        powers = torch.tensor([3 ** i for i in range(8)], dtype=torch.int64)
+        _LUT_CACHE[key] = (coords.to(dev), raw_to_rank.to(dev), powers.to(dev))
+    return _LUT_CACHE[key]
+
+
+class TernaryE8LatticePacker:
+    """Packs weight matrices into 1.50 bits/weight over D8 ∩ {-1, 0, +1}^8 (3,281 points)."""
+
+    @staticmethod
+    def pack(w: torch.Tensor, group_size: int = 32) -> Tuple[torch.Tensor, torch.Tensor, Tuple[int, int]]:
+        """Returns ``(packed uint8 1-D, scales float16 1-D, (rows, cols))``; bit-exact with the
+        reference's CPU packer for fp32, fp16 and bf16 inputs."""
+        if w.dim() != 2:
+            raise ValueError(f"not enough values to unpack: expected a 2-D weight, got {tuple(w.shape)}")
+        m, n = int(w.shape[0]), int(w.shape[1])
+        src = w if w.dtype in (torch.float32, torch.float16, torch.bfloat16) else w.to(torch.float32)
+        packed, scales = ops.encode(src, group_size)
+        return packed, scales, (m, n)
+
+    @staticmethod
+    def unpack(packed_codes: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, int],
+               dtype: torch.dtype = torch.float32, use_workspace: bool = False) -> torch.Tensor:
+        """Dense ``[rows, cols]`` weights in ``dtype``.  ``use_workspace`` is accepted for signature
+        compatibility; the forward pass never needs a decoded matrix, so no cache is kept."""
+        del use_workspace
+        return ops.decode(packed_codes, scales, (int(shape[0]), int(shape[1])), dtype)
+
+
+def _get_packer_for_bitrate(bitrate: float):
+    _check_bitrate(bitrate)
+    return TernaryE8LatticePacker
+
+
+class _FusedE8GEMMFunction(torch.autograd.Function):
+    """``y = x . dequant(W)^T + bias`` straight from the packed codes.
+
+    Nine inputs and nine gradients, as in the reference (``lattice.py:551-563,717``).  Forward runs the
+    fused kernels; x is not saved for backward (only the packed buffers are).  Backward (outside the
+    accelerated path) decodes W once with the decode kernel and multiplies with ``torch.matmul``.
+    """
+
+    @staticmethod
+    def forward(ctx, x, packed_weight, block_scales, bias, out_features, in_features, group_size, bitrate,
+                use_hadamard=False):
+        _check_bitrate(bitrate)
+        x_rot = fwht_block32(x) if (use_hadamard and in_features % 32 == 0) else x
+        ctx.save_for_backward(packed_weight, block_scales)
+        ctx.x_shape = x_rot.shape
+        ctx.x_dtype = x_rot.dtype
+        ctx.in_features = in_features
+        ctx.out_features = out_features
+        ctx.has_bias = bias is not None
+        ctx.use_hadamard = use_hadamard
+        x_2d = x_rot.reshape(-1, in_features)
+        y_2d = ops.linear(x_2d, packed_weight, block_scales, bias, out_features, in_features, group_size)
+        return y_2d.reshape(*x_rot.shape[:-1], out_features)
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        packed_weight, block_scales = ctx.saved_tensors
+        gy_2d = grad_y.reshape(-1, ctx.out_features).contiguous()
+        w = ops.decode(packed_weight, block_scales, (ctx.out_features, ctx.in_features), ctx.x_dtype)
+        grad_x = gy_2d.to(ctx.x_dtype).matmul(w).reshape(ctx.x_shape)
+        if ctx.use_hadamard and ctx.in_features % 32 == 0:
+            grad_x = fwht_block32(grad_x)
+        grad_bias = gy_2d.sum(dim=0) if ctx.has_bias else None
+        return grad_x, None, None, grad_bias, None, None, None, None, None
+
+
+class E8LatticeLinear(nn.Module):
+    """Linear layer whose base weights are packed ternary-E8 codes (buffers ``packed_weight`` uint8 and
+    ``block_scales`` float16, optional ``bias`` and LoRA factors ``lora_A [K, r]``, ``lora_B [r, N]``);
+    state-dict compatible with the reference layer (``lattice.py:727-781``)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, rank: int = 0,
+                 lora_alpha: float = 16.0, group_size: int = 8, bitrate: float = 2.0, use_hadamard: bool = False,
+                 device: Optional[torch.device] = None, dtype: Optional[torch.dtype] = None) -> None:
+        super().__init__()
+        _check_bitrate(bitrate)
+        self.in_features = in_features
+        self.out_features = out_features
+        self.rank = rank
+        self.lora_alpha = lora_alpha
+        self.scaling = (lora_alpha / rank) if rank > 0 else 0.0
+        self.bitrate = float(bitrate)
+        self.use_hadamard = bool(use_hadamard and (in_features % 32 == 0))
+        eff_group = group_size if (group_size >= 16 and group_size % 16 == 0) else 16
+        self.group_size = eff_group
+        num_bytes, num_scales = ops.packed_sizes(out_features, in_features, eff_group)
+        self.register_buffer("packed_weight", torch.zeros(num_bytes, dtype=torch.uint8, device=device))
+        self.register_buffer("block_scales", torch.ones(num_scales, dtype=torch.float16, device=device))
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device))
+        else:
+            self.register_parameter("bias", None)
+        if rank > 0:
+            self.lora_A = nn.Parameter(torch.zeros(in_features, rank, dtype=dtype, device=device))
+            self.lora_B = nn.Parameter(torch.zeros(rank, out_features, dtype=dtype, device=device))
+            nn.init.kaiming_uniform_(self.lora_A, a=math.sqrt(5))
+            nn.init.zeros_(self.lora_B)
+        else:
+            self.register_parameter("lora_A", None)
+            self.register_parameter("lora_B", None)
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, rank: int = 0, lora_alpha: float = 16.0, group_size: int = 8,
+                    bitrate: float = 2.0, use_hadamard: bool = False) -> "E8LatticeLinear":
+        _check_bitrate(bitrate)
+        eff_gs = max(16, group_size)
+        m = cls(linear.in_features, linear.out_features, bias=(linear.bias is not None), rank=rank,
+                lora_alpha=lora_alpha, group_size=eff_gs, bitrate=bitrate, use_hadamard=use_hadamard,
+                device=linear.weight.device, dtype=linear.weight.dtype)
+        with torch.no_grad():
+            w_to_pack = fwht_block32(linear.weight) if m.use_hadamard else linear.weight
+            ops.encode(w_to_pack, m.group_size, out=(m.packed_weight, m.block_scales))
+            if linear.bias is not None:
+                m.bias.copy_(linear.bias)
+        return m
+
+    def unpack_weights(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        w = TernaryE8LatticePacker.unpack(self.packed_weight, self.block_scales,
+                                          (self.out_features, self.in_features), dtype=dtype)
+        return fwht_block32(w) if self.use_hadamard else w
+
+    def forward_fused(self, x: torch.Tensor) -> torch.Tensor:
+        out = _FusedE8GEMMFunction.apply(x, self.packed_weight, self.block_scales, self.bias, self.out_features,
+                                         self.in_features, self.group_size, self.bitrate, self.use_hadamard)
+        if self.rank > 0 and self.lora_A is not None and self.lora_B is not None:
+            lora_a = self.lora_A.to(x.dtype) if self.lora_A.dtype != x.dtype else self.lora_A
+            lora_b = self.lora_B.to(x.dtype) if self.lora_B.dtype != x.dtype else self.lora_B
+            out = out + self.scaling * ((x @ lora_a) @ lora_b)
+        return out
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.forward_fused(x)
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bitrate={self.bitrate}, "
+                f"group_size={self.group_size}, rank={self.rank}, use_hadamard={self.use_hadamard}")
+
+
+def pack_model_e8(model: nn.Module, rank: int = 0, lora_alpha: float = 16.0, group_size: int = 32,
+                  bitrate: float = 2.0, use_hadamard: bool = False,
+                  target_modules: Optional[Union[list, tuple, str]] = None,
+                  exclude_modules: Optional[Union[list, tuple]] = None, inplace: bool = True) -> nn.Module:
+    """Recursively replaces ``nn.Linear`` children by :class:`E8LatticeLinear` (``lattice.py:901-945``);
+    name filters are substring matches on the child name, as in the reference."""
+    _check_bitrate(bitrate)
+    target_model = model if inplace else copy.deepcopy(model)
+    if isinstance(target_modules, str):
+        target_modules = [target_modules]
+    for name, module in target_model.named_children():
+        if exclude_modules is not None and any(ex in name for ex in exclude_modules):
+            continue
+        targeted = True if target_modules is None else any(t in name for t in target_modules)
+        if isinstance(module, nn.Linear) and targeted:
+            setattr(target_model, name, E8LatticeLinear.from_linear(
+                module, rank=rank, lora_alpha=lora_alpha, group_size=group_size, bitrate=bitrate,
+                use_hadamard=use_hadamard))
+        else:
+            pack_model_e8(module, rank=rank, lora_alpha=lora_alpha, group_size=group_size, bitrate=bitrate,
+                          use_hadamard=use_hadamard, target_modules=target_modules,
+                          exclude_modules=exclude_modules, inplace=True)
+    return target_model

@@ -1,0 +1,272 @@
+"""Tensor-level wrappers over the C ABI: encode, decode, decode-shape and prefill-shape linear.
+
+torch is used only for device memory and streams; every computation is a call into
+``libojx_e8t.so`` through plain pointers.  All functions require CUDA tensors and raise if
+the library is missing - there is no CPU or PyTorch fallback on this path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _cabi
+
+_DT = {torch.float32: _cabi.OJX_F32, torch.float16: _cabi.OJX_F16, torch.bfloat16: _cabi.OJX_BF16}
+
+# Largest M handled by the decode-shape kernel; larger batches go to the tensor-core GEMM.
+GEMV_MAX_M = 16
+
+_scratch: Dict[Tuple[int, int, str], torch.Tensor] = {}
+
+
+def _dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dt}; expected float32, float16 or bfloat16") from None
+
+
+def _require_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("the B200 ternary-E8 backend needs CUDA tensors (no CPU fallback on this path)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"tensors on different devices: {dev} and {t.device}")
+    assert dev is not None
+    return dev
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def scratch(device: torch.device, nbytes: int, tag: str = "ws") -> torch.Tensor:
+    """Grow-only scratch buffer per (device, stream, tag) - the counterpart of the reference's
+    ``_get_ephemeral_workspace`` (ojasx2/math/lattice.py:62-84), but only a few KB..MB of fp32
+    partial sums instead of a full decoded weight matrix."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           int(torch.cuda.current_stream(device).cuda_stream), tag)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def effective_group(group_size: int) -> int:
+    """The packer's coercion rule (ojasx2/math/lattice.py:346-347)."""
+    return 16 if (group_size <= 0 or group_size % 16 != 0) else int(group_size)
+
+
+def packed_sizes(rows: int, cols: int, group_size: int) -> Tuple[int, int]:
+    g = effective_group(group_size)
+    total = rows * cols
+    padded = total + ((-total) % g)
+    return padded * 3 // 16, padded // g
+
+
+def encode(w: torch.Tensor, group_size: int = 32, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+           ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``w`` [rows, cols] -> (packed uint8[P*3/16], scales fp16[P/g]); bit-exact with the
+    reference's ``TernaryE8LatticePacker.pack``."""
+    if w.dim() != 2:
+        raise ValueError(f"expected a 2-D weight, got shape {tuple(w.shape)}")
+    dev = _require_cuda(w)
+    rows, cols = int(w.shape[0]), int(w.shape[1])
+    if rows == 0 or cols == 0:
+        raise ValueError("empty weight")
+    wc = w.detach().contiguous()
+    nbytes, nscales = packed_sizes(rows, cols, group_size)
+    if out is None:
+        packed = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        scales = torch.empty(nscales, dtype=torch.float16, device=dev)
+    else:
+        packed, scales = out
+        if packed.numel() != nbytes or scales.numel() != nscales or packed.dtype != torch.uint8 \
+                or scales.dtype != torch.float16 or not packed.is_contiguous() or not scales.is_contiguous():
+            raise ValueError("output buffers have the wrong size, dtype or layout")
+    with torch.cuda.device(dev):
+        st = _cabi.lib().ojx_e8t_encode(wc.data_ptr(), _dtype_code(wc.dtype), rows, cols, int(group_size),
+                                        packed.data_ptr(), scales.data_ptr(), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_encode")
+    return packed, scales
+
+
+def decode(packed: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, int], dtype: torch.dtype = torch.float32,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Packed codes + scales -> dense [rows, cols] in ``dtype`` (the group size is inferred from the
+    buffer sizes exactly as the reference does, ojasx2/math/lattice.py:407-409)."""
+    dev = _require_cuda(packed, scales)
+    rows, cols = int(shape[0]), int(shape[1])
+    if packed.dtype != torch.uint8 or scales.dtype != torch.float16:
+        raise TypeError("packed must be uint8 and scales float16")
+    if packed.numel() % 3 != 0:
+        raise ValueError("packed length must be a multiple of 3")
+    padded = (packed.numel() // 3) * 16
+    group = padded // max(1, scales.numel())
+    if rows * cols > padded or group % 16 != 0 or group * scales.numel() != padded:
+        raise ValueError("packed/scales sizes are inconsistent with the requested shape")
+    pk, sc = packed.contiguous(), scales.contiguous()
+    if out is None:
+        out = torch.empty((rows, cols), dtype=dtype, device=dev)
+    elif out.numel() != rows * cols or out.dtype != dtype or not out.is_contiguous():
+        raise ValueError("output buffer has the wrong size, dtype or layout")
+    with torch.cuda.device(dev):
+        st = _cabi.lib().ojx_e8t_decode(pk.data_ptr(), sc.data_ptr(), rows, cols, group, _dtype_code(dtype),
+                                        out.data_ptr(), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_decode")
+    return out.view(rows, cols)
+
+
+def generate(count: int, seed: int, sigma: float, dtype: torch.dtype, device: torch.device, start: int = 0,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Seeded ~N(0, sigma) values produced on the device (same bits as the numpy generator of the test oracle)."""
+    if out is None:
+        out = torch.empty(count, dtype=dtype, device=device)
+    with torch.cuda.device(device):
+        st = _cabi.lib().ojx_e8t_generate(out.data_ptr(), _dtype_code(dtype), int(count), int(seed) & (2 ** 64 - 1),
+                                          int(start), float(sigma), _stream_ptr(out.device))
+    _cabi.check(st, "ojx_e8t_generate")
+    return out
+
+
+def _prep_linear(x2d, packed, scales, bias, n, k):
+    dev = _require_cuda(x2d, packed, scales, bias)
+    if x2d.dim() != 2 or x2d.shape[1] != k:
+        raise ValueError(f"x must be [M, {k}], got {tuple(x2d.shape)}")
+    if packed.dtype != torch.uint8 or scales.dtype != torch.float16:
+        raise TypeError("packed must be uint8 and scales float16")
+    x2d = x2d.contiguous()
+    b = None
+    if bias is not None:
+        if bias.numel() != n:
+            raise ValueError("bias has the wrong length")
+        b = bias.detach().to(x2d.dtype).contiguous()       # the reference casts bias to x's dtype (lattice.py:622)
+    return dev, x2d, packed.contiguous(), scales.contiguous(), b
+
+
+def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
+           out_features: int, in_features: int, group_size: int = 32,
+           out_dtype: Optional[torch.dtype] = None, force: Optional[str] = None) -> torch.Tensor:
+    """y[M, N] = x[M, K] . dequant(W)^T (+ bias), output in x's dtype unless ``out_dtype`` is given.
+
+    Routing: M <= 16 -> decode-shape kernel (``ojx_e8t_gemv``); larger M with K % 256 == 0 and 16-bit
+    activations -> tcgen05 kernel (``ojx_e8t_gemm``); everything else -> the generic kernel inside
+    ``ojx_e8t_gemv``.  ``force`` ("gemv" or "gemm") overrides the routing for tests.
+    """
+    n, k = int(out_features), int(in_features)
+    dev, x2d, pk, sc, b = _prep_linear(x2d, packed, scales, bias, n, k)
+    m = int(x2d.shape[0])
+    ydt = out_dtype or x2d.dtype
+    y = torch.empty((m, n), dtype=ydt, device=dev)
+    if m == 0:
+        return y
+    g = effective_group(group_size)
+    lib = _cabi.lib()
+    use_gemm = (m > GEMV_MAX_M and k % 256 == 0 and g == 32 and x2d.dtype in (torch.bfloat16, torch.float16)
+                and (k * 3 // 16) * n == pk.numel())
+    if force == "gemm":
+        use_gemm = True
+    elif force == "gemv":
+        use_gemm = False
+    with torch.cuda.device(dev):
+        if use_gemm:
+            need = lib.ojx_e8t_gemm_workspace_bytes(m, n, k)
+            ws = scratch(dev, need, "gemm")
+            st = lib.ojx_e8t_gemm(x2d.data_ptr(), _dtype_code(x2d.dtype), m, pk.data_ptr(), sc.data_ptr(),
+                                  b.data_ptr() if b is not None else None, n, k, g, y.data_ptr(), _dtype_code(ydt),
+                                  ws.data_ptr(), ws.numel(), _stream_ptr(dev))
+            _cabi.check(st, "ojx_e8t_gemm")
+        else:
+            need = lib.ojx_e8t_gemv_workspace_bytes(m, n, k)
+            ws = scratch(dev, need, "gemv") if need else None
+            st = lib.ojx_e8t_gemv(x2d.data_ptr(), _dtype_code(x2d.dtype), m, pk.data_ptr(), sc.data_ptr(),
+                                  b.data_ptr() if b is not None else None, n, k, g, y.data_ptr(), _dtype_code(ydt),
+                                  ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                  _stream_ptr(dev))
+            _cabi.check(st, "ojx_e8t_gemv")
+    return y
+
+
+def gemm_status(device: torch.device) -> None:
+    """Raise if a bounded wait inside the last prefill GEMM on this device/stream expired."""
+    ws = scratch(device, 16, "gemm")
+    with torch.cuda.device(device):
+        st = _cabi.lib().ojx_e8t_gemm_status(ws.data_ptr(), _stream_ptr(device))
+    _cabi.check(st, "ojx_e8t_gemm (device status)")
+
+
+class GroupedGemv:
+    """Several independent decode-shape linears launched as ONE kernel.
+
+    All buffers are fixed at construction (activations, outputs, packed weights), so the device
+    descriptor table is built once and a call is a single launch - suitable for CUDA graphs.
+    Typical groups: q/k/v of one layer, gate/up of one layer, or a benchmark's rotation of matrices.
+    """
+
+    def __init__(self, entries: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor], torch.Tensor]],
+                 shapes: Sequence[Tuple[int, int]]):
+        # entries: (x[M,K], packed, scales, bias-or-None, y[M,N]);  shapes: (N, K)
+        if not entries:
+            raise ValueError("empty problem list")
+        lib = _cabi.lib()
+        self.device = _require_cuda(*[t for e in entries for t in e if t is not None])
+        self.M = int(entries[0][0].shape[0])
+        self.x_dtype = entries[0][0].dtype
+        self.y_dtype = entries[0][4].dtype
+        if not (1 <= self.M <= GEMV_MAX_M):
+            raise ValueError(f"grouped decode-shape launch needs 1 <= M <= {GEMV_MAX_M}")
+        if self.x_dtype not in (torch.bfloat16, torch.float16):
+            raise TypeError("activations must be bfloat16 or float16")
+        arr = (_cabi.GemvProblem * len(entries))()
+        self._keep: List[torch.Tensor] = []
+        tile_begin, partial_bytes = 0, 0
+        offsets = []
+        for (x, pk, sc, b, y), (n, k) in zip(entries, shapes):
+            if k % 256 != 0:
+                raise ValueError("grouped launch needs K % 256 == 0")
+            if x.shape != (self.M, k) or y.shape != (self.M, n) or x.dtype != self.x_dtype or y.dtype != self.y_dtype:
+                raise ValueError("inconsistent shapes or dtypes in the problem list")
+            if pk.numel() != n * k * 3 // 16 or sc.numel() != n * k // 32:
+                raise ValueError("packed/scales sizes do not match (N, K)")
+            for t in (x, pk, sc, y):
+                if not t.is_contiguous() or t.data_ptr() % 16 != 0:
+                    raise ValueError("buffers must be contiguous and 16-byte aligned")
+            kc = lib.ojx_e8t_gemv_kchunks(k)
+            offsets.append(partial_bytes if kc > 1 else -1)
+            if kc > 1:
+                partial_bytes += kc * self.M * n * 4
+        self.partials = torch.empty(max(partial_bytes, 16), dtype=torch.uint8, device=self.device)
+        for i, ((x, pk, sc, b, y), (n, k)) in enumerate(zip(entries, shapes)):
+            bb = None
+            if b is not None:
+                bb = b.detach().to(self.x_dtype).contiguous()
+                self._keep.append(bb)
+            p = arr[i]
+            p.x, p.packed, p.scales, p.y = x.data_ptr(), pk.data_ptr(), sc.data_ptr(), y.data_ptr()
+            p.bias = bb.data_ptr() if bb is not None else None
+            p.partial = (self.partials.data_ptr() + offsets[i]) if offsets[i] >= 0 else None
+            p.N, p.K, p.tile_begin, p.reserved = n, k, tile_begin, 0
+            tile_begin += lib.ojx_e8t_gemv_tiles(n, k)
+            self._keep.extend([x, pk, sc, y])
+        self.count = len(entries)
+        self.total_tiles = tile_begin
+        self.needs_reduce = 1 if partial_bytes > 0 else 0
+        raw = bytes(arr)
+        self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self.device)
+        self.packed_bytes = sum(n * k // 4 for n, k in shapes)
+
+    def __call__(self) -> None:
+        with torch.cuda.device(self.device):
+            st = _cabi.lib().ojx_e8t_gemv_grouped(self.table.data_ptr(), self.count, self.total_tiles, self.M,
+                                                  _dtype_code(self.x_dtype), _dtype_code(self.y_dtype),
+                                                  self.needs_reduce, _stream_ptr(self.device))
+        _cabi.check(st, "ojx_e8t_gemv_grouped")

@@ -1,0 +1,175 @@
+"""CPU-side checks: the C-ABI library loads and exports every declared symbol (no compute calls),
+the header and the binding agree, the host mirror keeps the reference's names/signatures/errors,
+and the column-sharding logic works across two gloo ranks."""
+
+import ctypes
+import inspect
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, load_pkg
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def P():
+    pkg = load_pkg()
+    pkg._cabi.build()              # nvcc cross-compiles sm_100a without a GPU
+    return pkg
+
+
+def header_functions():
+    text = open(os.path.join(ROOT, "include", "ojx_e8t.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ojx_e8t_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(P):
+    lib = ctypes.CDLL(P._cabi.LIB_PATH)
+    declared = header_functions()
+    assert declared, "no declarations found in the header"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/ojx_e8t.h but not exported"
+    assert sorted(P._cabi.EXPORTED_SYMBOLS) == declared
+    assert P._cabi.lib().ojx_e8t_version() >= 100
+    assert P._cabi.status_name(0) == "OJX_OK" and P._cabi.status_name(-7) == "OJX_ERR_TIMEOUT"
+
+
+def test_pure_host_entry_points(P):
+    lib = P._cabi.lib()
+    # tile / chunk arithmetic is host-only
+    assert lib.ojx_e8t_gemv_kchunks(4096) == 1 and lib.ojx_e8t_gemv_kchunks(14336) == 4
+    assert lib.ojx_e8t_gemv_kchunks(8192) == 2 and lib.ojx_e8t_gemv_kchunks(100) == 0
+    assert lib.ojx_e8t_gemv_tiles(4096, 4096) == 256 and lib.ojx_e8t_gemv_tiles(4096, 14336) == 1024
+    assert lib.ojx_e8t_gemv_tiles(17, 256) == 2
+    assert lib.ojx_e8t_gemv_workspace_bytes(4, 4096, 4096) == 0
+    assert lib.ojx_e8t_gemv_workspace_bytes(4, 4096, 14336) == 4 * 4 * 4096 * 4
+    assert lib.ojx_e8t_gemm_workspace_bytes(2048, 4096, 4096) >= 16
+    assert ctypes.sizeof(P._cabi.GemvProblem) == 64
+
+
+def test_argument_validation_needs_no_gpu(P):
+    lib = P._cabi.lib()
+    assert lib.ojx_e8t_encode(None, 0, 4, 32, 32, None, None, None) == -1          # null
+    assert lib.ojx_e8t_decode(None, None, 4, 32, 32, 0, None, None) == -1
+    buf = (ctypes.c_uint8 * 64)()
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.ojx_e8t_encode(p, 0, 0, 32, 32, p, p, None) == -2                   # empty shape
+    assert lib.ojx_e8t_gemv(p, 2, 0, p, p, None, 4, 256, 32, p, 2, None, 0, None) == -2
+    assert lib.ojx_e8t_gemv(p, 9, 1, p, p, None, 4, 256, 32, p, 2, None, 0, None) == -4   # bad dtype
+
+
+def test_mirror_keeps_reference_signatures(P):
+    sig = inspect.signature
+    assert list(sig(P.TernaryE8LatticePacker.pack).parameters) == ["w", "group_size"]
+    assert list(sig(P.TernaryE8LatticePacker.unpack).parameters) == ["packed_codes", "scales", "shape", "dtype", "use_workspace"]
+    assert list(sig(P._FusedE8GEMMFunction.forward).parameters) == [
+        "ctx", "x", "packed_weight", "block_scales", "bias", "out_features", "in_features", "group_size", "bitrate", "use_hadamard"]
+    assert list(sig(P.E8LatticeLinear.__init__).parameters) == [
+        "self", "in_features", "out_features", "bias", "rank", "lora_alpha", "group_size", "bitrate", "use_hadamard", "device", "dtype"]
+    assert list(sig(P.dispatch_tilelang_e8_gemm).parameters) == [
+        "x_2d", "packed_weight", "block_scales", "bias", "out_features", "in_features", "group_size", "bitrate", "lut_coords"]
+    prw = sig(P.pack_weight_rowwise).parameters
+    assert [prw[k].default for k in ("bitrate", "group_size", "row_block", "use_hadamard")] == [1.5, 32, 32, False]
+    assert sig(P.E8LatticeLinear.__init__).parameters["bitrate"].default == 2.0
+    assert sig(P.pack_model_e8).parameters["group_size"].default == 32
+
+
+def test_layer_buffers_and_errors_on_cpu(P):
+    layer = P.E8LatticeLinear(128, 64, bias=True, rank=2, group_size=32, bitrate=1.5)
+    assert layer.packed_weight.numel() == 64 * 128 * 3 // 16 and layer.packed_weight.dtype == torch.uint8
+    assert layer.block_scales.numel() == 64 * 128 // 32 and layer.block_scales.dtype == torch.float16
+    assert tuple(layer.lora_A.shape) == (128, 2) and tuple(layer.lora_B.shape) == (2, 64)
+    odd = P.E8LatticeLinear(13, 7, bias=False, group_size=8, bitrate=1.5)      # padded flat layout, group coerced to 16
+    assert odd.group_size == 16 and odd.packed_weight.numel() == 96 * 3 // 16 and odd.block_scales.numel() == 6
+    with pytest.raises(NotImplementedError):
+        P.E8LatticeLinear(64, 8)                       # default bit-rate 2.0 is outside this backend
+    with pytest.raises(RuntimeError):
+        layer(torch.zeros(1, 128))                     # CPU tensors: the CUDA path is the only path
+    with pytest.raises(ValueError):
+        P.pack_weight_rowwise(torch.zeros(4, 48), group_size=32)
+    with pytest.raises(ValueError):
+        P.pack_weight_rowwise(torch.zeros(4, 64), group_size=16)
+    with pytest.raises(ValueError):
+        P.pack_weight_rowwise(torch.zeros(4, 64), row_block=0)
+    with pytest.raises(ValueError):
+        P.pack_weight_rowwise(torch.zeros(64), group_size=32)
+    assert P.dispatch_tilelang_e8_gemm(torch.zeros(1, 32), torch.zeros(6, dtype=torch.uint8),
+                                       torch.ones(1, dtype=torch.float16), None, 1, 32, 32, 1.5) is None
+
+
+def test_luts_and_fwht_match_oracle(P, oracle):
+    coords, raw_to_rank, powers = P._get_ternary_e8_luts()
+    oc, orr = oracle.ternary_luts()
+    assert np.array_equal(coords.numpy(), oc) and np.array_equal(raw_to_rank.numpy(), orr)
+    assert powers.tolist() == [3 ** i for i in range(8)]
+    x = torch.from_numpy(oracle.gen_normal(3, 4 * 64, 1.0).reshape(4, 64))
+    y = P.fwht_block32(x)
+    # orthonormal and an involution; untouched when the last dimension is not a multiple of 32
+    assert torch.allclose(P.fwht_block32(y), x, atol=1e-5)
+    assert torch.allclose(y.norm(), x.norm(), rtol=1e-5)
+    z = torch.zeros(2, 33)
+    assert P.fwht_block32(z) is z
+    h = P.fwht_block32(torch.eye(32))
+    assert torch.allclose(h.abs(), torch.full((32, 32), 32 ** -0.5))
+
+
+def test_shard_rows_cover_everything(P):
+    from importlib import import_module
+    sh = import_module(P.__name__ + ".sharding")
+    for n in (1, 15, 16, 17, 1024, 4096, 14336, 100):
+        for world in (1, 2, 3, 4, 8):
+            spans = [sh.shard_rows(n, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert all(s[0] % 16 == 0 for s in spans)
+    with pytest.raises(ValueError):
+        sh.shard_rows(10, 2, 2)
+
+
+_WORKER = r'''
+import importlib, os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["OJX_ROOT"])
+from oracle import e8t_oracle as O
+pkg = importlib.import_module("ojasx-open-source-cuda_b200")
+sh = importlib.import_module("ojasx-open-source-cuda_b200.sharding")
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+N, K, M = int(os.environ["OJX_N"]), 256, 3
+w = O.gen_normal(5, N * K, 0.02).reshape(N, K)
+packed_np, scales_np, _ = O.encode(w, 32)
+x = O.gen_normal(6, M * K, 1.0).reshape(M, K)
+bias = O.gen_normal(7, N, 0.1)
+def cpu_compute(x2d, pk, sc, b, n, k, g):      # stand-in for the CUDA kernel: the test's own oracle
+    y = O.linear_fp32(x2d.numpy(), pk.numpy(), sc.numpy().view(np.float16), n, k, None if b is None else b.numpy())
+    return torch.from_numpy(y)
+lin = sh.ColumnShardedLinear(torch.from_numpy(packed_np), torch.from_numpy(scales_np.view(np.int16)).view(torch.float16),
+                             torch.from_numpy(bias), N, K, 32, rank, world, None, compute=cpu_compute)
+y = lin(torch.from_numpy(x))
+ref = O.linear_fp32(x, packed_np, scales_np, N, K, bias)
+assert tuple(y.shape) == (M, N), y.shape
+assert np.array_equal(y.numpy(), ref), "sharded result differs"
+dist.barrier()
+if rank == 0:
+    print("SHARD_OK", lin.sizes)
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.parametrize("n_rows", [64, 50])      # equal shards, and a ragged last shard
+def test_column_sharding_two_gloo_ranks(tmp_path, n_rows):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    env = dict(os.environ, OJX_ROOT=ROOT, OJX_N=str(n_rows), MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(29611 + n_rows % 7), str(script)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert "SHARD_OK" in proc.stdout

@@ -1,0 +1,301 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI, against the CPU oracle and the
+golden vectors generated from the reference.  Bit-exact for codes, scales and decoded weights;
+the GEMM contract (max-abs <= 1e-2*|x|_inf*sqrt(K), rel-L2 <= 2e-3) for the linear kernels."""
+
+import hashlib
+import math
+
+import numpy as np
+import pytest
+
+from conftest import case_input, have_cuda, load_pkg
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+@pytest.fixture(scope="module")
+def P():
+    if not have_cuda():
+        pytest.skip("no CUDA device")
+    pkg = load_pkg()
+    pkg._cabi.lib()          # fails loudly when the extension is missing
+    return pkg
+
+
+DEV = "cuda:0"
+TD = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def to_dev(w_np, dtype):
+    t = torch.from_numpy(np.ascontiguousarray(w_np).astype(np.float32))
+    return t.to(TD[dtype]).to(DEV)       # values are already representable in the target dtype
+
+
+def f16_bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def test_generator_matches_oracle(P, oracle):
+    for dt, name in ((torch.float32, "f32"), (torch.float16, "f16"), (torch.bfloat16, "bf16")):
+        got = P.ops.generate(5000, 7, 0.02, dt, torch.device(DEV), start=123)
+        ref = oracle.gen_normal(7, 5000, 0.02, start=123)
+        if name == "f32":
+            assert np.array_equal(got.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+        elif name == "f16":
+            assert np.array_equal(f16_bits(got), ref.astype(np.float16).view(np.uint16))
+        else:
+            assert np.array_equal(f16_bits(got), oracle.f32_to_bf16_bits(ref))
+
+
+def test_encode_bit_exact_golden_cases(P, golden, oracle):
+    meta, arrays = golden
+    for case in meta["cases"]:
+        w = case_input(oracle, case)
+        wt = to_dev(w, case["dtype"])
+        packed, scales, shape = P.TernaryE8LatticePacker.pack(wt, group_size=case["group"])
+        assert shape == (case["rows"], case["cols"])
+        assert packed.numel() == case["packed_len"] and scales.numel() == case["scales_len"], case["name"]
+        assert sha(packed.cpu().numpy()) == case["sha_packed"], case["name"]
+        assert sha(f16_bits(scales).view(np.int16)) == case["sha_scales"], case["name"]
+        dec = P.TernaryE8LatticePacker.unpack(packed, scales, shape, dtype=torch.float32)
+        assert sha(dec.cpu().numpy()) == case["sha_decoded"], case["name"]
+
+
+def test_encode_special_inputs(P, golden):
+    meta, arrays = golden
+    for sp in meta["special"]:
+        key = "special/" + sp["name"]
+        wt = torch.from_numpy(arrays[key + "/input"]).to(DEV)
+        packed, scales, shape = P.TernaryE8LatticePacker.pack(wt, group_size=sp["group"])
+        assert np.array_equal(packed.cpu().numpy(), arrays[key + "/packed"]), sp["name"]
+        assert np.array_equal(f16_bits(scales), arrays[key + "/scales"]), sp["name"]
+        dec = P.TernaryE8LatticePacker.unpack(packed, scales, shape)
+        assert np.array_equal(dec.cpu().numpy().view(np.uint32), arrays[key + "/decoded"].view(np.uint32)), sp["name"]
+
+
+def test_decode_every_code(P, golden):
+    _, arrays = golden
+    packed = torch.from_numpy(arrays["all_codes/packed"]).to(DEV)
+    scales = torch.ones(1641, dtype=torch.float16, device=DEV)
+    for dt in (torch.float32, torch.float16, torch.bfloat16):
+        dec = P.TernaryE8LatticePacker.unpack(packed, scales, (3282, 8), dtype=dt)
+        assert np.array_equal(dec.float().cpu().numpy().astype(np.int8), arrays["all_codes/decoded"])
+
+
+def test_decode_dtypes_follow_reference_rule(P, oracle):
+    w = oracle.gen_normal(31, 64 * 512, 0.02).reshape(64, 512)
+    packed_np, scales_np, _ = oracle.encode(w, 32)
+    packed = torch.from_numpy(packed_np).to(DEV)
+    scales = torch.from_numpy(scales_np.view(np.int16)).view(torch.float16).to(DEV)
+    ref32 = oracle.decode(packed_np, scales_np, (64, 512))
+    d32 = P.ops.decode(packed, scales, (64, 512), torch.float32).cpu().numpy()
+    assert np.array_equal(d32.view(np.uint32), ref32.view(np.uint32))
+    d16 = P.ops.decode(packed, scales, (64, 512), torch.float16).float().cpu().numpy()
+    assert np.array_equal(d16, ref32)                                  # coord * fp16 scale is exact in fp16
+    # bf16: coordinate times the bf16-rounded scale (the reference casts the scale first)
+    coords = oracle.decode_coords(packed_np).reshape(-1, 32).astype(np.float32)
+    sbf = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(scales_np.astype(np.float32)))
+    refbf = (coords * sbf[:, None]).reshape(64, 512)
+    dbf = P.ops.decode(packed, scales, (64, 512), torch.bfloat16).float().cpu().numpy()
+    assert np.array_equal(dbf, refbf)
+
+
+def test_rowwise_pack_equals_whole_matrix(P, oracle):
+    w = to_dev(oracle.gen_normal(41, 37 * 256, 0.02).reshape(37, 256), "f32")
+    p, s, _ = P.TernaryE8LatticePacker.pack(w, 32)
+    for rb in (1, 5, 32, 64):
+        p2, s2 = P.pack_weight_rowwise(w, bitrate=1.5, group_size=32, row_block=rb)
+        assert torch.equal(p, p2) and torch.equal(s, s2)
+    with pytest.raises(ValueError):
+        P.pack_weight_rowwise(w[:, :48].contiguous(), group_size=32)
+    with pytest.raises(ValueError):
+        P.pack_weight_rowwise(w, group_size=16)
+
+
+def _linear_case(P, oracle, n, k, m, xdt, seed, bias=False, force=None, sigma=0.02):
+    w = oracle.gen_normal(seed, n * k, sigma).reshape(n, k)
+    packed_np, scales_np, _ = oracle.encode(w, 32)
+    x32 = oracle.gen_normal(seed + 100, m * k, 1.0).reshape(m, k)
+    if xdt == torch.bfloat16:
+        x32 = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(x32)).reshape(m, k)
+    elif xdt == torch.float16:
+        x32 = x32.astype(np.float16).astype(np.float32)
+    b32 = None
+    if bias:
+        b32 = oracle.gen_normal(seed + 200, n, 0.5)
+        b32 = (oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(b32)) if xdt == torch.bfloat16
+               else b32.astype(np.float16).astype(np.float32) if xdt == torch.float16 else b32)
+    y_ref = oracle.linear_fp32(x32, packed_np, scales_np, n, k, b32)
+    packed = torch.from_numpy(packed_np).to(DEV)
+    scales = torch.from_numpy(scales_np.view(np.int16)).view(torch.float16).to(DEV)
+    x = torch.from_numpy(x32).to(xdt).to(DEV)
+    b = torch.from_numpy(b32).to(xdt).to(DEV) if bias else None
+    y = P.ops.linear(x, packed, scales, b, n, k, 32, force=force)
+    torch.cuda.synchronize()
+    assert y.dtype == xdt and tuple(y.shape) == (m, n)
+    d = y.float().cpu().numpy().astype(np.float64) - y_ref
+    max_abs, rel_l2 = float(np.abs(d).max()), float(np.linalg.norm(d) / max(np.linalg.norm(y_ref), 1e-30))
+    bound_abs, bound_rel = oracle.gemm_tolerance(x32, k)
+    assert max_abs <= bound_abs, (n, k, m, max_abs, bound_abs)
+    assert rel_l2 <= bound_rel, (n, k, m, rel_l2)
+    return max_abs, rel_l2
+
+
+@pytest.mark.parametrize("n,k", [(16, 256), (100, 512), (64, 4096), (130, 14336), (48, 8192), (33, 3584)])
+@pytest.mark.parametrize("m", [1, 4, 8, 16])
+def test_gemv_bf16(P, oracle, n, k, m):
+    _linear_case(P, oracle, n, k, m, torch.bfloat16, seed=n + k + m, bias=(m % 2 == 0))
+
+
+@pytest.mark.parametrize("m", [1, 5, 16])
+def test_gemv_fp16(P, oracle, m):
+    _linear_case(P, oracle, 72, 1024, m, torch.float16, seed=77 + m, bias=True)
+
+
+def test_gemv_fp32_out_is_tight(P, oracle):
+    # with fp32 output the only error left is fp32 accumulation order
+    n, k, m = 96, 4096, 4
+    w = oracle.gen_normal(5, n * k, 0.02).reshape(n, k)
+    packed_np, scales_np, _ = oracle.encode(w, 32)
+    x32 = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(oracle.gen_normal(6, m * k, 1.0))).reshape(m, k)
+    y_ref = oracle.linear_fp32(x32, packed_np, scales_np, n, k)
+    packed = torch.from_numpy(packed_np).to(DEV)
+    scales = torch.from_numpy(scales_np.view(np.int16)).view(torch.float16).to(DEV)
+    y = P.ops.linear(torch.from_numpy(x32).bfloat16().to(DEV), packed, scales, None, n, k, 32, out_dtype=torch.float32)
+    rel = np.linalg.norm(y.cpu().numpy() - y_ref) / np.linalg.norm(y_ref)
+    assert rel < 5e-6, rel
+
+
+@pytest.mark.parametrize("n,k,m,xdt", [(7, 13, 3, torch.float32), (5, 19, 2, torch.float32), (4, 48, 2, torch.float32),
+                                       (24, 128, 5, torch.bfloat16), (40, 96, 20, torch.float32)])
+def test_generic_path_odd_shapes(P, oracle, n, k, m, xdt):
+    # flat packing whose groups cross row boundaries, fp32 activations, K not a multiple of 256
+    g = 16 if k % 32 else 32
+    w = oracle.gen_normal(n * k, n * k, 0.5).reshape(n, k)
+    packed_np, scales_np, _ = oracle.encode(w, g)
+    x32 = oracle.gen_normal(3, m * k, 1.0).reshape(m, k)
+    if xdt == torch.bfloat16:
+        x32 = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(x32)).reshape(m, k)
+    wd = oracle.decode(packed_np, scales_np, (n, k)).astype(np.float64)
+    y_ref = x32.astype(np.float64) @ wd.T
+    packed = torch.from_numpy(packed_np).to(DEV)
+    scales = torch.from_numpy(scales_np.view(np.int16)).view(torch.float16).to(DEV)
+    y = P.ops.linear(torch.from_numpy(x32).to(xdt).to(DEV), packed, scales, None, n, k, g)
+    tol = 2e-3 if xdt == torch.bfloat16 else 1e-5
+    assert np.linalg.norm(y.float().cpu().numpy() - y_ref) <= tol * np.linalg.norm(y_ref) + 1e-6
+
+
+@pytest.mark.parametrize("n,k,m", [(128, 256, 256), (256, 1024, 64), (200, 512, 300), (1000, 4096, 513)])
+def test_gemm_tcgen05_bf16(P, oracle, n, k, m):
+    _linear_case(P, oracle, n, k, m, torch.bfloat16, seed=n + k + m, bias=(m % 2 == 0), force="gemm")
+    P.ops.gemm_status(torch.device(DEV))
+
+
+def test_gemm_tcgen05_fp16(P, oracle):
+    _linear_case(P, oracle, 384, 768, 100, torch.float16, seed=9, bias=True, force="gemm")
+    P.ops.gemm_status(torch.device(DEV))
+
+
+def test_gemm_matches_gemv_small_batch(P, oracle):
+    # the two independent kernels agree on the same inputs (M = 16 is legal for both)
+    n, k, m = 256, 4096, 16
+    w = oracle.gen_normal(1, n * k, 0.02).reshape(n, k)
+    packed_np, scales_np, _ = oracle.encode(w, 32)
+    packed = torch.from_numpy(packed_np).to(DEV)
+    scales = torch.from_numpy(scales_np.view(np.int16)).view(torch.float16).to(DEV)
+    x = P.ops.generate(m * k, 2, 1.0, torch.bfloat16, torch.device(DEV)).view(m, k)
+    y1 = P.ops.linear(x, packed, scales, None, n, k, 32, out_dtype=torch.float32, force="gemv")
+    y2 = P.ops.linear(x, packed, scales, None, n, k, 32, out_dtype=torch.float32, force="gemm")
+    P.ops.gemm_status(torch.device(DEV))
+    assert float((y1 - y2).norm() / y1.norm()) < 1e-5
+
+
+def test_grouped_gemv_matches_single(P, oracle):
+    dev = torch.device(DEV)
+    shapes = [(64, 4096), (32, 4096), (48, 14336), (80, 256)]
+    m = 4
+    entries, singles = [], []
+    for i, (n, k) in enumerate(shapes):
+        w = P.ops.generate(n * k, 50 + i, 0.02, torch.float16, dev).view(n, k)
+        pk, sc = P.ops.encode(w, 32)
+        x = P.ops.generate(m * k, 60 + i, 1.0, torch.bfloat16, dev).view(m, k)
+        y = torch.zeros((m, n), dtype=torch.bfloat16, device=dev)
+        entries.append((x, pk, sc, None, y))
+        singles.append(P.ops.linear(x, pk, sc, None, n, k, 32))
+    grp = P.ops.GroupedGemv(entries, shapes)
+    grp()
+    torch.cuda.synchronize()
+    for (x, pk, sc, b, y), ref in zip(entries, singles):
+        assert torch.equal(y, ref)
+
+
+def test_module_forward_backward_and_state(P, oracle):
+    dev = torch.device(DEV)
+    lin = torch.nn.Linear(512, 96, bias=True).to(dev)
+    layer = P.E8LatticeLinear.from_linear(lin, rank=4, bitrate=1.5, group_size=32)
+    assert layer.packed_weight.numel() == 96 * 512 * 3 // 16 and layer.block_scales.numel() == 96 * 512 // 32
+    assert layer.packed_weight.dtype == torch.uint8 and layer.block_scales.dtype == torch.float16
+    x = torch.randn(3, 5, 512, device=dev, requires_grad=True)
+    y = layer(x)
+    assert tuple(y.shape) == (3, 5, 96)
+    w = layer.unpack_weights(torch.float32)
+    y_ref = torch.nn.functional.linear(x.detach(), w, layer.bias)
+    assert float((y.detach() - y_ref).abs().max()) < 1e-3
+    y.sum().backward()
+    assert x.grad is not None and tuple(x.grad.shape) == (3, 5, 512)
+    gx_ref = torch.ones(15, 96, device=dev) @ w
+    assert float((x.grad.reshape(15, 512) - gx_ref).abs().max()) < 1e-3
+    assert layer.lora_B.grad is not None
+    sd = layer.state_dict()
+    assert set(sd) == {"packed_weight", "block_scales", "bias", "lora_A", "lora_B"}
+    # group_size below 16 is coerced to 16, other bit-rates are refused
+    small = P.E8LatticeLinear.from_linear(torch.nn.Linear(64, 8).to(dev), bitrate=1.5, group_size=8)
+    assert small.group_size == 16
+    with pytest.raises(NotImplementedError):
+        P.E8LatticeLinear(64, 8, bitrate=2.0)
+
+
+def test_seam_signature_and_errors(P):
+    dev = torch.device(DEV)
+    x = torch.zeros(2, 256, dtype=torch.bfloat16, device=dev)
+    pk = torch.zeros(16 * 256 * 3 // 16, dtype=torch.uint8, device=dev)
+    sc = torch.ones(16 * 256 // 32, dtype=torch.float16, device=dev)
+    y = P.dispatch_tilelang_e8_gemm(x, pk, sc, None, 16, 256, 32, 1.5, None)
+    assert y is not None and tuple(y.shape) == (2, 16)
+    assert P.dispatch_tilelang_e8_gemm(x, pk, sc, None, 16, 256, 32, 2.0, None) is None
+    assert P.dispatch_tilelang_e8_gemm(x.cpu(), pk.cpu(), sc.cpu(), None, 16, 256, 32, 1.5, None) is None
+    with pytest.raises(RuntimeError):
+        P.ops.encode(torch.zeros(4, 32))            # CPU tensor: no fallback
+    st = P._cabi.lib().ojx_e8t_encode(None, 0, 4, 32, 32, None, None, None)
+    assert st == -1 and P._cabi.status_name(st) == "OJX_ERR_NULL"
+
+
+def test_full_size_properties_llama_q_proj(P, oracle, coracle):
+    """BASELINE-size checks that do not need a slow CPU pass over everything: the encoder's output over a
+    full 4096x4096 matrix hashes equal to the C oracle's, row-block packing equals whole packing, and the
+    decode GEMV and the tensor-core GEMM agree with a dense fp32 product of the decoded matrix."""
+    dev = torch.device(DEV)
+    n = k = 4096
+    w = P.ops.generate(n * k, 11, 0.02, torch.float16, dev).view(n, k)
+    pk, sc = P.ops.encode(w, 32)
+    w_host = oracle.gen_normal(11, n * k, 0.02).astype(np.float16).astype(np.float32)
+    cp, cs = coracle.encode(w_host, 32, threads=8)
+    assert sha(pk.cpu().numpy()) == sha(cp)
+    assert sha(f16_bits(sc)) == sha(cs.view(np.uint16))
+    p2, s2 = P.pack_weight_rowwise(w, row_block=512)
+    assert torch.equal(pk, p2) and torch.equal(sc, s2)
+    wd = P.ops.decode(pk, sc, (n, k), torch.float32)
+    for m, force in ((1, "gemv"), (16, "gemv"), (2048, "gemm")):
+        x = P.ops.generate(m * k, 12 + m, 1.0, torch.bfloat16, dev).view(m, k)
+        y = P.ops.linear(x, pk, sc, None, n, k, 32, force=force)
+        y_ref = x.float() @ wd.t()
+        rel = float((y.float() - y_ref).norm() / y_ref.norm())
+        max_abs = float((y.float() - y_ref).abs().max())
+        assert rel <= 2e-3 and max_abs <= 1e-2 * float(x.float().abs().max()) * math.sqrt(k), (m, rel, max_abs)
+    P.ops.gemm_status(dev)
