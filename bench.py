@@ -1,0 +1,393 @@
+#!/usr/bin/env python
+"""Benchmark of the ternary-E8 decode GEMV sweep (and, as extra lines of evidence, the prefill GEMM
+and the encoder) on B200.
+
+    python bench.py --gpus 1 --steps 20 --warmup 3            # this framework, one GPU
+    torchrun ... bench.py --gpus N ...                        # output-column shards + NCCL all-gather
+    python bench.py --impl reference                          # the reference's CPU kernel on host cores
+
+Workload ("step"): one pass over the decode sweep at Llama-3-8B linear shapes
+(K->N: 4096->4096, 4096->1024, 4096->14336, 14336->4096), batches 1, 4 and 16, over a rotation of
+distinct seeded matrices per shape (the whole sweep is ~2.1 GB of packed weights, far larger than
+L2, and a matrix is only revisited after the rest of the sweep has streamed through).  Every
+(shape, batch) pair is ONE grouped launch over the rotation.  The metric is packed bytes streamed
+per second.  Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)]      # (K, N)
+BATCHES = [1, 4, 16]
+METRIC = "E8 fused dequant-GEMM: decode GB/s on packed bytes @8B shapes"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return float(d["hbm_gbs"]), float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+        except Exception:
+            pass
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for p in self.samples:
+            try:
+                sm.append(float(p[0])); mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU baseline (the reference's native fused kernel compiled in place, else the oracle's C port)
+# --------------------------------------------------------------------------------------------------
+
+def cpu_baseline_run(repeats: int = 1, batches=(1, 4, 16)):
+    """One bounded sample of the sweep on host cores: ONE matrix per shape at every batch, random valid
+    codes (timing does not depend on the values).  Threads follow the reference's own wrapper, which
+    parallelises over the rows of x only."""
+    import numpy as np
+    cores = os.cpu_count() or 1
+    ref_so = os.path.join(ROOT, "oracle", "_ref", "libojx_ref.so")
+    port_so = os.path.join(ROOT, "oracle", "libe8t_oracle.so")
+    kind = None
+    if os.path.exists(ref_so):
+        lib = ctypes.CDLL(ref_so)
+        lib.ojx_ref_ternary_forward.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int64] * 4 + [ctypes.c_int]
+        kind = "reference"
+    else:
+        if not os.path.exists(port_so):
+            subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "all"], stdout=subprocess.DEVNULL)
+        lib = ctypes.CDLL(port_so)
+        lib.e8t_oracle_linear_mt.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int64] * 3 + [ctypes.c_int, ctypes.c_int]
+        kind = "port"
+    rng = np.random.default_rng(0)
+    total_bytes, total_time, used_threads = 0, 0.0, 1
+    for (k, n) in SHAPES:
+        codes = rng.integers(0, 3281, size=n * k // 8, dtype=np.int64).reshape(-1, 2)
+        packed = np.stack([codes[:, 0] & 0xFF, ((codes[:, 0] >> 8) & 0xF) | ((codes[:, 1] & 0xF) << 4), (codes[:, 1] >> 4) & 0xFF],
+                          axis=1).astype(np.uint8).reshape(-1)
+        for b in batches:
+            x = rng.standard_normal((b, k)).astype(np.float32)
+            y = np.zeros((b, n), dtype=np.float32)
+            threads = max(1, min(b, cores))
+            used_threads = max(used_threads, threads)
+            if kind == "reference":
+                scales = np.full(n * k // 32, 0.02, dtype=np.float32)
+                fn = lambda: lib.ojx_ref_ternary_forward(x.ctypes.data, packed.ctypes.data, scales.ctypes.data, None,
+                                                         y.ctypes.data, b, k, n, 32, threads)
+            else:
+                scales = np.full(n * k // 32, 0.02, dtype=np.float16).view(np.uint16)
+                fn = lambda: lib.e8t_oracle_linear_mt(x.ctypes.data, packed.ctypes.data, scales.ctypes.data, None,
+                                                      y.ctypes.data, b, k, n, 32, threads)
+            for _ in range(repeats):
+                t0 = time.perf_counter()
+                fn()
+                total_time += time.perf_counter() - t0
+                total_bytes += n * k // 4
+    return {"value": total_bytes / total_time / 1e9, "unit": "GB/s", "cores": used_threads, "kind": kind,
+            "sample": f"one matrix per shape x batches {list(batches)}, {repeats} pass(es), fp32 activations, "
+                      f"threads=min(batch, {cores} cores) as in the reference's wrapper",
+            "seconds": total_time}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    # bounded: every step is one pass of the sample; keep the whole run within a few minutes
+    times, total = [], None
+    for i in range(args.warmup + args.steps):
+        r = cpu_baseline_run(1)
+        if i >= args.warmup:
+            times.append(r["seconds"])
+        total = r
+    bytes_per_step = sum(n * k // 4 for k, n in SHAPES) * len(BATCHES)
+    val = bytes_per_step / (sum(times) / len(times)) / 1e9
+    line = {"metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "config": {"workload": "decode GEMV sweep, Llama-3-8B linear shapes, batch 1/4/16 (bounded sample: one matrix per shape)",
+                       "shapes_K_N": SHAPES, "batches": BATCHES},
+            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": total["cores"], "kind": total["kind"], "sample": total["sample"]},
+            "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rotation", type=int, default=64, help="distinct matrices per shape")
+    ap.add_argument("--no-extras", action="store_true", help="skip prefill/encoder/per-shape extras")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    pkg = importlib.import_module("ojasx-open-source-cuda_b200")
+    pkg._cabi.lib()                                        # no library -> loud failure, never a fallback
+    ops = pkg.ops
+    sharding = importlib.import_module("ojasx-open-source-cuda_b200.sharding")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    hbm_peak, tf_peak, tf_sustained, peak_src = measured_peaks()
+
+    # ---- build the sweep: per shape, R matrices (this rank's row shard of each), x and y buffers ----
+    R = args.rotation
+    groups = {}          # (shape index, batch) -> GroupedGemv
+    gathers = {}         # (shape index, batch) -> (local flat y, gathered buffer)
+    xs = {}
+    packed_store = []
+    launches_per_step = 0
+    bytes_per_step = 0
+    h2d_per_step = 0
+    d2h_per_step = 0
+    tmp = torch.empty(max(k * n for k, n in SHAPES), dtype=torch.float16, device=dev)
+    for si, (k, n) in enumerate(SHAPES):
+        n0, n1 = sharding.shard_rows(n, world, rank)
+        nl = n1 - n0
+        mats = []
+        for r in range(R):
+            seed = 1000 * (si + 1) + r
+            w = ops.generate(nl * k, seed, 0.02, torch.float16, dev, start=n0 * k, out=tmp[: nl * k]).view(nl, k)
+            pk, sc = ops.encode(w, 32)
+            mats.append((pk, sc))
+        packed_store.append(mats)
+        for b in BATCHES:
+            x = ops.generate(b * k, 7 + b + si, 1.0, torch.bfloat16, dev).view(b, k)
+            xs[(si, b)] = x
+            y_all = torch.zeros((R, b, nl), dtype=torch.bfloat16, device=dev)
+            entries = [(x, pk, sc, None, y_all[r]) for r, (pk, sc) in enumerate(mats)]
+            groups[(si, b)] = ops.GroupedGemv(entries, [(nl, k)] * R)
+            launches_per_step += 1 + groups[(si, b)].needs_reduce
+            gathered = torch.empty((world, R, b, nl), dtype=torch.bfloat16, device=dev) if world > 1 else None
+            gathers[(si, b)] = (y_all, gathered)
+            bytes_per_step += R * (n * k // 4) // 1            # whole-job packed bytes (all ranks)
+            h2d_per_step += b * k * 2
+            d2h_per_step += R * b * n * 2
+    del tmp
+    torch.cuda.synchronize()
+
+    def step():
+        for b in BATCHES:
+            for si in range(len(SHAPES)):
+                groups[(si, b)]()
+                if world > 1:
+                    y_all, gathered = gathers[(si, b)]
+                    dist.all_gather_into_tensor(gathered.view(world, -1), y_all.view(1, -1).squeeze(0), async_op=False)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public API with host buffers (pinned), copies inside the timed region ----
+    x_host = {key: x.cpu().pin_memory() for key, x in xs.items()}
+    y_host = {key: torch.empty(ya.shape, dtype=ya.dtype).pin_memory() for key, (ya, _) in gathers.items()}
+
+    def e2e_step():
+        for b in BATCHES:
+            for si in range(len(SHAPES)):
+                xs[(si, b)].copy_(x_host[(si, b)], non_blocking=True)
+                groups[(si, b)]()
+                if world > 1:
+                    y_all, gathered = gathers[(si, b)]
+                    dist.all_gather_into_tensor(gathered.view(world, -1), y_all.view(-1))
+                y_host[(si, b)].copy_(gathers[(si, b)][0], non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3 * 0.0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = bytes_per_step / (e2e_ms * 1e-3) / 1e9
+
+    extras = {}
+    if not args.no_extras and world == 1:
+        extras = run_extras(torch, ops, dev, groups, packed_store, hbm_peak, tf_peak)
+
+    if rank == 0:
+        # x and y traffic counted with the packed bytes in the roofline numerator
+        act_bytes = sum(R * (b * k * 2 + b * n * 2) for k, n in SHAPES for b in BATCHES)
+        algo_bytes = bytes_per_step + act_bytes
+        achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "decode GEMV sweep, Llama-3-8B linear shapes (K->N 4096->4096, 4096->1024, 4096->14336, 14336->4096), "
+                                   "batch 1/4/16, bf16 activations, bf16 outputs",
+                       "rotation": R, "l2": "inputs larger than L2: %.2f GB of packed weights per pass, a matrix is revisited only after the whole sweep" % (bytes_per_step / 3 / 1e9),
+                       "parallelism": "output-column shards + NCCL all-gather" if world > 1 else "single GPU",
+                       "launches_per_step": launches_per_step},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "traffic": None, "kernel": "gemv_mma_kernel", "peak_source": peak_src,
+                         "note": "achieved = (packed + activation + output bytes of a pass) / time of a pass; launch gaps included"},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d_per_step, "d2h_bytes_per_step": d2h_per_step,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            cb = cpu_baseline_run(1)
+            cb.pop("seconds", None)
+            line["cpu_baseline"] = cb
+        line.update(extras)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_extras(torch, ops, dev, groups, packed_store, hbm_peak, tf_peak):
+    """Per-(shape, batch) decode numbers, the prefill GEMM and the encoder, each timed with CUDA events."""
+    out = {"decode_detail": [], "prefill": [], "encoder": None}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)       # > L2
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    for (si, b), grp in sorted(groups.items()):
+        k, n = SHAPES[si]
+        ms = timed(grp, 5)
+        gbs = grp.packed_bytes / (ms * 1e-3) / 1e9
+        out["decode_detail"].append({"K": k, "N": n, "batch": b, "ms": ms, "packed_GBps": gbs, "frac_hbm": gbs / hbm_peak})
+
+    m = 2048
+    for si, (k, n) in enumerate(SHAPES):
+        pk, sc = packed_store[si][0]
+        x = ops.generate(m * k, 99 + si, 1.0, torch.bfloat16, dev).view(m, k)
+        ms = timed(lambda: ops.linear(x, pk, sc, None, n, k, 32, force="gemm"), 5)
+        ops.gemm_status(dev)
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        out["prefill"].append({"K": k, "N": n, "M": m, "ms": ms, "TFLOPs": tf, "frac_bf16_peak": tf / tf_peak})
+
+    k, n = 8192, 28672
+    w = ops.generate(n * k, 5, 0.02, torch.float16, dev).view(n, k)
+    pk = torch.empty(n * k * 3 // 16, dtype=torch.uint8, device=dev)
+    sc = torch.empty(n * k // 32, dtype=torch.float16, device=dev)
+    ms = timed(lambda: ops.encode(w, 32, out=(pk, sc)), 3)
+    gbs = n * k * 2.25 / (ms * 1e-3) / 1e9
+    out["encoder"] = {"rows": n, "cols": k, "dtype": "f16", "ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak,
+                      "Gweights_per_s": n * k / (ms * 1e-3) / 1e9}
+    return out
+
+
+if __name__ == "__main__":
+    main()

@@ -119,8 +119,11 @@ int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count
 /*
  * Prefill-shape linear (large M) on the tcgen05 tensor cores.  Same contract as ojx_e8t_gemv;
  * replaces the reference's TileLang builder (ojasx2/tilelang_kernels.py:277-363) and the
- * unpack + F.linear path (lattice.py:613-624).  `workspace` holds TMA descriptors and a device
- * status word; query its size with ojx_e8t_gemm_workspace_bytes.
+ * unpack + F.linear path (lattice.py:613-624).  Requires K % 256 == 0, group 32, bf16 or fp16 x.
+ * `workspace` (256-byte aligned, size from ojx_e8t_gemm_workspace_bytes) holds a status block and,
+ * for bf16 activations, their fp16 copy x * 2^-e (e = 0 unless max|x| >= 32768; the result is scaled
+ * back by 2^e): the tensor cores need both operands in one 16-bit format and the weights are only
+ * exact in fp16.
  * ojx_e8t_gemm_status reads back (synchronising the stream) whether any bounded wait inside the
  * last gemm on that workspace expired.
  */

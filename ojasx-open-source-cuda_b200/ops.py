@@ -180,7 +180,7 @@ def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: 
     with torch.cuda.device(dev):
         if use_gemm:
             need = lib.ojx_e8t_gemm_workspace_bytes(m, n, k)
-            ws = scratch(dev, need, "gemm")
+            ws = _gemm_scratch(dev, need)
             st = lib.ojx_e8t_gemm(x2d.data_ptr(), _dtype_code(x2d.dtype), m, pk.data_ptr(), sc.data_ptr(),
                                   b.data_ptr() if b is not None else None, n, k, g, y.data_ptr(), _dtype_code(ydt),
                                   ws.data_ptr(), ws.numel(), _stream_ptr(dev))
@@ -196,9 +196,16 @@ def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: 
     return y
 
 
+def _gemm_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """256-byte aligned scratch for the prefill kernel (status block + fp16 copy of bf16 activations)."""
+    buf = scratch(device, nbytes + 256, "gemm")
+    off = (-buf.data_ptr()) % 256
+    return buf[off: off + max(nbytes, 256)]
+
+
 def gemm_status(device: torch.device) -> None:
     """Raise if a bounded wait inside the last prefill GEMM on this device/stream expired."""
-    ws = scratch(device, 16, "gemm")
+    ws = _gemm_scratch(device, 256)
     with torch.cuda.device(device):
         st = _cabi.lib().ojx_e8t_gemm_status(ws.data_ptr(), _stream_ptr(device))
     _cabi.check(st, "ojx_e8t_gemm (device status)")

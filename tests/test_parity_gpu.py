@@ -202,6 +202,21 @@ def test_gemm_tcgen05_fp16(P, oracle):
     P.ops.gemm_status(torch.device(DEV))
 
 
+def test_gemm_large_magnitude_activations_are_rescaled(P, oracle):
+    # bf16 activations far outside the fp16 range go through the power-of-two rescaling pre-pass
+    n, k, m = 128, 512, 64
+    w = oracle.gen_normal(21, n * k, 0.02).reshape(n, k)
+    packed_np, scales_np, _ = oracle.encode(w, 32)
+    x32 = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(oracle.gen_normal(22, m * k, 1.0) * np.float32(2.0 ** 30))).reshape(m, k)
+    y_ref = oracle.linear_fp32(x32, packed_np, scales_np, n, k)
+    packed = torch.from_numpy(packed_np).to(DEV)
+    scales = torch.from_numpy(scales_np.view(np.int16)).view(torch.float16).to(DEV)
+    y = P.ops.linear(torch.from_numpy(x32).bfloat16().to(DEV), packed, scales, None, n, k, 32, out_dtype=torch.float32, force="gemm")
+    P.ops.gemm_status(torch.device(DEV))
+    assert np.isfinite(y.cpu().numpy()).all()
+    assert np.linalg.norm(y.cpu().numpy() - y_ref) / np.linalg.norm(y_ref) < 1e-5
+
+
 def test_gemm_matches_gemv_small_batch(P, oracle):
     # the two independent kernels agree on the same inputs (M = 16 is legal for both)
     n, k, m = 256, 4096, 16
