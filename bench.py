@@ -184,9 +184,18 @@ def main():
     ap.add_argument("--rotation", type=int, default=64, help="distinct matrices per shape")
     ap.add_argument("--no-extras", action="store_true", help="skip prefill/encoder/per-shape extras")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "encode", "decode"],
+                    help="run a few launches of ONE kernel on a small case and exit (used for ncu captures)")
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--N", type=int, default=4096)
+    ap.add_argument("--M", type=int, default=1)
+    ap.add_argument("--launches", type=int, default=3)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.case is not None:
+        run_case(args)
         return
 
     import torch
@@ -344,6 +353,57 @@ def main():
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_case(args):
+    """A few launches of one kernel on one shape, timed with CUDA events; prints one JSON line."""
+    import torch
+    pkg = importlib.import_module("ojasx-open-source-cuda_b200")
+    ops = pkg.ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    k, n, m = args.K, args.N, args.M
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w = ops.generate(n * k, 3, 0.02, torch.float16, dev).view(n, k)
+    info = {"case": args.case, "K": k, "N": n, "M": m, "launches": args.launches}
+    if args.case == "gemv":
+        R = args.rotation
+        mats = []
+        for r in range(R):
+            ops.generate(n * k, 100 + r, 0.02, torch.float16, dev, out=w.view(-1))
+            mats.append(ops.encode(w, 32))
+        x = ops.generate(m * k, 7, 1.0, torch.bfloat16, dev).view(m, k)
+        y = torch.zeros((R, m, n), dtype=torch.bfloat16, device=dev)
+        grp = ops.GroupedGemv([(x, pk, sc, None, y[r]) for r, (pk, sc) in enumerate(mats)], [(n, k)] * R)
+        fn = grp
+        info["bytes_per_launch"] = grp.packed_bytes + R * (m * k * 2 + m * n * 2)
+    elif args.case == "gemm":
+        pk, sc = ops.encode(w, 32)
+        x = ops.generate(m * k, 7, 1.0, torch.bfloat16, dev).view(m, k)
+        fn = lambda: ops.linear(x, pk, sc, None, n, k, 32, force="gemm")
+        info["flops_per_launch"] = 2.0 * m * n * k
+    elif args.case == "encode":
+        pk = torch.empty(n * k * 3 // 16, dtype=torch.uint8, device=dev)
+        sc = torch.empty(n * k // 32, dtype=torch.float16, device=dev)
+        fn = lambda: ops.encode(w, 32, out=(pk, sc))
+        info["bytes_per_launch"] = n * k * 2.25
+    else:
+        pk, sc = ops.encode(w, 32)
+        out = torch.empty((n, k), dtype=torch.float16, device=dev)
+        fn = lambda: ops.decode(pk, sc, (n, k), torch.float16, out=out)
+        info["bytes_per_launch"] = n * k * 2.25
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(args.launches):
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    info["ms"] = times
+    if "bytes_per_launch" in info:
+        info["GBps_last"] = info["bytes_per_launch"] / (times[-1] * 1e-3) / 1e9
+    else:
+        info["TFLOPs_last"] = info["flops_per_launch"] / (times[-1] * 1e-3) / 1e12
+    print(json.dumps(info))
 
 
 def run_extras(torch, ops, dev, groups, packed_store, hbm_peak, tf_peak):

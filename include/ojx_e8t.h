@@ -58,6 +58,15 @@ int32_t ojx_e8t_version(void);
 const char* ojx_e8t_status_string(int32_t status);
 
 /*
+ * Diagnostics.  ojx_e8t_last_cuda_error: text of the last CUDA runtime error that made an entry point
+ * return OJX_ERR_LAUNCH on the calling thread.  ojx_e8t_device_status: synchronises the device and
+ * returns OJX_ERR_TIMEOUT if a bounded wait inside a decode-shape kernel ever gave up, else OJX_OK.
+ * No counterpart in the reference.
+ */
+const char* ojx_e8t_last_cuda_error(void);
+int32_t ojx_e8t_device_status(void);
+
+/*
  * Encoder.  Replaces TernaryE8LatticePacker.pack (ojasx2/math/lattice.py:338-384); bit-exact.
  *   w         [rows, cols] row-major, dtype w_dtype (fp32 / fp16 / bf16), any alignment of rows
  *   group     scale group size; values that are not a positive multiple of 16 are replaced by 16,

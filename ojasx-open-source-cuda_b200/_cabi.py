@@ -25,7 +25,7 @@ EXPORTED_SYMBOLS = (
     "ojx_e8t_version", "ojx_e8t_status_string", "ojx_e8t_encode", "ojx_e8t_decode",
     "ojx_e8t_gemv_workspace_bytes", "ojx_e8t_gemv", "ojx_e8t_gemv_tiles", "ojx_e8t_gemv_kchunks",
     "ojx_e8t_gemv_grouped", "ojx_e8t_gemm_workspace_bytes", "ojx_e8t_gemm", "ojx_e8t_gemm_status",
-    "ojx_e8t_generate",
+    "ojx_e8t_generate", "ojx_e8t_last_cuda_error", "ojx_e8t_device_status",
 )
 
 NVCC_FLAGS = [
@@ -108,6 +108,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ojx_e8t_gemm.argtypes = [vp, i32, i64, vp, vp, vp, i64, i64, i32, vp, i32, vp, sz, vp]
     lib.ojx_e8t_gemm_status.restype = i32
     lib.ojx_e8t_gemm_status.argtypes = [vp, vp]
+    lib.ojx_e8t_last_cuda_error.restype = ctypes.c_char_p
+    lib.ojx_e8t_last_cuda_error.argtypes = []
+    lib.ojx_e8t_device_status.restype = i32
+    lib.ojx_e8t_device_status.argtypes = []
     lib.ojx_e8t_generate.restype = i32
     lib.ojx_e8t_generate.argtypes = [vp, i32, i64, u64, i64, ctypes.c_float, vp]
 
@@ -134,4 +138,7 @@ def status_name(code: int) -> str:
 
 def check(code: int, what: str) -> None:
     if code != 0:
-        raise OjxError(f"{what} failed: {status_name(code)} ({code})")
+        detail = ""
+        if code == -6:
+            detail = " - CUDA: " + lib().ojx_e8t_last_cuda_error().decode()
+        raise OjxError(f"{what} failed: {status_name(code)} ({code}){detail}")

@@ -63,13 +63,62 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ---- mbarrier helpers (shared by the GEMV ring and the tcgen05 pipeline) -------------------------
+constexpr uint32_t kSpinLimit = 1u << 24;                     // bounded waits: ~seconds, then give up
+__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t addr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is reached or
+// another thread already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(addr, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag != 0) return false;
+    }
+    atomicCAS(const_cast<int*>(abort_flag), 0, code);
+    return false;
+}
+
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.  Both addresses and
+// the size must be multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// Device-side status word: a bounded wait that gave up records its code here (0 = none).
+static __device__ int g_device_status = 0;
+
 // Validates the device once per process per device: kernels are built for sm_100a only.
 int check_arch();
 
 #define OJX_RETURN_IF(cond, code) do { if (cond) return (code); } while (0)
 
+// Last CUDA runtime error seen by this library on the calling thread (for diagnostics only).
+inline cudaError_t& last_cuda_error() {
+    static thread_local cudaError_t e = cudaSuccess;
+    return e;
+}
 inline int32_t launch_status() {
-    return cudaGetLastError() == cudaSuccess ? OJX_OK : OJX_ERR_LAUNCH;
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return OJX_OK;
+    last_cuda_error() = e;
+    return OJX_ERR_LAUNCH;
 }
 
 // Entry points implemented in the individual .cu files (called by api.cu).

@@ -45,7 +45,6 @@ constexpr uint32_t kXStageBytes = kGemmBN * kGemmBK * 2;      // 32768
 constexpr uint32_t kAStageBytes = kGemmBM * kGemmBK * 2;      // 16384
 constexpr uint32_t kGemmLutBytes = 13184;                     // 3281 * 4 rounded up to 64
 constexpr uint32_t kGemmSmemBytes = kGemmStages * (kXStageBytes + kAStageBytes) + kGemmLutBytes + 256 + 1024;
-constexpr uint32_t kSpinLimit = 1u << 24;                     // bounded waits: ~seconds, then give up
 
 struct GemmParams {
     const uint8_t* packed;
@@ -110,35 +109,7 @@ __global__ void __launch_bounds__(256) convert_bf16_to_f16_kernel(const __nv_bfl
     }
 }
 
-// ---- PTX wrappers -------------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t addr) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t addr, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(addr), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is reached or
-// another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity, volatile int* abort_flag, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_try_wait(addr, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag != 0) return false;
-    }
-    atomicCAS(const_cast<int*>(abort_flag), 0, code);
-    return false;
-}
+// ---- PTX wrappers (mbarrier helpers live in common.cuh) ------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

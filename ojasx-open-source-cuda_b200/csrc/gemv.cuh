@@ -7,14 +7,16 @@
 // Fast path (K % 256 == 0, bf16/fp16 activations, M <= 16)
 //   * one CTA = 16 warps; warp w owns one 256-wide slice of K and keeps that slice of x in
 //     registers as mma.m16n8k16 B fragments, so activations are read once per CTA;
-//   * a work item is 16 weight rows x one K chunk (= all slices of the CTA); per item a lane
-//     streams 48 B of codes + 16 B of scales per row with 128-bit loads (the next item's loads
-//     are issued before the current item is decoded);
+//   * a work item is 16 weight rows x one K chunk (= all slices of the CTA); a producer warp keeps a
+//     4-deep ring of items (~16 KB each) in flight with 1-D bulk copies (cp.async.bulk + mbarrier),
+//     so ~64 KB per SM is always on its way from HBM; consumer lanes then pick up 48 B of codes +
+//     16 B of scales per row with 128-bit shared-memory loads;
 //   * a 12-bit rank is turned into eight trits by ONE shared-memory lookup; the table is stored
 //     eight times (stride 32 B) so that lanes of different lane%8 never collide on a bank;
 //   * trits become +-2.0 / 0 fp16|bf16 operand registers with byte permutes, the MACs run on the
 //     tensor cores, and the group scale (times 1/2) is applied to the fp32 fragment per group;
-//   * warps' partial sums are combined in a fixed order through shared memory (deterministic).
+//   * warps' partial sums are combined in a fixed order through shared memory (deterministic), two
+//     items late and by a different warp each time, so the loop has no block-wide barrier.
 // K larger than one CTA's 16 slices is split into chunks whose fp32 partials go to caller-owned
 // scratch and are summed, again in a fixed order, by a second small kernel.
 #pragma once
@@ -25,9 +27,7 @@ namespace ojx {
 
 constexpr int kGemvWarps = 16;
 constexpr int kGemvThreads = kGemvWarps * 32;
-constexpr int kLutCopies = 8;
 constexpr int kLutEntries = 4096;                                  // any 12-bit code stays in bounds
-constexpr int kLutBytes = kLutEntries * kLutCopies * 4;            // 131072
 
 __host__ __device__ inline int gemv_active_warps(int K) {
     const int slices = K / 256;
@@ -63,40 +63,6 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     return v;
 }
 
-// One row's share of a work item: 48 B of codes (32 ranks = 8 groups) and 8 fp16 scales.
-struct RowSlice {
-    uint4 c[3];
-    uint4 s;
-};
-
-__device__ __forceinline__ void load_row_slice(RowSlice& r, const uint8_t* codes, const uint16_t* scales) {
-    const uint4* cp = reinterpret_cast<const uint4*>(codes);
-    r.c[0] = __ldg(cp);
-    r.c[1] = __ldg(cp + 1);
-    r.c[2] = __ldg(cp + 2);
-    r.s = __ldg(reinterpret_cast<const uint4*>(scales));
-}
-
-struct ItemCtx {
-    int prob, chunk, tile;
-};
-
-__device__ __forceinline__ ItemCtx locate_item(const ojx_e8t_gemv_problem* probs, int count, int item, int hint) {
-    int p = hint;
-    while (p + 1 < count && probs[p + 1].tile_begin <= item) ++p;
-    const int local = item - probs[p].tile_begin;
-    const int tiles = gemv_row_tiles(probs[p].N);
-    ItemCtx c;
-    c.prob = p;
-    c.chunk = local / tiles;
-    c.tile = local - c.chunk * tiles;
-    return c;
-}
-
-template <typename T> __device__ __forceinline__ void store_out(void* y, int y_dtype, int64_t idx, float v) {
-    (void)y_dtype;
-    static_cast<T*>(y)[idx] = from_f32<T>(v);
-}
 __device__ __forceinline__ void store_any(void* y, int y_dtype, int64_t idx, float v) {
     if (y_dtype == OJX_BF16) static_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
     else if (y_dtype == OJX_F16) static_cast<__half*>(y)[idx] = __float2half_rn(v);
@@ -107,22 +73,108 @@ template <bool kBf16> __device__ __forceinline__ float load_act(const void* p, i
     return __half2float(static_cast<const __half*>(p)[idx]);
 }
 
-template <bool kBf16, int NB>
-__global__ void __launch_bounds__(kGemvThreads, 1)
+__device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// Position of a work item: problem, K chunk, 16-row tile; plus the few per-problem numbers the
+// inner loop needs, refreshed only when the problem changes (no divisions per item).
+struct Cursor {
+    int prob, chunk, tile;
+    int N, K, act, tiles, kchunks;
+};
+
+__device__ __forceinline__ void cursor_load_problem(Cursor& c, const ojx_e8t_gemv_problem* probs) {
+    c.N = probs[c.prob].N;
+    c.K = probs[c.prob].K;
+    c.act = gemv_active_warps(c.K);
+    c.tiles = gemv_row_tiles(c.N);
+    c.kchunks = (c.K / 256) / c.act;
+}
+__device__ __forceinline__ void cursor_seek(Cursor& c, const ojx_e8t_gemv_problem* probs, int count, int item) {
+    int p = 0;
+    while (p + 1 < count && probs[p + 1].tile_begin <= item) ++p;
+    c.prob = p;
+    cursor_load_problem(c, probs);
+    const int local = item - probs[p].tile_begin;
+    c.chunk = local / c.tiles;
+    c.tile = local - c.chunk * c.tiles;
+}
+__device__ __forceinline__ void cursor_next(Cursor& c, const ojx_e8t_gemv_problem* probs, int count) {
+    if (++c.tile == c.tiles) {
+        c.tile = 0;
+        if (++c.chunk == c.kchunks) {
+            c.chunk = 0;
+            if (c.prob + 1 < count) {
+                ++c.prob;
+                cursor_load_problem(c, probs);
+            }
+        }
+    }
+}
+
+// Shared-memory plan of the fast kernel.
+//   lut    COPIES interleaved copies of the rank -> trit-nibble table (entry r, copy c at (r*COPIES + c)*4)
+//   ring   kGemvStages work items; an item holds 16 rows of codes (pitch = bytes + 16, so the 8 rows a
+//          128-bit load touches fall on distinct banks) followed by 16 rows of scales (same rule)
+//   red    kGemvRed buffers of per-warp fragments for the deterministic cross-warp sum
+constexpr int kGemvStages = 4;
+constexpr int kGemvRed = 4;
+constexpr int kGemvRedLag = 2;                              // an item is summed two items after it was computed
+constexpr int kGemvMaxCodePitch = kGemvWarps * 48 + 16;     // 784
+constexpr int kGemvMaxScalePitch = kGemvWarps * 16 + 16;    // 272
+constexpr int kGemvStageBytes = 16 * (kGemvMaxCodePitch + kGemvMaxScalePitch);   // 16896
+constexpr int kGemvBlock = kGemvThreads;
+
+template <int NB, int COPIES> constexpr size_t gemv_smem_bytes() {
+    return (size_t)kLutEntries * COPIES * 4 + (size_t)kGemvStages * kGemvStageBytes +
+           (size_t)kGemvRed * kGemvWarps * 32 * 4 * NB * sizeof(float) + 256;
+}
+
+// All 16 warps are symmetric.  For item n (counted from the CTA's first item):
+//   * warp (n mod 16) issued its bulk copies kGemvStages-1 items earlier, after waiting for the ring stage
+//     to be released by all warps ("empty" barrier);
+//   * every warp waits for the bytes ("full" barrier), pulls its rows' slice into registers, releases
+//     the stage, decodes and multiplies, and parks its fragment in a reduction buffer ("rfull" barrier);
+//   * warp ((n - 2) mod 16) then adds up the sixteen fragments of item n-2 in warp order and writes
+//     the outputs ("rempty" barrier frees the buffer).  No block-wide barrier in the loop.
+template <bool kBf16, int NB, int COPIES>
+__global__ void __launch_bounds__(kGemvBlock, 1)
 gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_constant__ ojx_e8t_gemv_problem single,
                 int count, int total_items, int M, int y_dtype) {
     // A single problem travels by value in the kernel parameters; a list lives in device memory.
     const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
-    extern __shared__ __align__(16) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int kLutB = kLutEntries * COPIES * 4;
+    constexpr int kRedFloats = kGemvWarps * 32 * 4 * NB;
     uint32_t* lut = reinterpret_cast<uint32_t*>(smem);
-    float* red = reinterpret_cast<float*>(smem + kLutBytes);        // [2][warps][32][4*NB]
+    const uint32_t ring = smem_u32(smem) + kLutB;
+    float* red = reinterpret_cast<float*>(smem + kLutB + kGemvStages * kGemvStageBytes);
+    uint8_t* tail = smem + kLutB + kGemvStages * kGemvStageBytes + kGemvRed * kRedFloats * sizeof(float);
+    const uint32_t bar_full = smem_u32(tail), bar_empty = bar_full + 8 * kGemvStages;
+    const uint32_t bar_rfull = bar_empty + 8 * kGemvStages, bar_rempty = bar_rfull + 8 * kGemvRed;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 16 * kGemvStages + 16 * kGemvRed);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
-    for (int i = tid; i < kLutEntries * kLutCopies; i += kGemvThreads) {
-        const int r = i >> 3;
+    for (int i = tid; i < kLutEntries * COPIES; i += kGemvBlock) {
+        const int r = i / COPIES;
         lut[i] = r < kNumPoints ? g_trit_nibbles[r] : 0u;
+    }
+    if (tid == 0) {
+        for (int s = 0; s < kGemvStages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);                 // the issuing lane's expect_tx arrive
+            mbar_init(bar_empty + 8 * s, kGemvWarps);       // every warp has pulled its slice
+        }
+        for (int b = 0; b < kGemvRed; ++b) {
+            mbar_init(bar_rfull + 8 * b, kGemvWarps);       // every warp has parked its fragment
+            mbar_init(bar_rempty + 8 * b, 1);               // the summing warp is done with the buffer
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
@@ -130,80 +182,123 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     const int i0 = (int)min((int64_t)total_items, per * blockIdx.x);
     const int i1 = (int)min((int64_t)total_items, per * (blockIdx.x + 1));
     if (i0 >= i1) return;
+    const int nitems = i1 - i0;
+
+    // Bounded wait; once any wait has given up, later waits return at once and the loop runs on (on stale
+    // data) so that every barrier keeps its arrival count.  The failure is reported in g_device_status.
+    auto wait = [&](uint32_t bar, uint32_t parity, int code) {
+        if (*abort_flag == 0) mbar_wait(bar, parity, abort_flag, code);
+    };
+
+    // ---- issue: bulk copies of item n into ring stage n mod S ----
+    Cursor ic;                                  // cursor of the next item to be issued
+    cursor_seek(ic, probs, count, i0);
+    int issued = 0;
+    auto issue_next = [&]() {
+        const int n = issued, s = n % kGemvStages;
+        if (warp == (n & (kGemvWarps - 1))) {
+            wait(bar_empty + 8 * s, ((uint32_t)(n / kGemvStages) & 1u) ^ 1u, 11);
+            const ojx_e8t_gemv_problem& P = probs[ic.prob];
+            const uint32_t cb = ic.act * 48, sb = ic.act * 16;
+            const int rows = min(16, ic.N - ic.tile * 16);
+            const uint32_t stage = ring + s * kGemvStageBytes;
+            if (lane == 0) mbar_expect_tx(bar_full + 8 * s, (uint32_t)rows * (cb + sb));
+            __syncwarp();
+            const int r = lane & 15;
+            if (r < rows) {
+                const int64_t row = (int64_t)ic.tile * 16 + r;
+                if (lane < 16)
+                    bulk_load(stage + r * (cb + 16), P.packed + row * ((int64_t)ic.K * 3 / 16) + (int64_t)ic.chunk * cb, cb, bar_full + 8 * s);
+                else
+                    bulk_load(stage + 16 * kGemvMaxCodePitch + r * (sb + 16),
+                              reinterpret_cast<const uint8_t*>(P.scales) + row * ((int64_t)ic.K / 16) + (int64_t)ic.chunk * sb, sb, bar_full + 8 * s);
+            }
+        }
+        ++issued;
+        cursor_next(ic, probs, count);
+    };
+    for (int n = 0; n < kGemvStages - 1 && n < nitems; ++n) issue_next();
+
+    // ---- reduction of item n (done by warp n mod 16, kGemvRedLag items late) ----
+    Cursor rc;                                  // cursor of the next item to be summed
+    cursor_seek(rc, probs, count, i0);
+    int reduced = 0;
+    auto reduce_next = [&]() {
+        const int n = reduced, b = n % kGemvRed;
+        if (warp == (n & (kGemvWarps - 1))) {
+            wait(bar_rfull + 8 * b, (uint32_t)(n / kGemvRed) & 1u, 13);
+            const float* rbuf = red + (size_t)b * kRedFloats;
+            const ojx_e8t_gemv_problem& P = probs[rc.prob];
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; ++w) {
+                    const float4 v = *reinterpret_cast<const float4*>(rbuf + ((size_t)(w * 32 + lane) * NB + nb) * 4);
+                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                const float vals[4] = {sum.x * 0.5f, sum.y * 0.5f, sum.z * 0.5f, sum.w * 0.5f};   // operands hold +-2.0
+#pragma unroll
+                for (int reg = 0; reg < 4; ++reg) {
+                    const int row = rc.tile * 16 + g + ((reg >> 1) << 3);
+                    const int col = nb * 8 + (t << 1) + (reg & 1);
+                    if (row < rc.N && col < M) {
+                        float v = vals[reg];
+                        if (P.partial != nullptr) {
+                            P.partial[((int64_t)rc.chunk * M + col) * rc.N + row] = v;
+                        } else {
+                            if (P.bias != nullptr) v += load_act<kBf16>(P.bias, row);
+                            store_any(P.y, y_dtype, (int64_t)col * rc.N + row, v);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_rempty + 8 * b);
+        }
+        ++reduced;
+        cursor_next(rc, probs, count);
+    };
 
     // lane-constant decode parameters
     const uint32_t bt = (t == 0) ? 0u : (t == 1) ? 1u : (t == 2) ? 3u : 4u;     // first byte of this lane's rank
     const uint32_t sel_even = bt | ((bt + 1) << 4);
     const uint32_t sel_odd = (bt + 2) | ((bt + 3) << 4);
-    const uint32_t lsh = (t & 1) ? 1u : 5u;
-    const uint32_t lut_lane = smem_u32(lut) + ((lane & 7) << 2);
-    constexpr uint32_t kConstH = 0x00C04000u;                         // byte 1: +2.0 high byte, byte 2: -2.0
+    constexpr int kEntryShift = COPIES == 8 ? 5 : (COPIES == 4 ? 4 : (COPIES == 2 ? 3 : 2));   // log2(COPIES * 4)
+    const uint32_t lsh = (t & 1) ? (uint32_t)(kEntryShift - 4) : (uint32_t)kEntryShift;
+    constexpr uint32_t kEntryMask = 0xFFFu << kEntryShift;
+    const uint32_t lut_lane = smem_u32(lut) + ((lane & (COPIES - 1)) << 2);
+    constexpr uint32_t kConstH = 0x00C04000u;                     // byte 1: +2.0 high byte, byte 2: -2.0
 
     uint32_t xf[NB][8][4];
     int cur_prob = -1, cur_chunk = -1;
-    int hint = 0;
+    Cursor cc;
+    cursor_seek(cc, probs, count, i0);
+    for (int n = 0; n < nitems; ++n) {
+        const int s = n % kGemvStages, b = n % kGemvRed;
+        if (issued < nitems) issue_next();                       // keeps kGemvStages-1 items in flight
 
-    ItemCtx ctx = locate_item(probs, count, i0, 0);
-    hint = ctx.prob;
-    RowSlice ra, rb;                       // current item
-    ra.c[0] = ra.c[1] = ra.c[2] = ra.s = make_uint4(0, 0, 0, 0);
-    rb = ra;
-    int active = 0;
-    {
-        const ojx_e8t_gemv_problem& P = probs[ctx.prob];
-        active = gemv_active_warps(P.K);
-        if (warp < active) {
-            const int64_t row_bytes = (int64_t)P.K * 3 / 16, row_scales = P.K / 32;
-            const int slice = ctx.chunk * active + warp;
-            const int r0 = min(ctx.tile * 16 + g, P.N - 1), r1 = min(ctx.tile * 16 + g + 8, P.N - 1);
-            load_row_slice(ra, P.packed + r0 * row_bytes + slice * 48, P.scales + r0 * row_scales + slice * 8);
-            load_row_slice(rb, P.packed + r1 * row_bytes + slice * 48, P.scales + r1 * row_scales + slice * 8);
-        }
-    }
-
-    int buf = 0;
-    for (int item = i0; item < i1; ++item) {
-        const ojx_e8t_gemv_problem& P = probs[ctx.prob];
-        const int act = active;
         // (re)load this warp's activations when the problem or the K chunk changes
-        if (ctx.prob != cur_prob || ctx.chunk != cur_chunk) {
-            cur_prob = ctx.prob;
-            cur_chunk = ctx.chunk;
-            if (warp < act) {
-                const int slice = ctx.chunk * act + warp;
+        if (cc.prob != cur_prob || cc.chunk != cur_chunk) {
+            cur_prob = cc.prob;
+            cur_chunk = cc.chunk;
+            if (warp < cc.act) {
+                const uint16_t* xp = static_cast<const uint16_t*>(probs[cc.prob].x);
+                const int slice = cc.chunk * cc.act + warp;
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
                     const int m = nb * 8 + g;
 #pragma unroll
                     for (int grp = 0; grp < 8; ++grp) {
                         uint4 v = make_uint4(0, 0, 0, 0);
-                        if (m < M)
-                            v = __ldg(reinterpret_cast<const uint4*>(
-                                static_cast<const uint16_t*>(P.x) + (int64_t)m * P.K + slice * 256 + grp * 32 + t * 8));
+                        if (m < M) v = __ldg(reinterpret_cast<const uint4*>(xp + (int64_t)m * cc.K + slice * 256 + grp * 32 + t * 8));
                         xf[nb][grp][0] = v.x; xf[nb][grp][1] = v.y; xf[nb][grp][2] = v.z; xf[nb][grp][3] = v.w;
                     }
                 }
             }
         }
 
-        // issue the next item's loads before decoding this one
-        ItemCtx nctx = ctx;
-        RowSlice na = ra, nbq = rb;
-        int nactive = act;
-        const bool has_next = item + 1 < i1;
-        if (has_next) {
-            nctx = locate_item(probs, count, item + 1, hint);
-            hint = nctx.prob;
-            const ojx_e8t_gemv_problem& Q = probs[nctx.prob];
-            nactive = gemv_active_warps(Q.K);
-            if (warp < nactive) {
-                const int64_t row_bytes = (int64_t)Q.K * 3 / 16, row_scales = Q.K / 32;
-                const int slice = nctx.chunk * nactive + warp;
-                const int r0 = min(nctx.tile * 16 + g, Q.N - 1), r1 = min(nctx.tile * 16 + g + 8, Q.N - 1);
-                load_row_slice(na, Q.packed + r0 * row_bytes + slice * 48, Q.scales + r0 * row_scales + slice * 8);
-                load_row_slice(nbq, Q.packed + r1 * row_bytes + slice * 48, Q.scales + r1 * row_scales + slice * 8);
-            }
-        }
+        wait(bar_full + 8 * s, (uint32_t)(n / kGemvStages) & 1u, 12);
 
         float acc[NB][4];
 #pragma unroll
@@ -211,20 +306,28 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
 
-        if (warp < act) {
-            const uint32_t* ca = reinterpret_cast<const uint32_t*>(ra.c);
-            const uint32_t* cb = reinterpret_cast<const uint32_t*>(rb.c);
-            const uint32_t* sa = reinterpret_cast<const uint32_t*>(&ra.s);
-            const uint32_t* sb = reinterpret_cast<const uint32_t*>(&rb.s);
+        if (warp < cc.act) {
+            const uint32_t cb = cc.act * 48, sb = cc.act * 16;
+            const uint32_t stage = ring + s * kGemvStageBytes;
+            const uint32_t ca_addr = stage + g * (cb + 16) + warp * 48, cb_addr = ca_addr + 8 * (cb + 16);
+            const uint32_t sa_addr = stage + 16 * kGemvMaxCodePitch + g * (sb + 16) + warp * 16, sb_addr = sa_addr + 8 * (sb + 16);
+            uint4 qa[3] = {lds_u128(ca_addr), lds_u128(ca_addr + 16), lds_u128(ca_addr + 32)};
+            uint4 qb[3] = {lds_u128(cb_addr), lds_u128(cb_addr + 16), lds_u128(cb_addr + 32)};
+            uint4 qsa = lds_u128(sa_addr), qsb = lds_u128(sb_addr);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);           // the stage may be refilled
+            const uint32_t* ca = reinterpret_cast<const uint32_t*>(qa);
+            const uint32_t* cbw = reinterpret_cast<const uint32_t*>(qb);
+            const __half2* sa = reinterpret_cast<const __half2*>(&qsa);
+            const __half2* sbh = reinterpret_cast<const __half2*>(&qsb);
 #pragma unroll
             for (int grp = 0; grp < 8; ++grp) {
-                constexpr int dummy = 0; (void)dummy;
                 const int w0 = (grp & 1) ? (3 * grp - 1) / 2 : (3 * grp) / 2;
                 const uint32_t sel = (grp & 1) ? sel_odd : sel_even;
                 const uint32_t wa = prmt(ca[w0], ca[w0 + 1], sel);
-                const uint32_t wb = prmt(cb[w0], cb[w0 + 1], sel);
-                const uint32_t na_ = lds_u32(((wa << lsh) & 0x1FFE0u) + lut_lane);
-                const uint32_t nb_ = lds_u32(((wb << lsh) & 0x1FFE0u) + lut_lane);
+                const uint32_t wb = prmt(cbw[w0], cbw[w0 + 1], sel);
+                const uint32_t na_ = lds_u32(((wa << lsh) & kEntryMask) + lut_lane);
+                const uint32_t nb_ = lds_u32(((wb << lsh) & kEntryMask) + lut_lane);
                 const uint32_t ha_lo = prmt(kConstH, 0u, na_), ha_hi = prmt(kConstH, 0u, na_ >> 16);
                 const uint32_t hb_lo = prmt(kConstH, 0u, nb_), hb_hi = prmt(kConstH, 0u, nb_ >> 16);
                 uint32_t a1[4], a2[4];
@@ -232,9 +335,8 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
                 a1[1] = prmt(hb_lo, 0u, 0x1404u); a1[3] = prmt(hb_lo, 0u, 0x3424u);
                 a2[0] = prmt(ha_hi, 0u, 0x1404u); a2[2] = prmt(ha_hi, 0u, 0x3424u);
                 a2[1] = prmt(hb_hi, 0u, 0x1404u); a2[3] = prmt(hb_hi, 0u, 0x3424u);
-                const uint32_t spa = sa[grp >> 1], spb = sb[grp >> 1];
-                const float fa = 0.5f * __half2float(__ushort_as_half((uint16_t)((grp & 1) ? (spa >> 16) : (spa & 0xFFFFu))));
-                const float fb = 0.5f * __half2float(__ushort_as_half((uint16_t)((grp & 1) ? (spb >> 16) : (spb & 0xFFFFu))));
+                const float fa = (grp & 1) ? __high2float(sa[grp >> 1]) : __low2float(sa[grp >> 1]);
+                const float fb = (grp & 1) ? __high2float(sbh[grp >> 1]) : __low2float(sbh[grp >> 1]);
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
                     float d[4] = {0.f, 0.f, 0.f, 0.f};
@@ -246,35 +348,32 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
                     acc[nb][3] = fmaf(d[3], fb, acc[nb][3]);
                 }
             }
+        } else {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
         }
 
-        // deterministic cross-warp sum through shared memory
-        float* rbuf = red + (size_t)buf * kGemvWarps * 32 * 4 * NB;
+        // park this warp's fragment; the sum over warps happens kGemvRedLag items later
+        wait(bar_rempty + 8 * b, ((uint32_t)(n / kGemvRed) & 1u) ^ 1u, 14);
+        float* rbuf = red + (size_t)b * kRedFloats;
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb)
             *reinterpret_cast<float4*>(rbuf + ((size_t)(warp * 32 + lane) * NB + nb) * 4) =
                 make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
-        __syncthreads();
-        if (tid < 128 * NB) {
-            const int nb = tid >> 7, l = (tid & 127) >> 2, reg = tid & 3;
-            float sum = 0.f;
-            for (int w = 0; w < act; ++w) sum += rbuf[((size_t)(w * 32 + l) * NB + nb) * 4 + reg];
-            const int row = ctx.tile * 16 + (l >> 2) + ((reg >> 1) << 3);
-            const int col = nb * 8 + ((l & 3) << 1) + (reg & 1);
-            if (row < P.N && col < M) {
-                if (P.partial != nullptr) {
-                    P.partial[((int64_t)ctx.chunk * M + col) * P.N + row] = sum;
-                } else {
-                    if (P.bias != nullptr) sum += load_act<kBf16>(P.bias, row);
-                    store_any(P.y, y_dtype, (int64_t)col * P.N + row, sum);
-                }
-            }
-        }
-        buf ^= 1;
-        ctx = nctx;
-        active = nactive;
-        ra = na;
-        rb = nbq;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rfull + 8 * b);
+        if (n >= kGemvRedLag) reduce_next();
+        cursor_next(cc, probs, count);
+    }
+    while (reduced < nitems) reduce_next();
+
+    __syncthreads();
+    if (tid == 0 && *abort_flag != 0) {
+        // copies that were issued but never consumed get a bounded time to land before shared memory is released
+        for (int s = 0; s < kGemvStages; ++s)
+            for (uint32_t i = 0; i < (1u << 16); ++i)
+                if (mbar_try_wait(bar_full + 8 * s, 0) || mbar_try_wait(bar_full + 8 * s, 1)) break;
+        atomicCAS(&g_device_status, 0, *abort_flag);
     }
 }
 
@@ -387,16 +486,17 @@ template <bool kBf16, int NB>
 static int32_t launch_gemv(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
                            int M, int y_dtype, cudaStream_t s) {
     static bool configured = false;
-    const size_t smem = kLutBytes + (size_t)2 * kGemvWarps * 32 * 4 * NB * sizeof(float);
+    constexpr int COPIES = NB == 1 ? 8 : 4;
+    const size_t smem = gemv_smem_bytes<NB, COPIES>();
     if (!configured) {
-        if (cudaFuncSetAttribute(gemv_mma_kernel<kBf16, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return OJX_ERR_LAUNCH;
+        const cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<kBf16, NB, COPIES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { last_cuda_error() = e; return OJX_ERR_LAUNCH; }
         configured = true;
     }
     const int sms = num_sms();
     const int per = (total + sms - 1) / sms;
     const int grid = (total + per - 1) / per;
-    gemv_mma_kernel<kBf16, NB><<<grid, kGemvThreads, smem, s>>>(probs, single, count, total, M, y_dtype);
+    gemv_mma_kernel<kBf16, NB, COPIES><<<grid, kGemvBlock, smem, s>>>(probs, single, count, total, M, y_dtype);
     return launch_status();
 }
 

@@ -42,6 +42,14 @@ const char* ojx_e8t_status_string(int32_t st) {
     }
 }
 
+const char* ojx_e8t_last_cuda_error(void) { return cudaGetErrorString(ojx::last_cuda_error()); }
+
+int32_t ojx_e8t_device_status(void) {
+    int h = 0;
+    if (cudaMemcpyFromSymbol(&h, ojx::g_device_status, sizeof(int)) != cudaSuccess) return OJX_ERR_LAUNCH;
+    return h == 0 ? OJX_OK : OJX_ERR_TIMEOUT;
+}
+
 int32_t ojx_e8t_encode(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
                        uint8_t* packed_out, uint16_t* scales_out, void* stream) {
     return ojx::encode_impl(w, w_dtype, rows, cols, group, packed_out, scales_out, (cudaStream_t)stream);
