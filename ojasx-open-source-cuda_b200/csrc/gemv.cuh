@@ -7,10 +7,10 @@
 // Fast path (K % 256 == 0, bf16/fp16 activations, M <= 16)
 //   * one CTA = 16 warps; warp w owns one 256-wide slice of K and keeps that slice of x in
 //     registers as mma.m16n8k16 B fragments, so activations are read once per CTA;
-//   * a work item is 16 weight rows x one K chunk (= all slices of the CTA); a producer warp keeps a
-//     4-deep ring of items (~16 KB each) in flight with 1-D bulk copies (cp.async.bulk + mbarrier),
-//     so ~64 KB per SM is always on its way from HBM; consumer lanes then pick up 48 B of codes +
-//     16 B of scales per row with 128-bit shared-memory loads;
+//   * a work item is 16 weight rows x one K chunk (= all slices of the CTA); three items (~16 KB each)
+//     beyond the current one are always in flight from HBM into a 5-stage shared-memory ring
+//     (16-byte cp.async copies issued by all threads, completion on mbarriers); lanes then pick up
+//     their rows' codes and scales with shared-memory loads;
 //   * a 12-bit rank is turned into eight trits by ONE shared-memory lookup; the table is stored
 //     eight times (stride 32 B) so that lanes of different lane%8 never collide on a bank;
 //   * trits become +-2.0 / 0 fp16|bf16 operand registers with byte permutes, the MACs run on the
@@ -36,7 +36,9 @@ __host__ __device__ inline int gemv_active_warps(int K) {
     return 1;
 }
 __host__ __device__ inline int gemv_kchunks(int K) { return (K / 256) / gemv_active_warps(K); }
-__host__ __device__ inline int gemv_row_tiles(int N) { return (N + 15) / 16; }
+// The public tile unit is 32 rows (ojx_e8t_gemv_tiles); this kernel walks them as two 16-row halves.
+__host__ __device__ inline int gemv_row_tiles32(int N) { return (N + 31) / 32; }
+__host__ __device__ inline int gemv_row_tiles(int N) { return 2 * gemv_row_tiles32(N); }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
@@ -95,10 +97,10 @@ __device__ __forceinline__ void cursor_load_problem(Cursor& c, const ojx_e8t_gem
 }
 __device__ __forceinline__ void cursor_seek(Cursor& c, const ojx_e8t_gemv_problem* probs, int count, int item) {
     int p = 0;
-    while (p + 1 < count && probs[p + 1].tile_begin <= item) ++p;
+    while (p + 1 < count && 2 * probs[p + 1].tile_begin <= item) ++p;      // tile_begin counts 32-row tiles
     c.prob = p;
     cursor_load_problem(c, probs);
-    const int local = item - probs[p].tile_begin;
+    const int local = item - 2 * probs[p].tile_begin;
     c.chunk = local / c.tiles;
     c.tile = local - c.chunk * c.tiles;
 }
@@ -115,12 +117,25 @@ __device__ __forceinline__ void cursor_next(Cursor& c, const ojx_e8t_gemv_proble
     }
 }
 
+// 16-byte asynchronous copy global -> shared (L2 only, no L1 allocation) and the mbarrier arrive that
+// fires when all of this thread's earlier copies have landed.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // Shared-memory plan of the fast kernel.
 //   lut    COPIES interleaved copies of the rank -> trit-nibble table (entry r, copy c at (r*COPIES + c)*4)
-//   ring   kGemvStages work items; an item holds 16 rows of codes (pitch = bytes + 16, so the 8 rows a
-//          128-bit load touches fall on distinct banks) followed by 16 rows of scales (same rule)
+//   ring   kGemvStages work items; an item holds 16 rows of codes (pitch = bytes + 16, so the 8 rows one
+//          shared-memory load touches fall on distinct banks) followed by 16 rows of scales (same rule);
+//          filled by all 512 threads with 16-byte cp.async copies (two per thread and item), completion
+//          counted on an mbarrier.  One bulk (TMA) copy per padded row was tried first and capped the
+//          kernel near 1 TB/s: ~32 small bulk copies per 16 KB item cost ~140 cycles each per SM.
 //   red    kGemvRed buffers of per-warp fragments for the deterministic cross-warp sum
-constexpr int kGemvStages = 4;
+constexpr int kGemvStages = 5;                              // ring depth
+constexpr int kGemvAhead = 3;                               // items in flight beyond the one being decoded
 constexpr int kGemvRed = 4;
 constexpr int kGemvRedLag = 2;                              // an item is summed two items after it was computed
 constexpr int kGemvMaxCodePitch = kGemvWarps * 48 + 16;     // 784
@@ -128,14 +143,72 @@ constexpr int kGemvMaxScalePitch = kGemvWarps * 16 + 16;    // 272
 constexpr int kGemvStageBytes = 16 * (kGemvMaxCodePitch + kGemvMaxScalePitch);   // 16896
 constexpr int kGemvBlock = kGemvThreads;
 
+// Per-thread share of filling ring stages: every thread copies up to two 16-byte chunks of each item.
+// The chunk -> (row, column) mapping depends only on the problem's K, so it is recomputed when the
+// issue cursor moves to another problem, not per item.
+struct ItemLoader {
+    uint32_t ring, bar_full, bar_empty;
+    int tid;
+    int prob;                      // problem the mapping below belongs to (-1: none)
+    uint32_t dst[2];               // byte offset inside a stage
+    int64_t src[2];                // byte offset from the tile's first row (codes) / first scale row
+    int row[2];                    // row inside the tile, -1: this thread has no chunk
+    bool is_scale[2];
+
+    __device__ __forceinline__ void map_problem(const Cursor& c) {
+        prob = c.prob;
+        const int cb = c.act * 48, sb = c.act * 16;
+        const int code_chunks = 48 * c.act, all_chunks = 64 * c.act;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int ch = tid + j * kGemvThreads;
+            if (ch < code_chunks) {
+                const int r = ch / (3 * c.act), col = ch - r * 3 * c.act;
+                row[j] = r; is_scale[j] = false;
+                dst[j] = (uint32_t)(r * (cb + 16) + col * 16);
+                src[j] = (int64_t)r * (c.K * 3 / 16) + col * 16;
+            } else if (ch < all_chunks) {
+                const int cs = ch - code_chunks;
+                const int r = cs / c.act, col = cs - r * c.act;
+                row[j] = r; is_scale[j] = true;
+                dst[j] = (uint32_t)(16 * kGemvMaxCodePitch + r * (sb + 16) + col * 16);
+                src[j] = (int64_t)r * (c.K / 16) + col * 16;
+            } else {
+                row[j] = -1; is_scale[j] = false; dst[j] = 0; src[j] = 0;
+            }
+        }
+    }
+
+    // Copies item number n of this CTA (cursor c) into stage n mod S once the stage has been released.
+    template <typename WaitFn>
+    __device__ __forceinline__ void issue(const Cursor& c, const ojx_e8t_gemv_problem* probs, int n, WaitFn&& wait) {
+        if (c.prob != prob) map_problem(c);
+        const int s = n % kGemvStages;
+        wait(bar_empty + 8 * s, ((uint32_t)(n / kGemvStages) & 1u) ^ 1u, 11);
+        const ojx_e8t_gemv_problem& P = probs[c.prob];
+        const int rows = min(16, c.N - c.tile * 16);
+        const uint32_t stage = ring + s * kGemvStageBytes;
+        const int64_t code_base = (int64_t)c.tile * 16 * (c.K * 3 / 16) + (int64_t)c.chunk * c.act * 48;
+        const int64_t scale_base = (int64_t)c.tile * 16 * (c.K / 16) + (int64_t)c.chunk * c.act * 16;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            if (row[j] >= 0 && row[j] < rows) {
+                const uint8_t* sp = is_scale[j] ? reinterpret_cast<const uint8_t*>(P.scales) + scale_base + src[j]
+                                                : P.packed + code_base + src[j];
+                cp_async16(stage + dst[j], sp);
+            }
+        cp_async_arrive(bar_full + 8 * s);
+    }
+};
+
 template <int NB, int COPIES> constexpr size_t gemv_smem_bytes() {
     return (size_t)kLutEntries * COPIES * 4 + (size_t)kGemvStages * kGemvStageBytes +
            (size_t)kGemvRed * kGemvWarps * 32 * 4 * NB * sizeof(float) + 256;
 }
 
 // All 16 warps are symmetric.  For item n (counted from the CTA's first item):
-//   * warp (n mod 16) issued its bulk copies kGemvStages-1 items earlier, after waiting for the ring stage
-//     to be released by all warps ("empty" barrier);
+//   * all threads issued its cp.async copies kGemvAhead items earlier, after waiting for the ring stage to
+//     be released by all warps ("empty" barrier); the stage being refilled was last used two items ago;
 //   * every warp waits for the bytes ("full" barrier), pulls its rows' slice into registers, releases
 //     the stage, decodes and multiplies, and parks its fragment in a reduction buffer ("rfull" barrier);
 //   * warp ((n - 2) mod 16) then adds up the sixteen fragments of item n-2 in warp order and writes
@@ -166,7 +239,7 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     }
     if (tid == 0) {
         for (int s = 0; s < kGemvStages; ++s) {
-            mbar_init(bar_full + 8 * s, 1);                 // the issuing lane's expect_tx arrive
+            mbar_init(bar_full + 8 * s, kGemvThreads);      // every thread's cp.async arrive
             mbar_init(bar_empty + 8 * s, kGemvWarps);       // every warp has pulled its slice
         }
         for (int b = 0; b < kGemvRed; ++b) {
@@ -190,34 +263,18 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
         if (*abort_flag == 0) mbar_wait(bar, parity, abort_flag, code);
     };
 
-    // ---- issue: bulk copies of item n into ring stage n mod S ----
+    // ---- issue: every thread copies its chunks of item n into ring stage n mod S ----
     Cursor ic;                                  // cursor of the next item to be issued
     cursor_seek(ic, probs, count, i0);
     int issued = 0;
+    ItemLoader loader;
+    loader.ring = ring; loader.bar_full = bar_full; loader.bar_empty = bar_empty; loader.tid = tid; loader.prob = -1;
     auto issue_next = [&]() {
-        const int n = issued, s = n % kGemvStages;
-        if (warp == (n & (kGemvWarps - 1))) {
-            wait(bar_empty + 8 * s, ((uint32_t)(n / kGemvStages) & 1u) ^ 1u, 11);
-            const ojx_e8t_gemv_problem& P = probs[ic.prob];
-            const uint32_t cb = ic.act * 48, sb = ic.act * 16;
-            const int rows = min(16, ic.N - ic.tile * 16);
-            const uint32_t stage = ring + s * kGemvStageBytes;
-            if (lane == 0) mbar_expect_tx(bar_full + 8 * s, (uint32_t)rows * (cb + sb));
-            __syncwarp();
-            const int r = lane & 15;
-            if (r < rows) {
-                const int64_t row = (int64_t)ic.tile * 16 + r;
-                if (lane < 16)
-                    bulk_load(stage + r * (cb + 16), P.packed + row * ((int64_t)ic.K * 3 / 16) + (int64_t)ic.chunk * cb, cb, bar_full + 8 * s);
-                else
-                    bulk_load(stage + 16 * kGemvMaxCodePitch + r * (sb + 16),
-                              reinterpret_cast<const uint8_t*>(P.scales) + row * ((int64_t)ic.K / 16) + (int64_t)ic.chunk * sb, sb, bar_full + 8 * s);
-            }
-        }
+        loader.issue(ic, probs, issued, wait);
         ++issued;
         cursor_next(ic, probs, count);
     };
-    for (int n = 0; n < kGemvStages - 1 && n < nitems; ++n) issue_next();
+    for (int n = 0; n < kGemvAhead && n < nitems; ++n) issue_next();
 
     // ---- reduction of item n (done by warp n mod 16, kGemvRedLag items late) ----
     Cursor rc;                                  // cursor of the next item to be summed
@@ -276,7 +333,7 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     cursor_seek(cc, probs, count, i0);
     for (int n = 0; n < nitems; ++n) {
         const int s = n % kGemvStages, b = n % kGemvRed;
-        if (issued < nitems) issue_next();                       // keeps kGemvStages-1 items in flight
+        if (issued < nitems) issue_next();                       // keeps kGemvAhead items in flight
 
         // (re)load this warp's activations when the problem or the K chunk changes
         if (cc.prob != cur_prob || cc.chunk != cur_chunk) {
@@ -449,28 +506,6 @@ __global__ void __launch_bounds__(256) generic_linear_kernel(const void* __restr
     }
 }
 
-// ---------------------------------------------------------------------------------------------
-// Host side
-// ---------------------------------------------------------------------------------------------
-inline bool gemv_fast_ok(int64_t M, int64_t N, int64_t K, int group, int x_dtype) {
-    return M >= 1 && M <= 16 && K % 256 == 0 && group == 32 && (x_dtype == OJX_BF16 || x_dtype == OJX_F16) &&
-           N >= 1 && N < (1 << 30) && K < (1 << 30);
-}
-
-int32_t gemv_tiles_impl(int64_t N, int64_t K) {
-    if (N <= 0 || K <= 0 || K % 256 != 0) return 0;
-    return gemv_row_tiles((int)N) * gemv_kchunks((int)K);
-}
-int32_t gemv_kchunks_impl(int64_t K) { return (K > 0 && K % 256 == 0) ? gemv_kchunks((int)K) : 0; }
-
-// Scratch of the single-problem entry point: fp32 partials [kchunks][M][N], needed only when K
-// spans more than one chunk of the CTA's 16 slices.
-size_t gemv_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
-    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 256 != 0) return 0;
-    const int kc = gemv_kchunks((int)K);
-    return kc > 1 ? (size_t)kc * M * N * sizeof(float) : 0;
-}
-
 static int g_num_sms = 0;
 static int num_sms() {
     if (g_num_sms == 0) {
@@ -480,87 +515,6 @@ static int num_sms() {
         g_num_sms = n > 0 ? n : 148;
     }
     return g_num_sms;
-}
-
-template <bool kBf16, int NB>
-static int32_t launch_gemv(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
-                           int M, int y_dtype, cudaStream_t s) {
-    static bool configured = false;
-    constexpr int COPIES = NB == 1 ? 8 : 4;
-    const size_t smem = gemv_smem_bytes<NB, COPIES>();
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<kBf16, NB, COPIES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { last_cuda_error() = e; return OJX_ERR_LAUNCH; }
-        configured = true;
-    }
-    const int sms = num_sms();
-    const int per = (total + sms - 1) / sms;
-    const int grid = (total + per - 1) / per;
-    gemv_mma_kernel<kBf16, NB, COPIES><<<grid, kGemvBlock, smem, s>>>(probs, single, count, total, M, y_dtype);
-    return launch_status();
-}
-
-int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
-                          int x_dtype, int y_dtype, int needs_reduce, cudaStream_t s) {
-    OJX_RETURN_IF(!problems, OJX_ERR_NULL);
-    OJX_RETURN_IF(count <= 0 || total_tiles <= 0 || M < 1 || M > 16, OJX_ERR_SHAPE);
-    OJX_RETURN_IF(x_dtype != OJX_BF16 && x_dtype != OJX_F16, OJX_ERR_DTYPE);
-    OJX_RETURN_IF(y_dtype != OJX_BF16 && y_dtype != OJX_F16 && y_dtype != OJX_F32, OJX_ERR_DTYPE);
-    OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
-    int32_t st;
-    const bool bf = x_dtype == OJX_BF16;
-    ojx_e8t_gemv_problem none = {};
-    if (M <= 8) st = bf ? launch_gemv<true, 1>(problems, none, count, total_tiles, (int)M, y_dtype, s)
-                        : launch_gemv<false, 1>(problems, none, count, total_tiles, (int)M, y_dtype, s);
-    else st = bf ? launch_gemv<true, 2>(problems, none, count, total_tiles, (int)M, y_dtype, s)
-                 : launch_gemv<false, 2>(problems, none, count, total_tiles, (int)M, y_dtype, s);
-    OJX_RETURN_IF(st != OJX_OK, st);
-    if (!needs_reduce) return OJX_OK;
-    // Problems whose K spans several chunks carry a partial buffer; the reduce pass skips the rest.
-    dim3 grid(64, count > 64 ? 64 : count);
-    if (bf) gemv_reduce_kernel<true><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype);
-    else gemv_reduce_kernel<false><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype);
-    return launch_status();
-}
-
-int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
-                  const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
-                  void* workspace, size_t workspace_bytes, cudaStream_t s) {
-    OJX_RETURN_IF(!x || !packed || !scales || !y, OJX_ERR_NULL);
-    OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0, OJX_ERR_SHAPE);
-    OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
-    OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
-    group = effective_group(group);
-    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) |
-                           reinterpret_cast<uintptr_t>(scales)) & 15) == 0;
-    if (gemv_fast_ok(M, N, K, group, x_dtype) && aligned) {
-        const size_t need = gemv_workspace_bytes_impl(M, N, K);
-        OJX_RETURN_IF(need > 0 && (!workspace || workspace_bytes < need), OJX_ERR_WORKSPACE);
-        OJX_RETURN_IF(need > 0 && (reinterpret_cast<uintptr_t>(workspace) & 15) != 0, OJX_ERR_ALIGN);
-        ojx_e8t_gemv_problem h;
-        h.x = x; h.packed = packed; h.scales = scales; h.bias = bias; h.y = y;
-        const int kc = gemv_kchunks((int)K);
-        h.partial = kc > 1 ? static_cast<float*>(workspace) : nullptr;
-        h.N = (int)N; h.K = (int)K; h.tile_begin = 0; h.reserved = 0;
-        const int total = gemv_row_tiles((int)N) * kc;
-        int32_t st;
-        const bool bf = x_dtype == OJX_BF16;
-        if (M <= 8) st = bf ? launch_gemv<true, 1>(nullptr, h, 1, total, (int)M, y_dtype, s) : launch_gemv<false, 1>(nullptr, h, 1, total, (int)M, y_dtype, s);
-        else st = bf ? launch_gemv<true, 2>(nullptr, h, 1, total, (int)M, y_dtype, s) : launch_gemv<false, 2>(nullptr, h, 1, total, (int)M, y_dtype, s);
-        OJX_RETURN_IF(st != OJX_OK, st);
-        if (kc > 1) {
-            dim3 grid(64, 1);
-            if (bf) gemv_reduce_kernel<true><<<grid, 256, 0, s>>>(nullptr, h, 1, (int)M, y_dtype);
-            else gemv_reduce_kernel<false><<<grid, 256, 0, s>>>(nullptr, h, 1, (int)M, y_dtype);
-        }
-        return launch_status();
-    }
-    // generic path
-    int64_t warps_needed = N;
-    int64_t blocks = (warps_needed * 32 + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    generic_linear_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
-    return launch_status();
 }
 
 }  // namespace ojx

@@ -1,0 +1,114 @@
+// Host-side routing of the decode-shape entry points to the kernels in gemv.cuh / gemv_e4m3.cuh.
+#pragma once
+
+#include "gemv.cuh"
+#include "gemv_b1.cuh"
+
+namespace ojx {
+
+inline bool gemv_fast_ok(int64_t M, int64_t N, int64_t K, int group, int x_dtype) {
+    return M >= 1 && M <= 16 && K % 256 == 0 && group == 32 && (x_dtype == OJX_BF16 || x_dtype == OJX_F16) &&
+           N >= 1 && N < (1 << 30) && K < (1 << 30);
+}
+
+int32_t gemv_tiles_impl(int64_t N, int64_t K) {
+    if (N <= 0 || K <= 0 || K % 256 != 0) return 0;
+    return gemv_row_tiles32((int)N) * gemv_kchunks((int)K);
+}
+int32_t gemv_kchunks_impl(int64_t K) { return (K > 0 && K % 256 == 0) ? gemv_kchunks((int)K) : 0; }
+
+// Scratch of the single-problem entry point: fp32 partials [kchunks][M][N], needed only when K
+// spans more than one chunk of the CTA's 16 slices.
+size_t gemv_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 256 != 0) return 0;
+    const int kc = gemv_kchunks((int)K);
+    return kc > 1 ? (size_t)kc * M * N * sizeof(float) : 0;
+}
+
+template <bool kBf16, int NB>
+static int32_t launch_gemv(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
+                           int M, int y_dtype, cudaStream_t s) {
+    static bool configured = false;
+    constexpr int COPIES = 4;
+    const size_t smem = gemv_smem_bytes<NB, COPIES>();
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<kBf16, NB, COPIES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { last_cuda_error() = e; return OJX_ERR_LAUNCH; }
+        configured = true;
+    }
+    const int sms = num_sms();
+    const int per = (total + sms - 1) / sms;
+    const int grid = (total + per - 1) / per;
+    gemv_mma_kernel<kBf16, NB, COPIES><<<grid, kGemvBlock, smem, s>>>(probs, single, count, total, M, y_dtype);
+    return launch_status();
+}
+
+// One bf16 activation row takes the int8 tensor-core kernel; everything else the 16-bit kernel.
+static int32_t dispatch_gemv(bool bf16, const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count,
+                             int total, int M, int y_dtype, cudaStream_t s) {
+    if (bf16 && M == 1) return launch_gemv_b1(probs, single, count, total, y_dtype, s);
+    // the multi-row kernel walks every 32-row tile as two 16-row halves
+    if (bf16) return M <= 8 ? launch_gemv<true, 1>(probs, single, count, 2 * total, M, y_dtype, s)
+                            : launch_gemv<true, 2>(probs, single, count, 2 * total, M, y_dtype, s);
+    return M <= 8 ? launch_gemv<false, 1>(probs, single, count, 2 * total, M, y_dtype, s)
+                  : launch_gemv<false, 2>(probs, single, count, 2 * total, M, y_dtype, s);
+}
+
+int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
+                          int x_dtype, int y_dtype, int needs_reduce, cudaStream_t s) {
+    OJX_RETURN_IF(!problems, OJX_ERR_NULL);
+    OJX_RETURN_IF(count <= 0 || total_tiles <= 0 || M < 1 || M > 16, OJX_ERR_SHAPE);
+    OJX_RETURN_IF(x_dtype != OJX_BF16 && x_dtype != OJX_F16, OJX_ERR_DTYPE);
+    OJX_RETURN_IF(y_dtype != OJX_BF16 && y_dtype != OJX_F16 && y_dtype != OJX_F32, OJX_ERR_DTYPE);
+    OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
+    const bool bf = x_dtype == OJX_BF16;
+    ojx_e8t_gemv_problem none = {};
+    const int32_t st = dispatch_gemv(bf, problems, none, count, total_tiles, (int)M, y_dtype, s);
+    OJX_RETURN_IF(st != OJX_OK, st);
+    if (!needs_reduce) return OJX_OK;
+    // Problems whose K spans several chunks carry a partial buffer; the reduce pass skips the rest.
+    dim3 grid(64, count > 64 ? 64 : count);
+    if (bf) gemv_reduce_kernel<true><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype);
+    else gemv_reduce_kernel<false><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype);
+    return launch_status();
+}
+
+int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                  const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
+                  void* workspace, size_t workspace_bytes, cudaStream_t s) {
+    OJX_RETURN_IF(!x || !packed || !scales || !y, OJX_ERR_NULL);
+    OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0, OJX_ERR_SHAPE);
+    OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
+    OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
+    group = effective_group(group);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) |
+                           reinterpret_cast<uintptr_t>(scales)) & 15) == 0;
+    if (gemv_fast_ok(M, N, K, group, x_dtype) && aligned) {
+        const size_t need = gemv_workspace_bytes_impl(M, N, K);
+        OJX_RETURN_IF(need > 0 && (!workspace || workspace_bytes < need), OJX_ERR_WORKSPACE);
+        OJX_RETURN_IF(need > 0 && (reinterpret_cast<uintptr_t>(workspace) & 15) != 0, OJX_ERR_ALIGN);
+        ojx_e8t_gemv_problem h;
+        h.x = x; h.packed = packed; h.scales = scales; h.bias = bias; h.y = y;
+        const int kc = gemv_kchunks((int)K);
+        h.partial = kc > 1 ? static_cast<float*>(workspace) : nullptr;
+        h.N = (int)N; h.K = (int)K; h.tile_begin = 0; h.reserved = 0;
+        const int total = gemv_row_tiles32((int)N) * kc;
+        const bool bf = x_dtype == OJX_BF16;
+        const int32_t st = dispatch_gemv(bf, nullptr, h, 1, total, (int)M, y_dtype, s);
+        OJX_RETURN_IF(st != OJX_OK, st);
+        if (kc > 1) {
+            dim3 grid(64, 1);
+            if (bf) gemv_reduce_kernel<true><<<grid, 256, 0, s>>>(nullptr, h, 1, (int)M, y_dtype);
+            else gemv_reduce_kernel<false><<<grid, 256, 0, s>>>(nullptr, h, 1, (int)M, y_dtype);
+        }
+        return launch_status();
+    }
+    // generic path
+    int64_t warps_needed = N;
+    int64_t blocks = (warps_needed * 32 + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    generic_linear_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
+    return launch_status();
+}
+
+}  // namespace ojx

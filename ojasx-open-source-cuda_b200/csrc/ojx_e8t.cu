@@ -3,6 +3,8 @@
 #include "common.cuh"
 #include "codec.cuh"
 #include "gemv.cuh"
+#include "gemv_b1.cuh"
+#include "gemv_host.cuh"
 #include "gemm_tcgen05.cuh"
 
 namespace ojx {

@@ -46,8 +46,8 @@ def test_pure_host_entry_points(P):
     # tile / chunk arithmetic is host-only
     assert lib.ojx_e8t_gemv_kchunks(4096) == 1 and lib.ojx_e8t_gemv_kchunks(14336) == 4
     assert lib.ojx_e8t_gemv_kchunks(8192) == 2 and lib.ojx_e8t_gemv_kchunks(100) == 0
-    assert lib.ojx_e8t_gemv_tiles(4096, 4096) == 256 and lib.ojx_e8t_gemv_tiles(4096, 14336) == 1024
-    assert lib.ojx_e8t_gemv_tiles(17, 256) == 2
+    assert lib.ojx_e8t_gemv_tiles(4096, 4096) == 128 and lib.ojx_e8t_gemv_tiles(4096, 14336) == 512      # 32-row tiles x K chunks
+    assert lib.ojx_e8t_gemv_tiles(17, 256) == 1 and lib.ojx_e8t_gemv_tiles(33, 256) == 2
     assert lib.ojx_e8t_gemv_workspace_bytes(4, 4096, 4096) == 0
     assert lib.ojx_e8t_gemv_workspace_bytes(4, 4096, 14336) == 4 * 4 * 4096 * 4
     assert lib.ojx_e8t_gemm_workspace_bytes(2048, 4096, 4096) >= 16

@@ -169,7 +169,7 @@ def test_gemv_fp32_out_is_tight(P, oracle):
     scales = torch.from_numpy(scales_np.view(np.int16)).view(torch.float16).to(DEV)
     y = P.ops.linear(torch.from_numpy(x32).bfloat16().to(DEV), packed, scales, None, n, k, 32, out_dtype=torch.float32)
     rel = np.linalg.norm(y.cpu().numpy() - y_ref) / np.linalg.norm(y_ref)
-    assert rel < 5e-6, rel
+    assert rel < 2e-5, rel      # e4m3 split of the activations: tiny elements are truncated at 2^-17 of the slice maximum
 
 
 @pytest.mark.parametrize("n,k,m,xdt", [(7, 13, 3, torch.float32), (5, 19, 2, torch.float32), (4, 48, 2, torch.float32),
