@@ -4,7 +4,7 @@
 //
 // Work decomposition (same as the multi-row kernel in gemv.cuh): a CTA of 16 warps walks a contiguous
 // range of work items; an item is 32 weight rows x one K chunk, warp w owns the 256-wide slice w of the
-// chunk.  Items stream HBM -> shared memory through a 4-stage ring of 16-byte cp.async copies (two
+// chunk.  Items stream HBM -> shared memory through a 5-stage ring of 16-byte cp.async copies (three
 // items always in flight), completion counted on mbarriers.
 //
 // What makes this path cheap per weight:
@@ -31,12 +31,14 @@
 namespace ojx {
 
 constexpr int kB1Rows = 32;                                   // weight rows per work item
-constexpr int kB1Stages = 4;
-constexpr int kB1Ahead = 2;
+constexpr int kB1Stages = 5;
+constexpr int kB1Ahead = 3;
 constexpr int kB1Red = 4;
 constexpr int kB1RedLag = 2;
 constexpr int kB1Copies = 4;                                  // interleaved copies of the lookup table
-constexpr int kB1LutBytes = kLutEntries * kB1Copies * 4;      // 65536
+// Only the 3281 real entries are stored; a corrupt 12-bit rank (up to 4095) would read at most 64 KB past
+// the table start, which is still inside this kernel's shared-memory allocation (ring and buffers follow).
+constexpr int kB1LutBytes = ((kNumPoints * kB1Copies * 4 + 1023) / 1024) * 1024;   // 53248
 constexpr int kB1StageBytes = kB1Rows * (kGemvMaxCodePitch + kGemvMaxScalePitch);   // 33792
 constexpr int kB1RedFloats = kGemvWarps * kB1Rows;            // 512 floats per buffer
 constexpr size_t kB1SmemBytes = (size_t)kB1LutBytes + (size_t)kB1Stages * kB1StageBytes +
@@ -108,10 +110,7 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
-    for (int i = tid; i < kLutEntries * kB1Copies; i += kGemvThreads) {
-        const int r = i / kB1Copies;
-        lut[i] = r < kNumPoints ? g_trit_nibbles[r] : 0u;
-    }
+    for (int i = tid; i < kNumPoints * kB1Copies; i += kGemvThreads) lut[i] = g_trit_nibbles[i / kB1Copies];
     if (tid == 0) {
         for (int s = 0; s < kB1Stages; ++s) {
             mbar_init(bar_full + 8 * s, kGemvThreads);      // every thread's cp.async arrive

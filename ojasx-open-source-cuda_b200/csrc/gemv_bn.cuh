@@ -1,0 +1,273 @@
+// Decode GEMV for 2..16 bf16 activation rows on the int8 tensor cores.
+//
+// Same work items, cp.async ring and deterministic deferred reduction as gemv_b1.cuh; the MMA is turned
+// around so that several activation rows cost one instruction:
+//   * the decoded weights are the "B" operand of mma.sync.m16n8k32.s8: eight weight rows x one scale
+//     group (32 k) per instruction; lane (g, t) supplies rank t of the group of row g as its two B
+//     registers (two byte permutes of the looked-up selector word);
+//   * the activations are the "A" operand (16 x 32): rows 0-7 carry the HIGH int8 term of activation rows
+//     0-7 and rows 8-15 their LOW term (x * 2^-e = 128 hi + lo, 13-bit fixed point relative to the
+//     slice maximum of each activation row, see gemv_b1.cuh), so ONE MMA yields both partial products of
+//     eight activation rows and they land in the same lane; 9-16 rows use a second A block;
+//   * per group the lane combines hi and lo in integers, converts once and multiplies by the group's
+//     scale (fp32 FMA), i.e. the reference's order: acc += (sum_k x * coord) * scale.
+#pragma once
+
+#include "gemv_b1.cuh"
+
+namespace ojx {
+
+template <int NBLK> struct BnCfg {
+    static constexpr int kStages = NBLK == 1 ? 4 : 3;
+    static constexpr int kAhead = 2;
+    static constexpr int kRed = 2;                                          // reduction buffers
+    static constexpr int kRedLag = 1;
+    static constexpr int kRedFloats = kGemvWarps * 256 * NBLK;              // per buffer: 16 warps x 32 rows x 8 NBLK
+    static constexpr size_t kSmem = (size_t)kB1LutBytes + (size_t)kStages * kB1StageBytes +
+                                    (size_t)kRed * kRedFloats * sizeof(float) + 256;
+};
+
+template <int NBLK>
+__global__ void __launch_bounds__(kGemvThreads, 1)
+gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_constant__ ojx_e8t_gemv_problem single,
+               int count, int total_items, int M, int y_dtype) {
+    using Cfg = BnCfg<NBLK>;
+    const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint32_t* lut = reinterpret_cast<uint32_t*>(smem);
+    const uint32_t ring = smem_u32(smem) + kB1LutBytes;
+    float* red = reinterpret_cast<float*>(smem + kB1LutBytes + Cfg::kStages * kB1StageBytes);
+    uint8_t* tail = smem + kB1LutBytes + Cfg::kStages * kB1StageBytes + Cfg::kRed * Cfg::kRedFloats * sizeof(float);
+    const uint32_t bar_full = smem_u32(tail), bar_empty = bar_full + 8 * Cfg::kStages;
+    const uint32_t bar_rfull = bar_empty + 8 * Cfg::kStages, bar_rempty = bar_rfull + 8 * Cfg::kRed;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 16 * Cfg::kStages + 16 * Cfg::kRed);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+
+    for (int i = tid; i < kNumPoints * kB1Copies; i += kGemvThreads) lut[i] = g_trit_nibbles[i / kB1Copies];
+    if (tid == 0) {
+        for (int s = 0; s < Cfg::kStages; ++s) {
+            mbar_init(bar_full + 8 * s, kGemvThreads);
+            mbar_init(bar_empty + 8 * s, kGemvWarps);
+        }
+        for (int b = 0; b < Cfg::kRed; ++b) {
+            mbar_init(bar_rfull + 8 * b, kGemvWarps);       // every warp has parked its partial sums
+            mbar_init(bar_rempty + 8 * b, kGemvWarps);      // every warp has summed its share of the outputs
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int64_t per = ((int64_t)total_items + gridDim.x - 1) / gridDim.x;
+    const int i0 = (int)min((int64_t)total_items, per * blockIdx.x);
+    const int i1 = (int)min((int64_t)total_items, per * (blockIdx.x + 1));
+    if (i0 >= i1) return;
+    const int nitems = i1 - i0;
+
+    // ---- loader (identical to the single-row kernel) ----
+    const int lr = tid >> 4, ls = tid & 15;
+    B1Cursor ic;
+    b1_seek(ic, probs, count, i0);
+    int issued = 0;
+    auto issue_next = [&]() {
+        const int n = issued, s = n % Cfg::kStages;
+        b1_wait(bar_empty + 8 * s, ((uint32_t)(n / Cfg::kStages) & 1u) ^ 1u, abort_flag, 41);
+        const int row = ic.tile * kB1Rows + lr;
+        if (row < ic.N) {
+            const ojx_e8t_gemv_problem& P = probs[ic.prob];
+            const int cchunks = 3 * ic.act;
+            const uint32_t cb = ic.act * 48, sb = ic.act * 16;
+            const uint32_t stage = ring + s * kB1StageBytes;
+            const uint8_t* csrc = P.packed + (int64_t)row * (ic.K * 3 / 16) + (int64_t)ic.chunk * cb + ls * 16;
+            const uint32_t cdst = stage + lr * (cb + 16) + ls * 16;
+#pragma unroll
+            for (int j = 0; j < 3; ++j)
+                if (ls + 16 * j < cchunks) cp_async16(cdst + 256 * j, csrc + 256 * j);
+            if (ls < ic.act)
+                cp_async16(stage + kB1Rows * kGemvMaxCodePitch + lr * (sb + 16) + ls * 16,
+                           reinterpret_cast<const uint8_t*>(P.scales) + (int64_t)row * (ic.K / 16) + (int64_t)ic.chunk * sb + ls * 16);
+        }
+        cp_async_arrive(bar_full + 8 * s);
+        ++issued;
+        b1_next(ic, probs, count);
+    };
+    for (int n = 0; n < Cfg::kAhead && n < nitems; ++n) issue_next();
+
+    // ---- reduction: every warp sums 16 * NBLK of the item's 256 * NBLK outputs over the 16 warps, in warp order ----
+    B1Cursor rc;
+    b1_seek(rc, probs, count, i0);
+    int reduced = 0;
+    auto reduce_next = [&]() {
+        const int n = reduced, b = n % Cfg::kRed;
+        b1_wait(bar_rfull + 8 * b, (uint32_t)(n / Cfg::kRed) & 1u, abort_flag, 43);
+        const float* rbuf = red + (size_t)b * Cfg::kRedFloats;
+        if (lane < 16 * NBLK) {
+            const int o = warp * 16 * NBLK + lane;                 // output slot inside a warp's 256*NBLK block
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < kGemvWarps; ++w) sum += rbuf[w * 256 * NBLK + o];
+            // slot layout: ((blk * 4 + tile8) * 32 + lane') * 2 + j   with lane' = (batch g', rank lane t')
+            const int j = o & 1, lp = (o >> 1) & 31, tile8 = (o >> 6) & 3, blk = o >> 8;
+            const int row = rc.tile * kB1Rows + tile8 * 8 + ((lp & 3) << 1) + j;
+            const int col = blk * 8 + (lp >> 2);
+            if (row < rc.N && col < M) {
+                const ojx_e8t_gemv_problem& P = probs[rc.prob];
+                if (P.partial != nullptr) P.partial[((int64_t)rc.chunk * M + col) * rc.N + row] = sum;
+                else {
+                    if (P.bias != nullptr) sum += __bfloat162float(static_cast<const __nv_bfloat16*>(P.bias)[row]);
+                    store_any(P.y, y_dtype, (int64_t)col * rc.N + row, sum);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rempty + 8 * b);
+        ++reduced;
+        b1_next(rc, probs, count);
+    };
+
+    // ---- lane constants: this lane takes rank t of every scale group (byte window + nibble shift) ----
+    const uint32_t lut_lane = smem_u32(lut) + ((lane & (kB1Copies - 1)) << 2);
+    constexpr uint32_t kTritBytes = 0x00FF0100u;
+    constexpr uint32_t kEntryMask = 0xFFFu << 4;
+    const uint32_t bt = (t == 0) ? 0u : (t == 1) ? 1u : (t == 2) ? 3u : 4u;     // first byte of this lane's rank
+    const uint32_t sel_even = bt | ((bt + 1) << 4);
+    const uint32_t sel_odd = (bt + 2) | ((bt + 3) << 4);
+    const uint32_t lsh = (t & 1) ? 0u : 4u;                                    // rank * 16 from the 16-bit window
+
+    uint32_t xa[NBLK][8][4];                          // A fragments: [block][group][a0 hi, a1 lo, a2 hi, a3 lo]
+    float upscale[NBLK];
+    int cur_prob = -1, cur_chunk = -1;
+    B1Cursor cc;
+    b1_seek(cc, probs, count, i0);
+
+    for (int n = 0; n < nitems; ++n) {
+        const int s = n % Cfg::kStages, b = n % Cfg::kRed;
+        if (issued < nitems) issue_next();
+
+        if (cc.prob != cur_prob || cc.chunk != cur_chunk) {
+            cur_prob = cc.prob;
+            cur_chunk = cc.chunk;
+            const uint16_t* xp = static_cast<const uint16_t*>(probs[cc.prob].x);
+            const int slice = cc.chunk * cc.act + warp;
+#pragma unroll
+            for (int blk = 0; blk < NBLK; ++blk) {
+                const int m = blk * 8 + g;
+                const bool on = warp < cc.act && m < M;
+                uint4 q[8];
+                float amax = 0.f;
+#pragma unroll
+                for (int grp = 0; grp < 8; ++grp) {
+                    q[grp] = make_uint4(0, 0, 0, 0);
+                    if (on) q[grp] = __ldg(reinterpret_cast<const uint4*>(xp + (int64_t)m * cc.K + slice * 256 + grp * 32 + t * 8));
+                    const uint32_t w[4] = {q[grp].x, q[grp].y, q[grp].z, q[grp].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w[i] << 16)), fabsf(__uint_as_float(w[i] & 0xFFFF0000u))));
+                }
+                amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));      // the four lanes of activation row m
+                int e = 0;
+                if (amax > 0.f) e = max(-100, min(100, (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127 - 12));
+                const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+                upscale[blk] = __uint_as_float((uint32_t)(127 + e) << 23);
+#pragma unroll
+                for (int grp = 0; grp < 8; ++grp) {
+                    const uint32_t w[4] = {q[grp].x, q[grp].y, q[grp].z, q[grp].w};
+                    uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float v = (i & 1) ? __uint_as_float(w[i >> 1] & 0xFFFF0000u) : __uint_as_float(w[i >> 1] << 16);
+                        const int X = __float2int_rn(v * down);
+                        const int hi = (X + 64) >> 7, lo = X - (hi << 7);
+                        hw[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
+                        lw[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
+                    }
+                    xa[blk][grp][0] = hw[0]; xa[blk][grp][1] = lw[0]; xa[blk][grp][2] = hw[1]; xa[blk][grp][3] = lw[1];
+                }
+            }
+        }
+
+        b1_wait(bar_full + 8 * s, (uint32_t)(n / Cfg::kStages) & 1u, abort_flag, 42);
+
+        float out[4][NBLK][2];                                     // [8-row tile][block][row 2t | 2t+1]
+#pragma unroll
+        for (int tl = 0; tl < 4; ++tl)
+#pragma unroll
+            for (int blk = 0; blk < NBLK; ++blk) out[tl][blk][0] = out[tl][blk][1] = 0.f;
+
+        if (warp < cc.act) {
+            const uint32_t cb = cc.act * 48, sb = cc.act * 16;
+            const uint32_t stage = ring + s * kB1StageBytes;
+#pragma unroll
+            for (int tl = 0; tl < 4; ++tl) {
+                const uint32_t ca = stage + (tl * 8 + g) * (cb + 16) + warp * 48;
+                const uint32_t sa = stage + kB1Rows * kGemvMaxCodePitch + (tl * 8 + 2 * t) * (sb + 16) + warp * 16;
+                const uint4 q0 = lds_u128(ca), q1 = lds_u128(ca + 16), q2 = lds_u128(ca + 32);
+                const uint4 s0 = lds_u128(sa), s1 = lds_u128(sa + sb + 16);      // scales of rows 2t and 2t+1 of the tile
+                const uint32_t cw[12] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x, q2.y, q2.z, q2.w};
+                const __half2* h0 = reinterpret_cast<const __half2*>(&s0);
+                const __half2* h1 = reinterpret_cast<const __half2*>(&s1);
+#pragma unroll
+                for (int grp = 0; grp < 8; ++grp) {
+                    const int w0 = (grp & 1) ? (3 * grp - 1) / 2 : (3 * grp) / 2;
+                    const uint32_t win = prmt(cw[w0], cw[w0 + 1], (grp & 1) ? sel_odd : sel_even);
+                    const uint32_t nib = lds_u32(((win << lsh) & kEntryMask) + lut_lane);
+                    const uint32_t b0 = prmt(kTritBytes, 0u, nib), b1 = prmt(kTritBytes, 0u, nib >> 16);
+                    const float f0 = (grp & 1) ? __high2float(h0[grp >> 1]) : __low2float(h0[grp >> 1]);
+                    const float f1 = (grp & 1) ? __high2float(h1[grp >> 1]) : __low2float(h1[grp >> 1]);
+#pragma unroll
+                    for (int blk = 0; blk < NBLK; ++blk) {
+                        int d[4] = {0, 0, 0, 0};
+                        mma_s8(d, xa[blk][grp][0], xa[blk][grp][1], xa[blk][grp][2], xa[blk][grp][3], b0, b1);
+                        // d[0], d[1]: high term for weight rows 2t, 2t+1;  d[2], d[3]: low term (same activation row g)
+                        out[tl][blk][0] = fmaf((float)(d[0] * 128 + d[2]), f0, out[tl][blk][0]);
+                        out[tl][blk][1] = fmaf((float)(d[1] * 128 + d[3]), f1, out[tl][blk][1]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+        } else {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+        }
+
+        b1_wait(bar_rempty + 8 * b, ((uint32_t)(n / Cfg::kRed) & 1u) ^ 1u, abort_flag, 44);
+        float* rbuf = red + (size_t)b * Cfg::kRedFloats + warp * 256 * NBLK;
+#pragma unroll
+        for (int blk = 0; blk < NBLK; ++blk)
+#pragma unroll
+            for (int tl = 0; tl < 4; ++tl)
+                *reinterpret_cast<float2*>(rbuf + ((blk * 4 + tl) * 32 + lane) * 2) =
+                    make_float2(out[tl][blk][0] * upscale[blk], out[tl][blk][1] * upscale[blk]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rfull + 8 * b);
+        if (n >= Cfg::kRedLag) reduce_next();
+        b1_next(cc, probs, count);
+    }
+    while (reduced < nitems) reduce_next();
+
+    __syncthreads();
+    if (tid == 0 && *abort_flag != 0) atomicCAS(&g_device_status, 0, *abort_flag);
+}
+
+template <int NBLK>
+static int32_t launch_gemv_bn(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
+                              int M, int y_dtype, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemv_bn_kernel<NBLK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)BnCfg<NBLK>::kSmem);
+        if (e != cudaSuccess) { last_cuda_error() = e; return OJX_ERR_LAUNCH; }
+        configured = true;
+    }
+    const int sms = num_sms();
+    const int per = (total + sms - 1) / sms;
+    const int grid = (total + per - 1) / per;
+    gemv_bn_kernel<NBLK><<<grid, kGemvThreads, BnCfg<NBLK>::kSmem, s>>>(probs, single, count, total, M, y_dtype);
+    return launch_status();
+}
+
+}  // namespace ojx

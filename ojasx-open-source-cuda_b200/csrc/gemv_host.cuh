@@ -3,6 +3,7 @@
 
 #include "gemv.cuh"
 #include "gemv_b1.cuh"
+#include "gemv_bn.cuh"
 
 namespace ojx {
 
@@ -43,13 +44,14 @@ static int32_t launch_gemv(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv
     return launch_status();
 }
 
-// One bf16 activation row takes the int8 tensor-core kernel; everything else the 16-bit kernel.
+// bf16 activations take the int8 tensor-core kernels (one row: gemv_b1, 2..16 rows: gemv_bn); fp16
+// activations the 16-bit kernel.
 static int32_t dispatch_gemv(bool bf16, const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count,
                              int total, int M, int y_dtype, cudaStream_t s) {
     if (bf16 && M == 1) return launch_gemv_b1(probs, single, count, total, y_dtype, s);
-    // the multi-row kernel walks every 32-row tile as two 16-row halves
-    if (bf16) return M <= 8 ? launch_gemv<true, 1>(probs, single, count, 2 * total, M, y_dtype, s)
-                            : launch_gemv<true, 2>(probs, single, count, 2 * total, M, y_dtype, s);
+    if (bf16) return M <= 8 ? launch_gemv_bn<1>(probs, single, count, total, M, y_dtype, s)
+                            : launch_gemv_bn<2>(probs, single, count, total, M, y_dtype, s);
+    // fp16 activations: the exact 16-bit kernel, which walks every 32-row tile as two 16-row halves
     return M <= 8 ? launch_gemv<false, 1>(probs, single, count, 2 * total, M, y_dtype, s)
                   : launch_gemv<false, 2>(probs, single, count, 2 * total, M, y_dtype, s);
 }

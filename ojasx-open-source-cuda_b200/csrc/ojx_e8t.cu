@@ -4,6 +4,7 @@
 #include "codec.cuh"
 #include "gemv.cuh"
 #include "gemv_b1.cuh"
+#include "gemv_bn.cuh"
 #include "gemv_host.cuh"
 #include "gemm_tcgen05.cuh"
 

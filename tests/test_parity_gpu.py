@@ -159,7 +159,8 @@ def test_gemv_fp16(P, oracle, m):
 
 
 def test_gemv_fp32_out_is_tight(P, oracle):
-    # with fp32 output the only error left is fp32 accumulation order
+    # with fp32 output what is left is the 13-bit fixed-point form of the activations inside the int8
+    # tensor-core kernels (error <= 2^-13 of each 256-wide slice's maximum, exact for large elements)
     n, k, m = 96, 4096, 4
     w = oracle.gen_normal(5, n * k, 0.02).reshape(n, k)
     packed_np, scales_np, _ = oracle.encode(w, 32)
@@ -169,7 +170,7 @@ def test_gemv_fp32_out_is_tight(P, oracle):
     scales = torch.from_numpy(scales_np.view(np.int16)).view(torch.float16).to(DEV)
     y = P.ops.linear(torch.from_numpy(x32).bfloat16().to(DEV), packed, scales, None, n, k, 32, out_dtype=torch.float32)
     rel = np.linalg.norm(y.cpu().numpy() - y_ref) / np.linalg.norm(y_ref)
-    assert rel < 2e-5, rel      # e4m3 split of the activations: tiny elements are truncated at 2^-17 of the slice maximum
+    assert rel < 1e-4, rel
 
 
 @pytest.mark.parametrize("n,k,m,xdt", [(7, 13, 3, torch.float32), (5, 19, 2, torch.float32), (4, 48, 2, torch.float32),
@@ -228,7 +229,7 @@ def test_gemm_matches_gemv_small_batch(P, oracle):
     y1 = P.ops.linear(x, packed, scales, None, n, k, 32, out_dtype=torch.float32, force="gemv")
     y2 = P.ops.linear(x, packed, scales, None, n, k, 32, out_dtype=torch.float32, force="gemm")
     P.ops.gemm_status(torch.device(DEV))
-    assert float((y1 - y2).norm() / y1.norm()) < 1e-5
+    assert float((y1 - y2).norm() / y1.norm()) < 1e-4     # activation fixed-point error of the decode kernel
 
 
 def test_grouped_gemv_matches_single(P, oracle):
