@@ -33,6 +33,9 @@ sys.path.insert(0, ROOT)
 SHAPES = [(4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)]      # (K, N)
 BATCHES = [1, 4, 16]
 METRIC = "E8 fused dequant-GEMM: decode GB/s on packed bytes @8B shapes"
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_b1_kernel launch (K=4096, N=14336, 16 matrices) from the
+# ncu capture summarised in profiles/gemv_b1_K4096_N14336.md; the algorithmic bytes of that launch are 235.5 MB.
+TRAFFIC_PER_LAUNCH = {"bytes": 238.4e6, "algorithmic_bytes": 235.5e6, "case": "gemv_b1_kernel K=4096 N=14336 R=16 M=1"}
 
 
 def measured_peaks():
@@ -338,7 +341,8 @@ def main():
                        "parallelism": "output-column shards + NCCL all-gather" if world > 1 else "single GPU",
                        "launches_per_step": launches_per_step},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "traffic": None, "kernel": "gemv_mma_kernel", "peak_source": peak_src,
+                         "traffic": TRAFFIC_PER_LAUNCH, "kernel": "gemv_b1_kernel / gemv_bn_kernel (one grouped launch per shape and batch)",
+                         "peak_source": peak_src + " (MEASURED_PEAKS.json hbm_gbs)" if peak_src == "measured" else peak_src,
                          "note": "achieved = (packed + activation + output bytes of a pass) / time of a pass; launch gaps included"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d_per_step, "d2h_bytes_per_step": d2h_per_step,
                     "ms_per_step": e2e_ms},

@@ -191,21 +191,26 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
 
         b1_wait(bar_full + 8 * s, (uint32_t)(n / Cfg::kStages) & 1u, abort_flag, 42);
 
-        float out[4][NBLK][2];                                     // [8-row tile][block][row 2t | 2t+1]
-#pragma unroll
-        for (int tl = 0; tl < 4; ++tl)
-#pragma unroll
-            for (int blk = 0; blk < NBLK; ++blk) out[tl][blk][0] = out[tl][blk][1] = 0.f;
+        // the reduction buffer of this item must have been drained (it was last used kRed items ago)
+        b1_wait(bar_rempty + 8 * b, ((uint32_t)(n / Cfg::kRed) & 1u) ^ 1u, abort_flag, 44);
+        float* rbuf = red + (size_t)b * Cfg::kRedFloats + warp * 256 * NBLK;
 
         if (warp < cc.act) {
             const uint32_t cb = cc.act * 48, sb = cc.act * 16;
             const uint32_t stage = ring + s * kB1StageBytes;
 #pragma unroll
             for (int tl = 0; tl < 4; ++tl) {
+                float out[NBLK][2];                                // [block][weight row 2t | 2t+1] of this 8-row tile
+#pragma unroll
+                for (int blk = 0; blk < NBLK; ++blk) out[blk][0] = out[blk][1] = 0.f;
                 const uint32_t ca = stage + (tl * 8 + g) * (cb + 16) + warp * 48;
                 const uint32_t sa = stage + kB1Rows * kGemvMaxCodePitch + (tl * 8 + 2 * t) * (sb + 16) + warp * 16;
                 const uint4 q0 = lds_u128(ca), q1 = lds_u128(ca + 16), q2 = lds_u128(ca + 32);
                 const uint4 s0 = lds_u128(sa), s1 = lds_u128(sa + sb + 16);      // scales of rows 2t and 2t+1 of the tile
+                if (tl == 3) {                                     // everything of this stage is in registers now
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+                }
                 const uint32_t cw[12] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x, q2.y, q2.z, q2.w};
                 const __half2* h0 = reinterpret_cast<const __half2*>(&s0);
                 const __half2* h1 = reinterpret_cast<const __half2*>(&s1);
@@ -222,26 +227,21 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
                         int d[4] = {0, 0, 0, 0};
                         mma_s8(d, xa[blk][grp][0], xa[blk][grp][1], xa[blk][grp][2], xa[blk][grp][3], b0, b1);
                         // d[0], d[1]: high term for weight rows 2t, 2t+1;  d[2], d[3]: low term (same activation row g)
-                        out[tl][blk][0] = fmaf((float)(d[0] * 128 + d[2]), f0, out[tl][blk][0]);
-                        out[tl][blk][1] = fmaf((float)(d[1] * 128 + d[3]), f1, out[tl][blk][1]);
+                        out[blk][0] = fmaf((float)(d[0] * 128 + d[2]), f0, out[blk][0]);
+                        out[blk][1] = fmaf((float)(d[1] * 128 + d[3]), f1, out[blk][1]);
                     }
                 }
+#pragma unroll
+                for (int blk = 0; blk < NBLK; ++blk)
+                    *reinterpret_cast<float2*>(rbuf + ((blk * 4 + tl) * 32 + lane) * 2) =
+                        make_float2(out[blk][0] * upscale[blk], out[blk][1] * upscale[blk]);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
         } else {
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+#pragma unroll
+            for (int i = 0; i < 4 * NBLK; ++i) *reinterpret_cast<float2*>(rbuf + (i * 32 + lane) * 2) = make_float2(0.f, 0.f);
         }
-
-        b1_wait(bar_rempty + 8 * b, ((uint32_t)(n / Cfg::kRed) & 1u) ^ 1u, abort_flag, 44);
-        float* rbuf = red + (size_t)b * Cfg::kRedFloats + warp * 256 * NBLK;
-#pragma unroll
-        for (int blk = 0; blk < NBLK; ++blk)
-#pragma unroll
-            for (int tl = 0; tl < 4; ++tl)
-                *reinterpret_cast<float2*>(rbuf + ((blk * 4 + tl) * 32 + lane) * 2) =
-                    make_float2(out[tl][blk][0] * upscale[blk], out[tl][blk][1] * upscale[blk]);
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_rfull + 8 * b);
         if (n >= Cfg::kRedLag) reduce_next();
