@@ -102,6 +102,30 @@ int32_t ojx_e8t_gemv(const void* x, int32_t x_dtype, int64_t M,
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * ojx_e8t_gemv for callers that cannot hand over scratch memory (no counterpart in the reference).
+ * Meant for hosts where a plug-in only ever sees its input and output buffers: a serving process whose
+ * device memory is pre-carved by its own arena, a callback that runs where cudaMalloc is not allowed
+ * (it synchronises the device), a worker without allocation rights.  The fp32 partial sums that
+ * K > 4096 needs are kept in a 4 MiB array that is part of the library image on every GPU that loads
+ * it; the call allocates nothing and frees nothing.
+ *   - Same arguments and results as ojx_e8t_gemv, minus the workspace.
+ *   - Limit: ojx_e8t_gemv_workspace_bytes(M, N, K) must not exceed
+ *     ojx_e8t_gemv_static_scratch_capacity() (4 MiB; e.g. K = 14336, N = 4096, M = 16 needs 1 MiB);
+ *     larger problems return OJX_ERR_WORKSPACE and must use ojx_e8t_gemv with caller scratch.
+ *   - The first call on each device looks up the array's device address (a driver query, done once
+ *     per device with that device current); make that first call before starting a stream capture.
+ *   - All calls share the one array.  It keeps whatever the last call left; nothing needs clearing
+ *     because every element is written before it is read.  Two calls that run on the GPU at the same
+ *     time (different streams, or different threads) would overwrite each other's partial sums:
+ *     serialise them.
+ */
+size_t  ojx_e8t_gemv_static_scratch_capacity(void);
+int32_t ojx_e8t_gemv_static_scratch(const void* x, int32_t x_dtype, int64_t M,
+                                    const uint8_t* packed, const uint16_t* scales, const void* bias,
+                                    int64_t N, int64_t K, int32_t group,
+                                    void* y, int32_t y_dtype, void* stream);
+
+/*
  * Several independent decode-shape linears in ONE launch (for example q/k/v, or gate/up, or a
  * rotation of matrices in a benchmark).  `problems` is a DEVICE array of `count` descriptors;
  * `total_tiles` is the sum over problems of ojx_e8t_gemv_tiles(N, K).  All problems share M,

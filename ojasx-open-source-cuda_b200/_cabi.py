@@ -26,6 +26,7 @@ EXPORTED_SYMBOLS = (
     "ojx_e8t_gemv_workspace_bytes", "ojx_e8t_gemv", "ojx_e8t_gemv_tiles", "ojx_e8t_gemv_kchunks",
     "ojx_e8t_gemv_grouped", "ojx_e8t_gemm_workspace_bytes", "ojx_e8t_gemm", "ojx_e8t_gemm_status",
     "ojx_e8t_generate", "ojx_e8t_last_cuda_error", "ojx_e8t_device_status",
+    "ojx_e8t_gemv_static_scratch", "ojx_e8t_gemv_static_scratch_capacity",
 )
 
 NVCC_FLAGS = [
@@ -96,6 +97,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ojx_e8t_gemv_workspace_bytes.argtypes = [i64, i64, i64]
     lib.ojx_e8t_gemv.restype = i32
     lib.ojx_e8t_gemv.argtypes = [vp, i32, i64, vp, vp, vp, i64, i64, i32, vp, i32, vp, sz, vp]
+    lib.ojx_e8t_gemv_static_scratch.restype = i32
+    lib.ojx_e8t_gemv_static_scratch.argtypes = [vp, i32, i64, vp, vp, vp, i64, i64, i32, vp, i32, vp]
+    lib.ojx_e8t_gemv_static_scratch_capacity.restype = sz
+    lib.ojx_e8t_gemv_static_scratch_capacity.argtypes = []
     lib.ojx_e8t_gemv_tiles.restype = i32
     lib.ojx_e8t_gemv_tiles.argtypes = [i64, i64]
     lib.ojx_e8t_gemv_kchunks.restype = i32

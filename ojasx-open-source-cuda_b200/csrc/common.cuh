@@ -132,6 +132,9 @@ size_t  gemv_workspace_bytes_impl(int64_t M, int64_t N, int64_t K);
 int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                   const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
                   void* workspace, size_t workspace_bytes, cudaStream_t s);
+size_t  gemv_static_scratch_capacity_impl();
+int32_t gemv_static_scratch_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                                 const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s);
 int32_t gemv_tiles_impl(int64_t N, int64_t K);
 int32_t gemv_kchunks_impl(int64_t K);
 int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,

@@ -1,6 +1,8 @@
 // Host-side routing of the decode-shape entry points to the kernels in gemv.cuh / gemv_e4m3.cuh.
 #pragma once
 
+#include <mutex>
+
 #include "gemv.cuh"
 #include "gemv_b1.cuh"
 #include "gemv_bn.cuh"
@@ -111,6 +113,57 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
     if (blocks > 148 * 8) blocks = 148 * 8;
     generic_linear_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
     return launch_status();
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Decode-shape linear that brings its own scratch.
+//
+// Some hosts hand a plug-in nothing but its input and output buffers: an inference server whose
+// device memory is carved up front by its own arena, a callback running where cudaMalloc is
+// forbidden (it synchronises the whole device), a sandboxed worker without allocation rights.
+// For them the fp32 partial sums that K > 4096 needs live in this file-scope device array instead
+// of a caller buffer.  Every GPU that loads the library carries the array until the process ends.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchFloats = (size_t)1 << 20;                     // 4 MiB per GPU
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+// In host code the array's name is only a handle; the device address is asked for once per device,
+// with that device current, and cached.
+static float* static_scratch_ptr(int32_t* status) {
+    static float* cached[64] = {nullptr};
+    static std::mutex mtx;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *status = OJX_ERR_LAUNCH; return nullptr; }
+    std::lock_guard<std::mutex> lock(mtx);
+    if (cached[dev] == nullptr) {
+        float* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch);
+        if (e != cudaSuccess || p == nullptr) { last_cuda_error() = e; *status = OJX_ERR_LAUNCH; return nullptr; }
+        cached[dev] = p;
+    }
+    *status = OJX_OK;
+    return cached[dev];
+}
+
+size_t gemv_static_scratch_capacity_impl() { return kStaticScratchFloats * sizeof(float); }
+
+int32_t gemv_static_scratch_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                                 const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s) {
+    OJX_RETURN_IF(!x || !packed || !scales || !y, OJX_ERR_NULL);
+    OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0, OJX_ERR_SHAPE);
+    const size_t need = gemv_workspace_bytes_impl(M, N, K);
+    // larger problems do not fit the built-in array: the caller has to use ojx_e8t_gemv with its own scratch
+    OJX_RETURN_IF(need > kStaticScratchFloats * sizeof(float), OJX_ERR_WORKSPACE);
+    float* scratch = nullptr;
+    if (need > 0) {
+        int32_t st = OJX_OK;
+        scratch = static_scratch_ptr(&st);
+        OJX_RETURN_IF(st != OJX_OK, st);
+    }
+    // Every partial sum is written by exactly one work item before the reduce pass reads it, so the
+    // array's previous contents never matter and nothing has to be cleared.
+    return gemv_impl(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, scratch, need, s);
 }
 
 }  // namespace ojx

@@ -72,6 +72,14 @@ int32_t ojx_e8t_gemv(const void* x, int32_t x_dtype, int64_t M, const uint8_t* p
                           (cudaStream_t)stream);
 }
 
+size_t ojx_e8t_gemv_static_scratch_capacity(void) { return ojx::gemv_static_scratch_capacity_impl(); }
+
+int32_t ojx_e8t_gemv_static_scratch(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                                    const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype,
+                                    void* stream) {
+    return ojx::gemv_static_scratch_impl(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream);
+}
+
 int32_t ojx_e8t_gemv_tiles(int64_t N, int64_t K) { return ojx::gemv_tiles_impl(N, K); }
 int32_t ojx_e8t_gemv_kchunks(int64_t K) { return ojx::gemv_kchunks_impl(K); }
 
