@@ -22,10 +22,19 @@ template <int NBLK> struct BnCfg {
     static constexpr int kAhead = 2;
     static constexpr int kRed = 2;                                          // reduction buffers
     static constexpr int kRedLag = 1;
+    static constexpr int kCopies = 4;                                       // interleaved copies of the lookup table
+    static constexpr int kLutBytes = ((kNumPoints * kCopies * 4 + 1023) / 1024) * 1024;
     static constexpr int kRedFloats = kGemvWarps * 256 * NBLK;              // per buffer: 16 warps x 32 rows x 8 NBLK
-    static constexpr size_t kSmem = (size_t)kB1LutBytes + (size_t)kStages * kB1StageBytes +
+    static constexpr size_t kSmem = (size_t)kLutBytes + (size_t)kStages * kB1StageBytes +
                                     (size_t)kRed * kRedFloats * sizeof(float) + 256;
 };
+
+// m16n8k32 int8 MMA with a zero accumulator input (the zero registers cost no instructions).
+__device__ __forceinline__ void mma_s8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 
 template <int NBLK>
 __global__ void __launch_bounds__(kGemvThreads, 1)
@@ -35,9 +44,9 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
     extern __shared__ __align__(128) uint8_t smem[];
     uint32_t* lut = reinterpret_cast<uint32_t*>(smem);
-    const uint32_t ring = smem_u32(smem) + kB1LutBytes;
-    float* red = reinterpret_cast<float*>(smem + kB1LutBytes + Cfg::kStages * kB1StageBytes);
-    uint8_t* tail = smem + kB1LutBytes + Cfg::kStages * kB1StageBytes + Cfg::kRed * Cfg::kRedFloats * sizeof(float);
+    const uint32_t ring = smem_u32(smem) + Cfg::kLutBytes;
+    float* red = reinterpret_cast<float*>(smem + Cfg::kLutBytes + Cfg::kStages * kB1StageBytes);
+    uint8_t* tail = smem + Cfg::kLutBytes + Cfg::kStages * kB1StageBytes + Cfg::kRed * Cfg::kRedFloats * sizeof(float);
     const uint32_t bar_full = smem_u32(tail), bar_empty = bar_full + 8 * Cfg::kStages;
     const uint32_t bar_rfull = bar_empty + 8 * Cfg::kStages, bar_rempty = bar_rfull + 8 * Cfg::kRed;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 16 * Cfg::kStages + 16 * Cfg::kRed);
@@ -45,7 +54,7 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
-    for (int i = tid; i < kNumPoints * kB1Copies; i += kGemvThreads) lut[i] = g_trit_nibbles[i / kB1Copies];
+    for (int i = tid; i < kNumPoints * Cfg::kCopies; i += kGemvThreads) lut[i] = g_trit_nibbles[i / Cfg::kCopies];
     if (tid == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) {
             mbar_init(bar_full + 8 * s, kGemvThreads);
@@ -128,13 +137,17 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     };
 
     // ---- lane constants: this lane takes rank t of every scale group (byte window + nibble shift) ----
-    const uint32_t lut_lane = smem_u32(lut) + ((lane & (kB1Copies - 1)) << 2);
+    const uint32_t lut_lane = smem_u32(lut) + ((lane & (Cfg::kCopies - 1)) << 2);
     constexpr uint32_t kTritBytes = 0x00FF0100u;
-    constexpr uint32_t kEntryMask = 0xFFFu << 4;
+    constexpr uint32_t kEntryBytes = Cfg::kCopies * 4;                         // table stride
     const uint32_t bt = (t == 0) ? 0u : (t == 1) ? 1u : (t == 2) ? 3u : 4u;     // first byte of this lane's rank
     const uint32_t sel_even = bt | ((bt + 1) << 4);
     const uint32_t sel_odd = (bt + 2) | ((bt + 3) << 4);
-    const uint32_t lsh = (t & 1) ? 0u : 4u;                                    // rank * 16 from the 16-bit window
+    // the rank sits in bits 0-11 (even t) or 4-15 (odd t) of the 16-bit window: mask, then one multiply-add
+    // turns it into the table address (stride 16 bytes)
+    static_assert(kEntryBytes == 16, "the multiply-add below assumes a 16-byte table stride");
+    const uint32_t win_mask = (t & 1) ? 0xFFF0u : 0x0FFFu;
+    const uint32_t win_mul = (t & 1) ? 1u : 16u;
 
     uint32_t xa[NBLK][8][4];                          // A fragments: [block][group][a0 hi, a1 lo, a2 hi, a3 lo]
     float upscale[NBLK];
@@ -218,14 +231,14 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
                 for (int grp = 0; grp < 8; ++grp) {
                     const int w0 = (grp & 1) ? (3 * grp - 1) / 2 : (3 * grp) / 2;
                     const uint32_t win = prmt(cw[w0], cw[w0 + 1], (grp & 1) ? sel_odd : sel_even);
-                    const uint32_t nib = lds_u32(((win << lsh) & kEntryMask) + lut_lane);
+                    const uint32_t nib = lds_u32((win & win_mask) * win_mul + lut_lane);
                     const uint32_t b0 = prmt(kTritBytes, 0u, nib), b1 = prmt(kTritBytes, 0u, nib >> 16);
                     const float f0 = (grp & 1) ? __high2float(h0[grp >> 1]) : __low2float(h0[grp >> 1]);
                     const float f1 = (grp & 1) ? __high2float(h1[grp >> 1]) : __low2float(h1[grp >> 1]);
 #pragma unroll
                     for (int blk = 0; blk < NBLK; ++blk) {
-                        int d[4] = {0, 0, 0, 0};
-                        mma_s8(d, xa[blk][grp][0], xa[blk][grp][1], xa[blk][grp][2], xa[blk][grp][3], b0, b1);
+                        int d[4];
+                        mma_s8_zero(d, xa[blk][grp][0], xa[blk][grp][1], xa[blk][grp][2], xa[blk][grp][3], b0, b1);
                         // d[0], d[1]: high term for weight rows 2t, 2t+1;  d[2], d[3]: low term (same activation row g)
                         out[blk][0] = fmaf((float)(d[0] * 128 + d[2]), f0, out[blk][0]);
                         out[blk][1] = fmaf((float)(d[1] * 128 + d[3]), f1, out[blk][1]);
