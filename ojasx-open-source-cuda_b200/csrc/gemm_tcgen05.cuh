@@ -26,10 +26,10 @@
 // Operand types.  The weight tile must be fp16: coord * fp16 scale is exact in fp16 but not in bf16,
 // and bf16-rounded weights together with bf16 outputs exceed the 2e-3 relative-L2 contract.  On B200
 // a kind::f16 MMA whose A and B formats differ (fp16 x bf16) is rejected as an illegal instruction,
-// so bf16 activations are first rewritten as fp16 by a small pre-pass into caller-owned scratch
-// (one read-convert-write pass that also finds max|x|; a second pass runs only if rescaling is needed):
-// x * 2^-e with e chosen from the tensor's absolute maximum so nothing overflows (e = 0, i.e. an
-// exact copy, whenever |x| < 32768); the epilogue multiplies the fp32 result by 2^e.
+// so bf16 activations are first rewritten as fp16 by a small pre-pass into caller-owned scratch:
+// every token row is multiplied by its own power of two 2^-e so that its largest magnitude lands in
+// [2^14, 2^15) (exact for every element within 28 binades of the row maximum; smaller ones keep an
+// absolute error below 2^-39 of that maximum), and the epilogue multiplies the token's outputs by 2^e.
 #pragma once
 
 #include <cuda.h>
@@ -63,54 +63,82 @@ struct GemmParams {
     uint32_t idesc;
     int rows;                      // weight rows per CTA tile: 128 or 256
     int bn;                        // tokens per CTA tile (MMA N): 128 or 256
-    const uint32_t* amax_bits;     // fp32 bit pattern of max|x| when activations were rescaled, else null
+    const float* up;               // per-token output factors 2^e written by the pre-pass (null: 1)
 };
 
-// Power-of-two exponent e >= 0 with max|x| * 2^-e < 2^15.
-__device__ __forceinline__ int prescale_exponent(uint32_t amax_bits) {
-    const int ex = (int)((amax_bits >> 23) & 0xFFu) - 127;
-    return ex > 14 ? ex - 14 : 0;
-}
-
-// Pass 1 (always): fp16 copy of the bf16 activations assuming no rescaling is needed, plus the tensor's
-// absolute maximum.  Pass 2 does the rescaled copy only when the maximum turned out to be >= 32768.
-__global__ void __launch_bounds__(256) convert_bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                   __half* __restrict__ out, int64_t count,
-                                                                   uint32_t* __restrict__ amax_bits) {
+// Activation pre-pass: a group of TPR threads (a warp for rows of up to 4096 elements, else the whole CTA)
+// takes one token row, finds its largest magnitude, then writes the row as fp16 scaled by the power of two
+// that brings that magnitude into [2^14, 2^15), and the inverse factor for the epilogue.  Rows of up to
+// TPR * 8 * VECS elements stay in registers between the two steps (one global read); longer rows are read
+// twice.  The first thread also clears the status word the GEMM kernel reports through.
+template <int TPR, int VECS>
+__global__ void __launch_bounds__(256) normalize_rows_bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                          __half* __restrict__ out, float* __restrict__ up,
+                                                                          int64_t M, int64_t K, int32_t* __restrict__ status) {
+    __shared__ uint32_t warp_max[8];
+    constexpr int kRowsPerCta = 256 / TPR;
+    const int t = threadIdx.x % TPR;
+    const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + threadIdx.x / TPR;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && status != nullptr) *status = 0;
+    const bool live = row < M;                                            // whole warps share `live`
+    const uint4* src = reinterpret_cast<const uint4*>(x + (live ? row : 0) * K);   // K % 256 == 0: rows are 16-byte aligned
+    uint4* dst = reinterpret_cast<uint4*>(out + (live ? row : 0) * K);
+    const int64_t vecs = live ? K / 8 : 0;
+    const bool resident = vecs <= (int64_t)TPR * VECS;
+    uint4 keep[VECS];
     uint32_t m = 0;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i * 8 < count; i += (int64_t)gridDim.x * blockDim.x) {
-        if (i * 8 + 8 <= count) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(x) + i);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            uint32_t o[4];
+    if (resident) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                m = max(m, (w[j] << 16) & 0x7FFFFFFFu);
-                m = max(m, w[j] & 0x7FFF0000u);
-                const __half2 h = __floats2half2_rn(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xFFFF0000u));
-                o[j] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-            reinterpret_cast<uint4*>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
-        } else {
-            for (int64_t j = i * 8; j < count; ++j) {
-                m = max(m, ((uint32_t)__bfloat16_as_ushort(x[j]) << 16) & 0x7FFFFFFFu);
-                out[j] = __float2half_rn(__bfloat162float(x[j]));
-            }
+        for (int j = 0; j < VECS; ++j) {
+            const int64_t i = t + TPR * j;
+            keep[j] = i < vecs ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < VECS; ++j) {
+            const uint32_t w[4] = {keep[j].x, keep[j].y, keep[j].z, keep[j].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) m = max(m, max((w[q] << 16) & 0x7FFFFFFFu, w[q] & 0x7FFF0000u));
+        }
+    } else {
+        for (int64_t i = t; i < vecs; i += TPR) {
+            const uint4 v = __ldg(src + i);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) m = max(m, max((w[q] << 16) & 0x7FFFFFFFu, w[q] & 0x7FFF0000u));
         }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(amax_bits, m);      // positive floats order like integers
-}
-
-__global__ void __launch_bounds__(256) rescale_bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                   __half* __restrict__ out, int64_t count,
-                                                                   const uint32_t* __restrict__ amax_bits) {
-    const int e = prescale_exponent(*amax_bits);
-    if (e == 0) return;                                                   // pass 1 was already exact
+    if (TPR > 32) {
+        if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+        __syncthreads();
+#pragma unroll
+        for (int w = 0; w < 8; ++w) m = max(m, warp_max[w]);
+    }
+    int e = 0;
+    const int ex = (int)((m >> 23) & 0xFFu);
+    if (ex != 0 && ex != 0xFF) e = max(-100, min(100, ex - 127 - 14));
     const float down = __int_as_float((127 - e) << 23);
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x)
-        out[i] = __float2half_rn(__bfloat162float(x[i]) * down);
+    if (t == 0 && live) up[row] = __int_as_float((127 + e) << 23);
+    auto convert = [&](const uint4& v) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const __half2 h = __floats2half2_rn(__uint_as_float(w[q] << 16) * down, __uint_as_float(w[q] & 0xFFFF0000u) * down);
+            o[q] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        return make_uint4(o[0], o[1], o[2], o[3]);
+    };
+    if (resident) {
+#pragma unroll
+        for (int j = 0; j < VECS; ++j) {
+            const int64_t i = t + TPR * j;
+            if (i < vecs) dst[i] = convert(keep[j]);
+        }
+    } else {
+        for (int64_t i = t; i < vecs; i += TPR) dst[i] = convert(__ldg(src + i));
+    }
 }
 
 // ---- PTX wrappers (mbarrier helpers live in common.cuh) ------------------------------------------
@@ -166,6 +194,69 @@ __device__ __forceinline__ uint4 decode_chunk_f16(uint2 hb, uint32_t scale2) {
         o[i] = *reinterpret_cast<uint32_t*>(&v);
     }
     return out;
+}
+
+// Thirty-two consecutive tokens of one weight row: scale by the token's power of two (lane i of `up_lane`
+// holds the factor of token m0 + i), add bias, cast, store.  Lanes = consecutive weight rows, so every store
+// instruction writes one contiguous run of y.
+template <typename T>
+__device__ __forceinline__ void gemm_store32(T* __restrict__ y, int64_t N, int n, int m0, int M, const uint32_t (&v)[32],
+                                             float up_lane, float bias, bool live) {
+    float f[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = __shfl_sync(0xFFFFFFFFu, up_lane, i);     // all lanes, before any divergence
+    if (!live) return;
+    T* dst = y + (int64_t)m0 * N + n;
+    if (m0 + 32 <= M) {                                                            // straight-line: the stores pipeline
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dst[(int64_t)i * N] = static_cast<T>(fmaf(__uint_as_float(v[i]), f[i], bias));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (m0 + i < M) dst[(int64_t)i * N] = static_cast<T>(fmaf(__uint_as_float(v[i]), f[i], bias));
+    }
+}
+
+// One epilogue warp's share of a finished tile: TMEM lanes 32 * warp .. of both row blocks, all token columns.
+// Kept out of line so that its registers are allocated independently of the decoders' inner loop.
+__device__ __noinline__ void gemm_drain_tile(void* __restrict__ y, int y_dtype, const void* __restrict__ bias_ptr, int bias_dtype,
+                                             const float* __restrict__ up, int M, int N, int rows, int bn,
+                                             uint32_t tmem_base, int warp, int lane, int n_blk, int m_blk) {
+    const int blocks = bn / 32;
+    for (int h = 0; h < rows / kGemmHalf; ++h) {
+        const int n = n_blk * rows + h * kGemmHalf + warp * 32 + lane;
+        const bool live = n < N;
+        float bias = 0.f;
+        if (bias_ptr != nullptr && live) bias = load_any(bias_ptr, bias_dtype, n);
+        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + h * kGemmBN;
+        // Token factors (lane l keeps the factor of token m0 + l) and accumulator blocks both travel one
+        // 32-token block ahead of their use, so neither the global nor the TMEM load latency is exposed.
+        auto load_up = [&](int cb) {
+            const int m = m_blk * bn + cb * 32 + lane;
+            return (up != nullptr && cb < blocks && m < M) ? __ldg(up + m) : 1.0f;
+        };
+        auto store = [&](int cb, const uint32_t (&v)[32], float up_lane) {
+            const int m0 = m_blk * bn + cb * 32;
+            if (m0 >= M) return;                                   // warp-uniform
+            if (y_dtype == OJX_BF16) gemm_store32(static_cast<__nv_bfloat16*>(y), N, n, m0, M, v, up_lane, bias, live);
+            else if (y_dtype == OJX_F16) gemm_store32(static_cast<__half*>(y), N, n, m0, M, v, up_lane, bias, live);
+            else gemm_store32(static_cast<float*>(y), N, n, m0, M, v, up_lane, bias, live);
+        };
+        uint32_t va[32], vb[32];
+        float ua = load_up(0), ub;
+        tmem_ld_32x32b_x32(taddr, va);
+#pragma unroll 1
+        for (int cb = 0; cb < blocks; cb += 2) {                   // blocks is 4 or 8
+            tmem_ld_wait();
+            tmem_ld_32x32b_x32(taddr + (cb + 1) * 32, vb);
+            ub = load_up(cb + 1);
+            store(cb, va, ua);
+            tmem_ld_wait();
+            if (cb + 2 < blocks) tmem_ld_32x32b_x32(taddr + (cb + 2) * 32, va);
+            ua = load_up(cb + 2);
+            store(cb + 1, vb, ub);
+        }
+    }
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -340,26 +431,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
             ok = __all_sync(0xFFFFFFFFu, ok);          // warp-uniform decision before the aligned TMEM loads
             if (!ok) break;
             tc_fence_after();
-            const float up = p.amax_bits != nullptr ? __int_as_float((127 + prescale_exponent(*p.amax_bits)) << 23) : 1.0f;
-#pragma unroll 1
-            for (int h = 0; h < p.rows / kGemmHalf; ++h) {
-                const int n = n_blk * p.rows + h * kGemmHalf + warp * 32 + lane;
-                float bias = 0.f;
-                if (p.bias != nullptr && n < p.N) bias = load_any(p.bias, p.bias_dtype, n);
-                const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + h * kGemmBN;
-#pragma unroll 1
-                for (int cb = 0; cb < p.bn / 32; ++cb) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(taddr + cb * 32, v);
-                    tmem_ld_wait();
-                    const int m0 = m_blk * p.bn + cb * 32;
-                    if (n < p.N) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (m0 + i < p.M) store_any(p.y, p.y_dtype, (int64_t)(m0 + i) * p.N + n, fmaf(__uint_as_float(v[i]), up, bias));
-                    }
-                }
-            }
+            gemm_drain_tile(p.y, p.y_dtype, p.bias, p.bias_dtype, p.up, p.M, p.N, p.rows, p.bn, tmem_base, warp, lane, n_blk, m_blk);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(0));
@@ -397,12 +469,13 @@ inline bool gemm_fast_ok(int64_t M, int64_t N, int64_t K, int group, int x_dtype
            (x_dtype == OJX_BF16 || x_dtype == OJX_F16) && M < (1 << 30) && N < (1 << 30) && K < (1 << 30);
 }
 
-// Scratch: a 256-byte status block (word 0: give-up code of a bounded wait, word 1: bit pattern of
-// max|x|; zeroed by every call) followed by room for an fp16 copy of the activations.
+// Scratch: a 256-byte status block (word 0: give-up code of a bounded wait; zeroed by every call), the
+// per-token output factors (M floats, padded to 256 bytes), then room for an fp16 copy of the activations.
+inline size_t gemm_up_bytes(int64_t M) { return (((size_t)M * 4) + 255) & ~(size_t)255; }
 size_t gemm_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
     (void)N;
     if (M <= 0 || K <= 0) return 256;
-    return 256 + (size_t)M * (size_t)K * 2;
+    return 256 + gemm_up_bytes(M) + (size_t)M * (size_t)K * 2;
 }
 
 int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
@@ -443,8 +516,8 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
     }
     const cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)bn};
     const cuuint32_t estr[2] = {1, 1};
-    uint32_t* status_words = static_cast<uint32_t*>(workspace);
-    void* x_f16 = convert ? static_cast<void*>(static_cast<uint8_t*>(workspace) + 256) : const_cast<void*>(x);
+    float* up = convert ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256) : nullptr;
+    void* x_f16 = convert ? static_cast<void*>(static_cast<uint8_t*>(workspace) + 256 + gemm_up_bytes(M)) : const_cast<void*>(x);
     if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x_f16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -456,16 +529,16 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
             return OJX_ERR_LAUNCH;
         configured = true;
     }
-    if (cudaMemsetAsync(workspace, 0, 256, s) != cudaSuccess) return OJX_ERR_LAUNCH;
     if (convert) {
-        const int64_t count = M * K;
-        int64_t blocks = (count / 8 + 255) / 256 + 1;
-        if (blocks > 148 * 8) blocks = 148 * 8;
-        convert_bf16_to_f16_kernel<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
-                                                                    static_cast<__half*>(x_f16), count, status_words + 1);
-        rescale_bf16_to_f16_kernel<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
-                                                                    static_cast<__half*>(x_f16), count, status_words + 1);
+        if (K <= 4096)
+            normalize_rows_bf16_to_f16_kernel<32, 16><<<(unsigned)((M + 7) / 8), 256, 0, s>>>(
+                static_cast<const __nv_bfloat16*>(x), static_cast<__half*>(x_f16), up, M, K, static_cast<int32_t*>(workspace));
+        else
+            normalize_rows_bf16_to_f16_kernel<256, 8><<<(unsigned)M, 256, 0, s>>>(
+                static_cast<const __nv_bfloat16*>(x), static_cast<__half*>(x_f16), up, M, K, static_cast<int32_t*>(workspace));
         if (cudaGetLastError() != cudaSuccess) return OJX_ERR_LAUNCH;
+    } else if (cudaMemsetAsync(workspace, 0, 4, s) != cudaSuccess) {
+        return OJX_ERR_LAUNCH;
     }
 
     GemmParams prm;
@@ -473,7 +546,7 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
     prm.status = static_cast<int32_t*>(workspace);
     prm.M = (int)M; prm.N = (int)N; prm.K = (int)K;
     prm.y_dtype = y_dtype; prm.bias_dtype = x_dtype;
-    prm.amax_bits = convert ? status_words + 1 : nullptr;
+    prm.up = up;
     // instruction descriptor: fp32 accumulate (bits 4-5 = 1), A and B both fp16 (format 0), both K-major,
     // N >> 3 at bits 17-22, M >> 4 at bits 24-28
     prm.rows = rows; prm.bn = bn;
