@@ -34,8 +34,8 @@ SHAPES = [(4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)]      # (K, N
 BATCHES = [1, 4, 16]
 METRIC = "E8 fused dequant-GEMM: decode GB/s on packed bytes @8B shapes"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_b1_kernel launch (K=4096, N=14336, 16 matrices) from the
-# ncu capture summarised in profiles/gemv_b1_K4096_N14336.md; the algorithmic bytes of that launch are 235.5 MB.
-TRAFFIC_PER_LAUNCH = {"bytes": 238.4e6, "algorithmic_bytes": 235.5e6, "case": "gemv_b1_kernel K=4096 N=14336 R=16 M=1"}
+# ncu capture summarised in profiles/gemv_b1_kernel_K4096_N14336_R16_M1.md; the launch's algorithmic bytes are 235.5 MB.
+TRAFFIC_PER_LAUNCH = {"bytes": 240.1e6, "algorithmic_bytes": 235.5e6, "case": "gemv_b1_kernel K=4096 N=14336 R=16 M=1"}
 
 
 def measured_peaks():
