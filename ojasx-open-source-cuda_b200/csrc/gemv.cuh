@@ -95,9 +95,20 @@ __device__ __forceinline__ void cursor_load_problem(Cursor& c, const ojx_e8t_gem
     c.tiles = gemv_row_tiles(c.N);
     c.kchunks = (c.K / 256) / c.act;
 }
-__device__ __forceinline__ void cursor_seek(Cursor& c, const ojx_e8t_gemv_problem* probs, int count, int item) {
-    int p = 0;
-    while (p + 1 < count && 2 * probs[p + 1].tile_begin <= item) ++p;      // tile_begin counts 32-row tiles
+// Index of the problem that owns work item `item` (tile_begin ascends): the whole CTA counts the entries that
+// start at or before it, one coalesced pass over the table instead of a chain of dependent loads (a 64-entry
+// table walked entry by entry cost the last CTAs ~40 us at the start of every grouped launch).  Every thread of
+// the CTA must call this.
+__device__ __forceinline__ int find_problem(const ojx_e8t_gemv_problem* probs, int count, int item, int scale) {
+    int found = 0;
+    for (int base = 0; base < count; base += (int)blockDim.x) {
+        const int t = base + (int)threadIdx.x;
+        found += __syncthreads_count(t < count && scale * probs[t].tile_begin <= item);
+    }
+    return max(found - 1, 0);
+}
+
+__device__ __forceinline__ void cursor_seek(Cursor& c, const ojx_e8t_gemv_problem* probs, int p, int item) {
     c.prob = p;
     cursor_load_problem(c, probs);
     const int local = item - 2 * probs[p].tile_begin;
@@ -256,6 +267,7 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     const int i1 = (int)min((int64_t)total_items, per * (blockIdx.x + 1));
     if (i0 >= i1) return;
     const int nitems = i1 - i0;
+    const int p0 = find_problem(probs, count, i0, 2);        // tile_begin counts 32-row tiles, items are 16-row halves
 
     // Bounded wait; once any wait has given up, later waits return at once and the loop runs on (on stale
     // data) so that every barrier keeps its arrival count.  The failure is reported in g_device_status.
@@ -265,7 +277,7 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
 
     // ---- issue: every thread copies its chunks of item n into ring stage n mod S ----
     Cursor ic;                                  // cursor of the next item to be issued
-    cursor_seek(ic, probs, count, i0);
+    cursor_seek(ic, probs, p0, i0);
     int issued = 0;
     ItemLoader loader;
     loader.ring = ring; loader.bar_full = bar_full; loader.bar_empty = bar_empty; loader.tid = tid; loader.prob = -1;
@@ -278,7 +290,7 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
 
     // ---- reduction of item n (done by warp n mod 16, kGemvRedLag items late) ----
     Cursor rc;                                  // cursor of the next item to be summed
-    cursor_seek(rc, probs, count, i0);
+    cursor_seek(rc, probs, p0, i0);
     int reduced = 0;
     auto reduce_next = [&]() {
         const int n = reduced, b = n % kGemvRed;
@@ -330,7 +342,7 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     uint32_t xf[NB][8][4];
     int cur_prob = -1, cur_chunk = -1;
     Cursor cc;
-    cursor_seek(cc, probs, count, i0);
+    cursor_seek(cc, probs, p0, i0);
     for (int n = 0; n < nitems; ++n) {
         const int s = n % kGemvStages, b = n % kGemvRed;
         if (issued < nitems) issue_next();                       // keeps kGemvAhead items in flight

@@ -72,9 +72,7 @@ __device__ __forceinline__ void b1_load_problem(B1Cursor& c, const ojx_e8t_gemv_
     c.tiles = b1_row_tiles(c.N);
     c.kchunks = (c.K / 256) / c.act;
 }
-__device__ __forceinline__ void b1_seek(B1Cursor& c, const ojx_e8t_gemv_problem* probs, int count, int item) {
-    int p = 0;
-    while (p + 1 < count && probs[p + 1].tile_begin <= item) ++p;
+__device__ __forceinline__ void b1_seek(B1Cursor& c, const ojx_e8t_gemv_problem* probs, int p, int item) {
     c.prob = p;
     b1_load_problem(c, probs);
     const int local = item - probs[p].tile_begin;
@@ -110,7 +108,6 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
-    for (int i = tid; i < kNumPoints * kB1Copies; i += kGemvThreads) lut[i] = g_trit_nibbles[i / kB1Copies];
     if (tid == 0) {
         for (int s = 0; s < kB1Stages; ++s) {
             mbar_init(bar_full + 8 * s, kGemvThreads);      // every thread's cp.async arrive
@@ -130,11 +127,12 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const int i1 = (int)min((int64_t)total_items, per * (blockIdx.x + 1));
     if (i0 >= i1) return;
     const int nitems = i1 - i0;
+    const int p0 = find_problem(probs, count, i0, 1);
 
     // ---- loader: thread (lr, ls) copies chunks ls, ls+16, ls+32 of row lr's codes and chunk ls of its scales ----
     const int lr = tid >> 4, ls = tid & 15;
     B1Cursor ic;
-    b1_seek(ic, probs, count, i0);
+    b1_seek(ic, probs, p0, i0);
     int issued = 0;
     auto issue_next = [&]() {
         const int n = issued, s = n % kB1Stages;
@@ -160,9 +158,18 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     };
     for (int n = 0; n < kB1Ahead && n < nitems; ++n) issue_next();
 
+    // The lookup table is built while the first items are in flight: one global read per rank, stored as its
+    // kB1Copies interleaved copies with a single 16-byte store.
+    static_assert(kB1Copies == 4, "one uint4 per table entry");
+    for (int e = tid; e < kNumPoints; e += kGemvThreads) {
+        const uint32_t v = g_trit_nibbles[e];
+        reinterpret_cast<uint4*>(lut)[e] = make_uint4(v, v, v, v);
+    }
+    __syncthreads();
+
     // ---- reduction of item n by warp n mod 16, kB1RedLag items after it was computed ----
     B1Cursor rc;
-    b1_seek(rc, probs, count, i0);
+    b1_seek(rc, probs, p0, i0);
     int reduced = 0;
     auto reduce_next = [&]() {
         const int n = reduced, b = n % kB1Red;
@@ -197,7 +204,7 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     float upscale = 1.f;                              // 2^e of this warp's slice
     int cur_prob = -1, cur_chunk = -1;
     B1Cursor cc;
-    b1_seek(cc, probs, count, i0);
+    b1_seek(cc, probs, p0, i0);
 
     for (int n = 0; n < nitems; ++n) {
         const int s = n % kB1Stages, b = n % kB1Red;

@@ -54,7 +54,6 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
-    for (int i = tid; i < kNumPoints * Cfg::kCopies; i += kGemvThreads) lut[i] = g_trit_nibbles[i / Cfg::kCopies];
     if (tid == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) {
             mbar_init(bar_full + 8 * s, kGemvThreads);
@@ -74,11 +73,12 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const int i1 = (int)min((int64_t)total_items, per * (blockIdx.x + 1));
     if (i0 >= i1) return;
     const int nitems = i1 - i0;
+    const int p0 = find_problem(probs, count, i0, 1);
 
     // ---- loader (identical to the single-row kernel) ----
     const int lr = tid >> 4, ls = tid & 15;
     B1Cursor ic;
-    b1_seek(ic, probs, count, i0);
+    b1_seek(ic, probs, p0, i0);
     int issued = 0;
     auto issue_next = [&]() {
         const int n = issued, s = n % Cfg::kStages;
@@ -104,9 +104,18 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     };
     for (int n = 0; n < Cfg::kAhead && n < nitems; ++n) issue_next();
 
+    // The lookup table is built while the first items are in flight: one global read per rank, stored as its
+    // interleaved copies with a single 16-byte store.
+    static_assert(Cfg::kCopies == 4, "one uint4 per table entry");
+    for (int e = tid; e < kNumPoints; e += kGemvThreads) {
+        const uint32_t v = g_trit_nibbles[e];
+        reinterpret_cast<uint4*>(lut)[e] = make_uint4(v, v, v, v);
+    }
+    __syncthreads();
+
     // ---- reduction: every warp sums 16 * NBLK of the item's 256 * NBLK outputs over the 16 warps, in warp order ----
     B1Cursor rc;
-    b1_seek(rc, probs, count, i0);
+    b1_seek(rc, probs, p0, i0);
     int reduced = 0;
     auto reduce_next = [&]() {
         const int n = reduced, b = n % Cfg::kRed;
@@ -153,7 +162,7 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     float upscale[NBLK];
     int cur_prob = -1, cur_chunk = -1;
     B1Cursor cc;
-    b1_seek(cc, probs, count, i0);
+    b1_seek(cc, probs, p0, i0);
 
     for (int n = 0; n < nitems; ++n) {
         const int s = n % Cfg::kStages, b = n % Cfg::kRed;
