@@ -75,6 +75,9 @@ template <bool kBf16> __device__ __forceinline__ float load_act(const void* p, i
     return __half2float(static_cast<const __half*>(p)[idx]);
 }
 
+__device__ __forceinline__ void sts_u128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 __device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));

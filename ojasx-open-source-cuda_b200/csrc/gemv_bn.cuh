@@ -36,7 +36,25 @@ __device__ __forceinline__ void mma_s8_zero(int (&d)[4], uint32_t a0, uint32_t a
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-template <int NBLK>
+// fp16 MMA with fp32 accumulation: D (16 x 8) += A (16 x 16, row-major) * B (16 x 8, column-major).
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// kF16 (9-16 activation rows): the weights enter the MMA as EXACT fp16 values coord * scale, built by byte
+// permutes from a {0, +scale, -scale} byte pool with selectors fetched from a 64-bit table, and the activations
+// as fp16 (x * 2^-e per row and slice, exact for bf16 inputs), sixteen rows per mma.sync.m16n8k16 with fp32
+// accumulation across all eight groups of the slice - so no per-group integer combine, convert and scale
+// multiply remain, which is what the int8 form spends most of its instructions on at 16 rows.
+template <int NBLK, bool kF16>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_constant__ ojx_e8t_gemv_problem single,
                int count, int total_items, int M, int y_dtype) {
@@ -53,6 +71,8 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    constexpr uint32_t kItemDescOffset = kB1Rows * kGemvMaxCodePitch - 16;      // free: row pitches end in 16 bytes of padding
+    const uint32_t red_desc = smem_u32(tail) + 128;                              // one 16-byte item descriptor per reduction buffer
 
     if (tid == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) {
@@ -98,6 +118,10 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
                 cp_async16(stage + kB1Rows * kGemvMaxCodePitch + lr * (sb + 16) + ls * 16,
                            reinterpret_cast<const uint8_t*>(P.scales) + (int64_t)row * (ic.K / 16) + (int64_t)ic.chunk * sb + ls * 16);
         }
+        // The item's coordinates travel with its data (in the padding behind the last row's codes), so that
+        // only the loader keeps a cursor in registers.
+        if (tid == 0)
+            sts_u128(ring + s * kB1StageBytes + kItemDescOffset, make_uint4((uint32_t)ic.prob, (uint32_t)ic.chunk, (uint32_t)ic.tile, (uint32_t)ic.act));
         cp_async_arrive(bar_full + 8 * s);
         ++issued;
         b1_next(ic, probs, count);
@@ -109,44 +133,57 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     static_assert(Cfg::kCopies == 4, "one uint4 per table entry");
     for (int e = tid; e < kNumPoints; e += kGemvThreads) {
         const uint32_t v = g_trit_nibbles[e];
-        reinterpret_cast<uint4*>(lut)[e] = make_uint4(v, v, v, v);
+        if constexpr (!kF16) {
+            reinterpret_cast<uint4*>(lut)[e] = make_uint4(v, v, v, v);
+        } else {
+            // two copies of a 64-bit entry: four 16-bit permute selectors, one per pair of coordinates; a
+            // coordinate code c (0: zero, 1: plus, 2: minus) selects low byte c of the first pool word and high
+            // byte c of the second (index 4 + c)
+            uint32_t sel[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t ca = (v >> (8 * j)) & 0xFu, cb = (v >> (8 * j + 4)) & 0xFu;
+                sel[j] = ca | ((ca + 4) << 4) | (cb << 8) | ((cb + 4) << 12);
+            }
+            const uint32_t w0 = sel[0] | (sel[1] << 16), w1 = sel[2] | (sel[3] << 16);
+            reinterpret_cast<uint4*>(lut)[e] = make_uint4(w0, w1, w0, w1);
+        }
     }
     __syncthreads();
 
     // ---- reduction: every warp sums 16 * NBLK of the item's 256 * NBLK outputs over the 16 warps, in warp order ----
-    B1Cursor rc;
-    b1_seek(rc, probs, p0, i0);
     int reduced = 0;
     auto reduce_next = [&]() {
         const int n = reduced, b = n % Cfg::kRed;
         b1_wait(bar_rfull + 8 * b, (uint32_t)(n / Cfg::kRed) & 1u, abort_flag, 43);
         const float* rbuf = red + (size_t)b * Cfg::kRedFloats;
         if (lane < 16 * NBLK) {
+            const uint4 desc = lds_u128(red_desc + 16 * b);          // {problem, K chunk, 32-row tile, -} of item n
+            const ojx_e8t_gemv_problem& P = probs[desc.x];
+            const int rN = P.N, rchunk = (int)desc.y, rtile = (int)desc.z;
             const int o = warp * 16 * NBLK + lane;                 // output slot inside a warp's 256*NBLK block
             float sum = 0.f;
 #pragma unroll
             for (int w = 0; w < kGemvWarps; ++w) sum += rbuf[w * 256 * NBLK + o];
             // slot layout: ((blk * 4 + tile8) * 32 + lane') * 2 + j   with lane' = (batch g', rank lane t')
             const int j = o & 1, lp = (o >> 1) & 31, tile8 = (o >> 6) & 3, blk = o >> 8;
-            const int row = rc.tile * kB1Rows + tile8 * 8 + ((lp & 3) << 1) + j;
+            const int row = rtile * kB1Rows + tile8 * 8 + ((lp & 3) << 1) + j;
             const int col = blk * 8 + (lp >> 2);
-            if (row < rc.N && col < M) {
-                const ojx_e8t_gemv_problem& P = probs[rc.prob];
-                if (P.partial != nullptr) P.partial[((int64_t)rc.chunk * M + col) * rc.N + row] = sum;
+            if (row < rN && col < M) {
+                if (P.partial != nullptr) P.partial[((int64_t)rchunk * M + col) * rN + row] = sum;
                 else {
                     if (P.bias != nullptr) sum += __bfloat162float(static_cast<const __nv_bfloat16*>(P.bias)[row]);
-                    store_any(P.y, y_dtype, (int64_t)col * rc.N + row, sum);
+                    store_any(P.y, y_dtype, (int64_t)col * rN + row, sum);
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_rempty + 8 * b);
         ++reduced;
-        b1_next(rc, probs, count);
     };
 
     // ---- lane constants: this lane takes rank t of every scale group (byte window + nibble shift) ----
-    const uint32_t lut_lane = smem_u32(lut) + ((lane & (Cfg::kCopies - 1)) << 2);
+    const uint32_t lut_lane = smem_u32(lut) + (kF16 ? ((lane & 1) << 3) : ((lane & (Cfg::kCopies - 1)) << 2));
     constexpr uint32_t kTritBytes = 0x00FF0100u;
     constexpr uint32_t kEntryBytes = Cfg::kCopies * 4;                         // table stride
     const uint32_t bt = (t == 0) ? 0u : (t == 1) ? 1u : (t == 2) ? 3u : 4u;     // first byte of this lane's rank
@@ -158,21 +195,67 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const uint32_t win_mask = (t & 1) ? 0xFFF0u : 0x0FFFu;
     const uint32_t win_mul = (t & 1) ? 1u : 16u;
 
-    uint32_t xa[NBLK][8][4];                          // A fragments: [block][group][a0 hi, a1 lo, a2 hi, a3 lo]
+    // A fragments.  int8 form: [block][group][a0 hi, a1 lo, a2 hi, a3 lo].  fp16 form (flattened as
+    // [k half j = index 0][group][a0, a1, a2, a3]): rows g and g + 8 of the sixteen activation rows.
+    uint32_t xa[NBLK][8][4];
     float upscale[NBLK];
     int cur_prob = -1, cur_chunk = -1;
-    B1Cursor cc;
-    b1_seek(cc, probs, p0, i0);
+    struct { int prob, chunk, tile, act, K; } cc;
+    cc.K = 0;
 
     for (int n = 0; n < nitems; ++n) {
         const int s = n % Cfg::kStages, b = n % Cfg::kRed;
         if (issued < nitems) issue_next();
 
+        b1_wait(bar_full + 8 * s, (uint32_t)(n / Cfg::kStages) & 1u, abort_flag, 42);
+        {
+            const uint4 desc = lds_u128(ring + s * kB1StageBytes + kItemDescOffset);
+            cc.prob = (int)desc.x; cc.chunk = (int)desc.y; cc.tile = (int)desc.z; cc.act = (int)desc.w;
+        }
         if (cc.prob != cur_prob || cc.chunk != cur_chunk) {
+            if (cc.prob != cur_prob) cc.K = probs[cc.prob].K;
             cur_prob = cc.prob;
             cur_chunk = cc.chunk;
             const uint16_t* xp = static_cast<const uint16_t*>(probs[cc.prob].x);
             const int slice = cc.chunk * cc.act + warp;
+            if constexpr (kF16) {
+                static_assert(!kF16 || NBLK == 2, "the fp16 form holds sixteen activation rows");
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {             // activation rows g and g + 8
+                    const int m = hrow * 8 + g;
+                    const bool on = warp < cc.act && m < M;
+                    uint4 q[8];
+                    uint32_t amax = 0;
+#pragma unroll
+                    for (int grp = 0; grp < 8; ++grp) {
+                        q[grp] = make_uint4(0, 0, 0, 0);
+                        if (on) q[grp] = __ldg(reinterpret_cast<const uint4*>(xp + (int64_t)m * cc.K + slice * 256 + grp * 32 + t * 8));
+                        const uint32_t w[4] = {q[grp].x, q[grp].y, q[grp].z, q[grp].w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) amax = max(amax, max((w[i] << 16) & 0x7FFFFFFFu, w[i] & 0x7FFF0000u));
+                    }
+                    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+                    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));  // the four lanes of activation row m
+                    int e = 0;
+                    const int ex = (int)((amax >> 23) & 0xFFu);
+                    if (ex != 0 && ex != 0xFF) e = max(-100, min(100, ex - 127 - 14));   // row maximum -> [2^14, 2^15)
+                    const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+                    upscale[hrow] = __uint_as_float((uint32_t)(127 + e) << 23);
+#pragma unroll
+                    for (int grp = 0; grp < 8; ++grp) {
+                        const uint32_t w[4] = {q[grp].x, q[grp].y, q[grp].z, q[grp].w};
+                        uint32_t h[4];                             // this lane's eight k of the group as four fp16 pairs
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const __half2 v = __floats2half2_rn(__uint_as_float(w[i] << 16) * down, __uint_as_float(w[i] & 0xFFFF0000u) * down);
+                            h[i] = *reinterpret_cast<const uint32_t*>(&v);
+                        }
+                        // k half 0 multiplies coordinates 0-3 of the lane's rank, k half 1 coordinates 4-7
+                        xa[0][grp][hrow] = h[0]; xa[0][grp][2 + hrow] = h[1];
+                        xa[1][grp][hrow] = h[2]; xa[1][grp][2 + hrow] = h[3];
+                    }
+                }
+            } else {
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk) {
                 const int m = blk * 8 + g;
@@ -209,9 +292,8 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
                     xa[blk][grp][0] = hw[0]; xa[blk][grp][1] = lw[0]; xa[blk][grp][2] = hw[1]; xa[blk][grp][3] = lw[1];
                 }
             }
+            }
         }
-
-        b1_wait(bar_full + 8 * s, (uint32_t)(n / Cfg::kStages) & 1u, abort_flag, 42);
 
         // the reduction buffer of this item must have been drained (it was last used kRed items ago)
         b1_wait(bar_rempty + 8 * b, ((uint32_t)(n / Cfg::kRed) & 1u) ^ 1u, abort_flag, 44);
@@ -220,6 +302,49 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
         if (warp < cc.act) {
             const uint32_t cb = cc.act * 48, sb = cc.act * 16;
             const uint32_t stage = ring + s * kB1StageBytes;
+            if constexpr (kF16) {
+#pragma unroll
+                for (int tl = 0; tl < 4; ++tl) {
+                    // [activation row g | g + 8][weight row 2t | 2t + 1]; kChains independent accumulation chains
+                    // keep the MMA pipe from waiting on its own latency
+                    constexpr int kChains = 1;
+                    float acc[kChains][4];
+#pragma unroll
+                    for (int c = 0; c < kChains; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+                    const uint32_t ca = stage + (tl * 8 + g) * (cb + 16) + warp * 48;
+                    const uint32_t sa = stage + kB1Rows * kGemvMaxCodePitch + (tl * 8 + g) * (sb + 16) + warp * 16;
+                    const uint4 q0 = lds_u128(ca), q1 = lds_u128(ca + 16), q2 = lds_u128(ca + 32);
+                    const uint4 s0 = lds_u128(sa);                     // the eight group scales of weight row g of the tile
+                    if (tl == 3) {                                     // everything of this stage is in registers now
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+                    }
+                    const uint32_t cw[12] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x, q2.y, q2.z, q2.w};
+                    const uint32_t sw[4] = {s0.x, s0.y, s0.z, s0.w};
+#pragma unroll
+                    for (int grp = 0; grp < 8; ++grp) {
+                        const int w0 = (grp & 1) ? (3 * grp - 1) / 2 : (3 * grp) / 2;
+                        const uint32_t win = prmt(cw[w0], cw[w0 + 1], (grp & 1) ? sel_odd : sel_even);
+                        const uint2 sel = lds_u64((win & win_mask) * win_mul + lut_lane);
+                        // byte pools {0, lo, lo, 0} and {0, hi, hi ^ 0x80, 0} of the group's fp16 scale
+                        const uint32_t pa = prmt(sw[grp >> 1], 0u, (grp & 1) ? 0x4224u : 0x4004u);
+                        const uint32_t pb = prmt(sw[grp >> 1], 0u, (grp & 1) ? 0x4334u : 0x4114u) ^ 0x00800000u;
+                        mma_f16(acc[(2 * grp) % kChains], xa[0][grp][0], xa[0][grp][1], xa[0][grp][2], xa[0][grp][3],
+                                prmt(pa, pb, sel.x), prmt(pa, pb, sel.x >> 16));
+                        mma_f16(acc[(2 * grp + 1) % kChains], xa[1][grp][0], xa[1][grp][1], xa[1][grp][2], xa[1][grp][3],
+                                prmt(pa, pb, sel.y), prmt(pa, pb, sel.y >> 16));
+                    }
+                    float sum[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        sum[i] = acc[0][i];
+#pragma unroll
+                        for (int c = 1; c < kChains; ++c) sum[i] += acc[c][i];
+                    }
+                    *reinterpret_cast<float2*>(rbuf + ((0 * 4 + tl) * 32 + lane) * 2) = make_float2(sum[0] * upscale[0], sum[1] * upscale[0]);
+                    *reinterpret_cast<float2*>(rbuf + ((1 * 4 + tl) * 32 + lane) * 2) = make_float2(sum[2] * upscale[1], sum[3] * upscale[1]);
+                }
+            } else {
 #pragma unroll
             for (int tl = 0; tl < 4; ++tl) {
                 float out[NBLK][2];                                // [block][weight row 2t | 2t+1] of this 8-row tile
@@ -258,16 +383,17 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
                     *reinterpret_cast<float2*>(rbuf + ((blk * 4 + tl) * 32 + lane) * 2) =
                         make_float2(out[blk][0] * upscale[blk], out[blk][1] * upscale[blk]);
             }
+            }
         } else {
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);
 #pragma unroll
             for (int i = 0; i < 4 * NBLK; ++i) *reinterpret_cast<float2*>(rbuf + (i * 32 + lane) * 2) = make_float2(0.f, 0.f);
         }
+        if (tid == 0) sts_u128(red_desc + 16 * b, make_uint4((uint32_t)cc.prob, (uint32_t)cc.chunk, (uint32_t)cc.tile, 0u));
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_rfull + 8 * b);
         if (n >= Cfg::kRedLag) reduce_next();
-        b1_next(cc, probs, count);
     }
     while (reduced < nitems) reduce_next();
 
@@ -275,12 +401,12 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     if (tid == 0 && *abort_flag != 0) atomicCAS(&g_device_status, 0, *abort_flag);
 }
 
-template <int NBLK>
+template <int NBLK, bool kF16>
 static int32_t launch_gemv_bn(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
                               int M, int y_dtype, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemv_bn_kernel<NBLK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        const cudaError_t e = cudaFuncSetAttribute(gemv_bn_kernel<NBLK, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    (int)BnCfg<NBLK>::kSmem);
         if (e != cudaSuccess) { last_cuda_error() = e; return OJX_ERR_LAUNCH; }
         configured = true;
@@ -288,7 +414,7 @@ static int32_t launch_gemv_bn(const ojx_e8t_gemv_problem* probs, const ojx_e8t_g
     const int sms = num_sms();
     const int per = (total + sms - 1) / sms;
     const int grid = (total + per - 1) / per;
-    gemv_bn_kernel<NBLK><<<grid, kGemvThreads, BnCfg<NBLK>::kSmem, s>>>(probs, single, count, total, M, y_dtype);
+    gemv_bn_kernel<NBLK, kF16><<<grid, kGemvThreads, BnCfg<NBLK>::kSmem, s>>>(probs, single, count, total, M, y_dtype);
     return launch_status();
 }
 

@@ -51,8 +51,8 @@ static int32_t launch_gemv(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv
 static int32_t dispatch_gemv(bool bf16, const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count,
                              int total, int M, int y_dtype, cudaStream_t s) {
     if (bf16 && M == 1) return launch_gemv_b1(probs, single, count, total, y_dtype, s);
-    if (bf16) return M <= 8 ? launch_gemv_bn<1>(probs, single, count, total, M, y_dtype, s)
-                            : launch_gemv_bn<2>(probs, single, count, total, M, y_dtype, s);
+    if (bf16) return M <= 8 ? launch_gemv_bn<1, false>(probs, single, count, total, M, y_dtype, s)
+                            : launch_gemv_bn<2, true>(probs, single, count, total, M, y_dtype, s);
     // fp16 activations: the exact 16-bit kernel, which walks every 32-row tile as two 16-row halves
     return M <= 8 ? launch_gemv<false, 1>(probs, single, count, 2 * total, M, y_dtype, s)
                   : launch_gemv<false, 2>(probs, single, count, 2 * total, M, y_dtype, s);
