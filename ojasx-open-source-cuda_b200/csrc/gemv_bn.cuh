@@ -1,4 +1,5 @@
-// Decode GEMV for 2..16 bf16 activation rows on the int8 tensor cores.
+// Decode GEMV for 2..16 bf16 activation rows: int8 tensor cores for 2-8 rows, fp16 tensor cores with
+// scale-folded weights for 9-16 rows (template parameter kF16, described at the kernel).
 //
 // Same work items, cp.async ring and deterministic deferred reduction as gemv_b1.cuh; the MMA is turned
 // around so that several activation rows cost one instruction:
