@@ -163,13 +163,15 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
             const ojx_e8t_gemv_problem& P = probs[desc.x];
             const int rN = P.N, rchunk = (int)desc.y, rtile = (int)desc.z;
             const int o = warp * 16 * NBLK + lane;                 // output slot inside a warp's 256*NBLK block
-            float sum = 0.f;
-#pragma unroll
-            for (int w = 0; w < kGemvWarps; ++w) sum += rbuf[w * 256 * NBLK + o];
             // slot layout: ((blk * 4 + tile8) * 32 + lane') * 2 + j   with lane' = (batch g', rank lane t')
             const int j = o & 1, lp = (o >> 1) & 31, tile8 = (o >> 6) & 3, blk = o >> 8;
             const int row = rtile * kB1Rows + tile8 * 8 + ((lp & 3) << 1) + j;
             const int col = blk * 8 + (lp >> 2);
+            float sum = 0.f;
+            if (col < M) {                                         // activation rows beyond M hold zeros: nothing to add up
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; ++w) sum += rbuf[w * 256 * NBLK + o];
+            }
             if (row < rN && col < M) {
                 if (P.partial != nullptr) P.partial[((int64_t)rchunk * M + col) * rN + row] = sum;
                 else {
