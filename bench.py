@@ -262,12 +262,17 @@ def main():
     torch.cuda.synchronize()
 
     def step():
+        # The groups are independent, so each all-gather (own buffers, NCCL's stream) overlaps the next group's
+        # kernel; the compute stream joins all of them at the end of the pass.
+        pending = []
         for b in BATCHES:
             for si in range(len(SHAPES)):
                 groups[(si, b)]()
                 if world > 1:
                     y_all, gathered = gathers[(si, b)]
-                    dist.all_gather_into_tensor(gathered.view(world, -1), y_all.view(1, -1).squeeze(0), async_op=False)
+                    pending.append(dist.all_gather_into_tensor(gathered.view(world, -1), y_all.view(1, -1).squeeze(0), async_op=True))
+        for work in pending:
+            work.wait()
 
     def barrier():
         if world > 1:
@@ -360,11 +365,11 @@ def main():
                        "rotation": R, "l2": "inputs larger than L2: %.2f GB of packed weights per pass, a matrix is revisited only after the whole sweep" % (bytes_per_step / 3 / 1e9),
                        "parallelism": "output-column shards + NCCL all-gather" if world > 1 else "single GPU",
                        "launches_per_step": launches_per_step},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s", "frac": achieved / (hbm_peak * world),
                          "traffic": TRAFFIC_PER_LAUNCH, "traffic_per_kernel": NCU_TRAFFIC,
                          "kernel": "gemv_b1_kernel / gemv_bn_kernel (one grouped launch per shape and batch)",
                          "peak_source": peak_src + " (MEASURED_PEAKS.json hbm_gbs)" if peak_src == "measured" else peak_src,
-                         "note": "achieved = (packed + activation + output bytes of a pass) / time of a pass; launch gaps included"},
+                         "note": "achieved = (packed + activation + output bytes of a pass) / time of a pass, all GPUs together; launch gaps included; peak = measured per-GPU HBM bandwidth x n_gpus"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d_per_step, "d2h_bytes_per_step": d2h_per_step,
                     "ms_per_step": e2e_ms},
             "gpu_launches": launches_per_step * args.steps,

@@ -161,9 +161,19 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     // The lookup table is built while the first items are in flight: one global read per rank, stored as its
     // kB1Copies interleaved copies with a single 16-byte store.
     static_assert(kB1Copies == 4, "one uint4 per table entry");
-    for (int e = tid; e < kNumPoints; e += kGemvThreads) {
-        const uint32_t v = g_trit_nibbles[e];
-        reinterpret_cast<uint4*>(lut)[e] = make_uint4(v, v, v, v);
+    {
+        constexpr int kPerThread = (kNumPoints + kGemvThreads - 1) / kGemvThreads;
+        uint32_t v[kPerThread];
+#pragma unroll
+        for (int j = 0; j < kPerThread; ++j) {                 // all loads first: one global latency, not seven
+            const int e = tid + j * kGemvThreads;
+            v[j] = e < kNumPoints ? g_trit_nibbles[e] : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < kPerThread; ++j) {
+            const int e = tid + j * kGemvThreads;
+            if (e < kNumPoints) reinterpret_cast<uint4*>(lut)[e] = make_uint4(v[j], v[j], v[j], v[j]);
+        }
     }
     __syncthreads();
 

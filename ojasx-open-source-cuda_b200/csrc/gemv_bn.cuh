@@ -132,22 +132,34 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     // The lookup table is built while the first items are in flight: one global read per rank, stored as its
     // interleaved copies with a single 16-byte store.
     static_assert(Cfg::kCopies == 4, "one uint4 per table entry");
-    for (int e = tid; e < kNumPoints; e += kGemvThreads) {
-        const uint32_t v = g_trit_nibbles[e];
-        if constexpr (!kF16) {
-            reinterpret_cast<uint4*>(lut)[e] = make_uint4(v, v, v, v);
-        } else {
-            // two copies of a 64-bit entry: four 16-bit permute selectors, one per pair of coordinates; a
-            // coordinate code c (0: zero, 1: plus, 2: minus) selects low byte c of the first pool word and high
-            // byte c of the second (index 4 + c)
-            uint32_t sel[4];
+    {
+        constexpr int kPerThread = (kNumPoints + kGemvThreads - 1) / kGemvThreads;
+        uint32_t nib[kPerThread];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t ca = (v >> (8 * j)) & 0xFu, cb = (v >> (8 * j + 4)) & 0xFu;
-                sel[j] = ca | ((ca + 4) << 4) | (cb << 8) | ((cb + 4) << 12);
+        for (int j = 0; j < kPerThread; ++j) {                 // all loads first: one global latency, not seven
+            const int e = tid + j * kGemvThreads;
+            nib[j] = e < kNumPoints ? g_trit_nibbles[e] : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < kPerThread; ++j) {
+            const int e = tid + j * kGemvThreads;
+            if (e >= kNumPoints) continue;
+            const uint32_t v = nib[j];
+            if constexpr (!kF16) {
+                reinterpret_cast<uint4*>(lut)[e] = make_uint4(v, v, v, v);
+            } else {
+                // two copies of a 64-bit entry: four 16-bit permute selectors, one per pair of coordinates; a
+                // coordinate code c (0: zero, 1: plus, 2: minus) selects low byte c of the first pool word and high
+                // byte c of the second (index 4 + c)
+                uint32_t sel[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t ca = (v >> (8 * q)) & 0xFu, cb = (v >> (8 * q + 4)) & 0xFu;
+                    sel[q] = ca | ((ca + 4) << 4) | (cb << 8) | ((cb + 4) << 12);
+                }
+                const uint32_t w0 = sel[0] | (sel[1] << 16), w1 = sel[2] | (sel[3] << 16);
+                reinterpret_cast<uint4*>(lut)[e] = make_uint4(w0, w1, w0, w1);
             }
-            const uint32_t w0 = sel[0] | (sel[1] << 16), w1 = sel[2] | (sel[3] << 16);
-            reinterpret_cast<uint4*>(lut)[e] = make_uint4(w0, w1, w0, w1);
         }
     }
     __syncthreads();
