@@ -10,11 +10,13 @@ from .lattice import (E8LatticeLinear, TernaryE8LatticePacker, _FusedE8GEMMFunct
                       _get_ternary_e8_luts, fwht_block32, pack_model_e8)
 from .streaming_e8 import (_copy_row_block_into_layer, _pack_row_block, _validate_row_layout,   # noqa: F401
                            pack_weight_rowwise)
-from .hardware import dispatch_tilelang_e8_gemm, install_into_reference      # noqa: F401
+from .hardware import (dispatch_tilelang_e8_gemm, fused_ternary_e8_gemm_bwd_dx, fused_ternary_e8_gemm_fwd,     # noqa: F401
+                       install_into_reference)
 from .sharding import ColumnShardedLinear, shard_rows                        # noqa: F401
 
 __all__ = [
     "E8LatticeLinear", "TernaryE8LatticePacker", "_FusedE8GEMMFunction", "pack_model_e8", "fwht_block32",
-    "pack_weight_rowwise", "dispatch_tilelang_e8_gemm", "install_into_reference", "ColumnShardedLinear",
+    "pack_weight_rowwise", "dispatch_tilelang_e8_gemm", "install_into_reference",
+    "fused_ternary_e8_gemm_fwd", "fused_ternary_e8_gemm_bwd_dx", "ColumnShardedLinear",
     "shard_rows", "ops",
 ]

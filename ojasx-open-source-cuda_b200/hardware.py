@@ -31,6 +31,40 @@ def dispatch_tilelang_e8_gemm(x_2d: torch.Tensor, packed_weight: torch.Tensor, b
     return ops.linear(x_2d, packed_weight, block_scales, bias, out_features, in_features, group_size)
 
 
+def fused_ternary_e8_gemm_fwd(x: torch.Tensor, packed_weight: torch.Tensor, block_scales: torch.Tensor,
+                              bias: Optional[torch.Tensor] = None, group_size: int = 32) -> torch.Tensor:
+    """Same schema as the reference's native op ``fused_ternary_e8_gemm_fwd(Tensor x, Tensor packed_weight,
+    Tensor block_scales, Tensor? bias=None, int group_size=32) -> Tensor``
+    (``ojasx2/math/csrc/ojasx_math_bindings.cpp:407-477,592``): ``x [M, K]``, row-major 2-D
+    ``packed_weight [N, K*3/16]`` and ``block_scales [N, K/group]``; returns ``y [M, N]`` in x's dtype.
+    The reference casts the scales to x's dtype before the call; fp16 scales are used as they are and any
+    other dtype is converted back to fp16 (exact for values that were fp16 to begin with)."""
+    if x.dim() != 2 or packed_weight.dim() != 2 or block_scales.dim() != 2:
+        raise RuntimeError("fused_ternary_e8_gemm_fwd expects 2-D x, packed_weight and block_scales")
+    n, k = int(packed_weight.shape[0]), int(x.shape[1])
+    if int(packed_weight.shape[1]) * 16 != k * 3 or int(block_scales.shape[0]) != n:
+        raise RuntimeError("fused_ternary_e8_gemm_fwd: packed_weight / block_scales do not match x")
+    scales = block_scales if block_scales.dtype == torch.float16 else block_scales.to(torch.float16)
+    return ops.linear(x.contiguous(), packed_weight.contiguous().view(-1), scales.contiguous().view(-1), bias, n, k, group_size)
+
+
+def fused_ternary_e8_gemm_bwd_dx(grad_y: torch.Tensor, packed_weight: torch.Tensor, block_scales: torch.Tensor,
+                                 in_features: int, group_size: int = 32) -> torch.Tensor:
+    """Same schema as the reference's ``fused_ternary_e8_gemm_bwd_dx(Tensor grad_y, Tensor packed_weight,
+    Tensor block_scales, int in_features, int group_size=32) -> Tensor``
+    (``ojasx_math_bindings.cpp:479-533,594``): ``dX [M, K] = dY [M, N] . W [N, K]``.  Not on the accelerated
+    path: the weights are decoded once by the decode kernel and multiplied with ``torch.matmul``."""
+    if grad_y.dim() != 2 or packed_weight.dim() != 2 or block_scales.dim() != 2:
+        raise RuntimeError("fused_ternary_e8_gemm_bwd_dx expects 2-D grad_y, packed_weight and block_scales")
+    n = int(packed_weight.shape[0])
+    if int(grad_y.shape[1]) != n or int(packed_weight.shape[1]) * 16 != int(in_features) * 3:
+        raise RuntimeError("fused_ternary_e8_gemm_bwd_dx: shapes do not match")
+    del group_size
+    scales = block_scales if block_scales.dtype == torch.float16 else block_scales.to(torch.float16)
+    w = ops.decode(packed_weight.contiguous().view(-1), scales.contiguous().view(-1), (n, int(in_features)), grad_y.dtype)
+    return grad_y.matmul(w)
+
+
 def install_into_reference() -> bool:
     """Rebinds the reference's seam to this backend when the reference package is importable.
     Returns True when the patch was applied."""

@@ -73,6 +73,10 @@ def test_mirror_keeps_reference_signatures(P):
         "ctx", "x", "packed_weight", "block_scales", "bias", "out_features", "in_features", "group_size", "bitrate", "use_hadamard"]
     assert list(sig(P.E8LatticeLinear.__init__).parameters) == [
         "self", "in_features", "out_features", "bias", "rank", "lora_alpha", "group_size", "bitrate", "use_hadamard", "device", "dtype"]
+    # native-op schemas (ojasx_math_bindings.cpp:592-594)
+    assert list(sig(P.fused_ternary_e8_gemm_fwd).parameters) == ["x", "packed_weight", "block_scales", "bias", "group_size"]
+    assert sig(P.fused_ternary_e8_gemm_fwd).parameters["group_size"].default == 32
+    assert list(sig(P.fused_ternary_e8_gemm_bwd_dx).parameters) == ["grad_y", "packed_weight", "block_scales", "in_features", "group_size"]
     assert list(sig(P.dispatch_tilelang_e8_gemm).parameters) == [
         "x_2d", "packed_weight", "block_scales", "bias", "out_features", "in_features", "group_size", "bitrate", "lut_coords"]
     prw = sig(P.pack_weight_rowwise).parameters

@@ -315,3 +315,25 @@ def test_full_size_properties_llama_q_proj(P, oracle, coracle):
         max_abs = float((y.float() - y_ref).abs().max())
         assert rel <= 2e-3 and max_abs <= 1e-2 * float(x.float().abs().max()) * math.sqrt(k), (m, rel, max_abs)
     P.ops.gemm_status(dev)
+
+
+def test_native_op_schema_entry_points(P, oracle):
+    """fused_ternary_e8_gemm_fwd / _bwd_dx with the reference's 2-D row-major operands
+    (ojasx_math_bindings.cpp:407-533): forward against the oracle, dX against a dense product."""
+    dev = torch.device(DEV)
+    n, k, m = 512, 1024, 8
+    w = P.ops.generate(n * k, 321, 0.02, torch.float16, dev).view(n, k)
+    pk, sc = P.ops.encode(w, 32)
+    pk2, sc2 = pk.view(n, k * 3 // 16), sc.view(n, k // 32)
+    x = P.ops.generate(m * k, 322, 1.0, torch.bfloat16, dev).view(m, k)
+    bias = P.ops.generate(n, 323, 0.1, torch.bfloat16, dev)
+    y = P.fused_ternary_e8_gemm_fwd(x, pk2, sc2, bias, 32)
+    wd = P.ops.decode(pk, sc, (n, k), torch.float32)
+    ref = x.float() @ wd.t() + bias.float()
+    assert float((y.float() - ref).norm() / ref.norm()) <= 2e-3
+    gy = P.ops.generate(m * n, 324, 1.0, torch.float32, dev).view(m, n)
+    dx = P.fused_ternary_e8_gemm_bwd_dx(gy, pk2, sc2, k, 32)
+    assert dx.shape == (m, k)
+    assert float((dx - gy @ wd).norm() / (gy @ wd).norm()) <= 1e-5
+    with pytest.raises(RuntimeError):
+        P.fused_ternary_e8_gemm_fwd(x, pk, sc2, None, 32)
