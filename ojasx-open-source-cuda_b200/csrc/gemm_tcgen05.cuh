@@ -58,6 +58,8 @@ struct GemmParams {
     void* y;
     int32_t* status;
     int M, N, K;
+    int y_stride;                  // elements between consecutive token rows of y (N of the whole matrix)
+    int tile_limit;                // process only the first tile_limit tiles of the enumeration
     int y_dtype;
     int bias_dtype;
     uint32_t idesc;
@@ -220,7 +222,7 @@ __device__ __forceinline__ void gemm_store32(T* __restrict__ y, int64_t N, int n
 // One epilogue warp's share of a finished tile: TMEM lanes 32 * warp .. of both row blocks, all token columns.
 // Kept out of line so that its registers are allocated independently of the decoders' inner loop.
 __device__ __noinline__ void gemm_drain_tile(void* __restrict__ y, int y_dtype, const void* __restrict__ bias_ptr, int bias_dtype,
-                                             const float* __restrict__ up, int M, int N, int rows, int bn,
+                                             const float* __restrict__ up, int M, int N, int y_stride, int rows, int bn,
                                              uint32_t tmem_base, int warp, int lane, int n_blk, int m_blk) {
     const int blocks = bn / 32;
     for (int h = 0; h < rows / kGemmHalf; ++h) {
@@ -238,9 +240,9 @@ __device__ __noinline__ void gemm_drain_tile(void* __restrict__ y, int y_dtype, 
         auto store = [&](int cb, const uint32_t (&v)[32], float up_lane) {
             const int m0 = m_blk * bn + cb * 32;
             if (m0 >= M) return;                                   // warp-uniform
-            if (y_dtype == OJX_BF16) gemm_store32(static_cast<__nv_bfloat16*>(y), N, n, m0, M, v, up_lane, bias, live);
-            else if (y_dtype == OJX_F16) gemm_store32(static_cast<__half*>(y), N, n, m0, M, v, up_lane, bias, live);
-            else gemm_store32(static_cast<float*>(y), N, n, m0, M, v, up_lane, bias, live);
+            if (y_dtype == OJX_BF16) gemm_store32(static_cast<__nv_bfloat16*>(y), y_stride, n, m0, M, v, up_lane, bias, live);
+            else if (y_dtype == OJX_F16) gemm_store32(static_cast<__half*>(y), y_stride, n, m0, M, v, up_lane, bias, live);
+            else gemm_store32(static_cast<float*>(y), y_stride, n, m0, M, v, up_lane, bias, live);
         };
         uint32_t va[32], vb[32];
         float ua = load_up(0), ub;
@@ -311,7 +313,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     const int n_blocks = (p.N + p.rows - 1) / p.rows;
     const int m_blocks = (p.M + p.bn - 1) / p.bn;
     const uint32_t x_bytes = (uint32_t)p.bn * kGemmBK * 2;
-    const int tiles = n_blocks * m_blocks;
+    const int tiles = min(n_blocks * m_blocks, p.tile_limit);
     const int k_blocks = p.K / kGemmBK;
 
     if (warp == 12) {
@@ -431,7 +433,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
             ok = __all_sync(0xFFFFFFFFu, ok);          // warp-uniform decision before the aligned TMEM loads
             if (!ok) break;
             tc_fence_after();
-            gemm_drain_tile(p.y, p.y_dtype, p.bias, p.bias_dtype, p.up, p.M, p.N, p.rows, p.bn, tmem_base, warp, lane, n_blk, m_blk);
+            gemm_drain_tile(p.y, p.y_dtype, p.bias, p.bias_dtype, p.up, p.M, p.N, p.y_stride, p.rows, p.bn, tmem_base, warp, lane, n_blk, m_blk);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(0));
@@ -496,9 +498,9 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
     PFN_encodeTiled encode = get_encode_tiled();
     OJX_RETURN_IF(encode == nullptr, OJX_ERR_LAUNCH);
 
-    CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    float* up = convert ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256) : nullptr;
+    void* x_f16 = convert ? static_cast<void*>(static_cast<uint8_t*>(workspace) + 256 + gemm_up_bytes(M)) : const_cast<void*>(x);
+
     // Tile shape: the choice that minimises (waves over the SMs) x (work per tile), with a small
     // penalty for the shapes that reuse each fetched x tile or decoded weight tile less.
     int rows = kGemmBM, bn = kGemmBN;
@@ -514,14 +516,6 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
                 if (cost < best) { best = cost; rows = cand_rows[ri]; bn = cand_bn[bi]; }
             }
     }
-    const cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)bn};
-    const cuuint32_t estr[2] = {1, 1};
-    float* up = convert ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256) : nullptr;
-    void* x_f16 = convert ? static_cast<void*>(static_cast<uint8_t*>(workspace) + 256 + gemm_up_bytes(M)) : const_cast<void*>(x);
-    if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x_f16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return OJX_ERR_LAUNCH;
 
     static bool configured = false;
     if (!configured) {
@@ -541,21 +535,53 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         return OJX_ERR_LAUNCH;
     }
 
-    GemmParams prm;
-    prm.packed = packed; prm.scales = scales; prm.bias = bias; prm.y = y;
-    prm.status = static_cast<int32_t*>(workspace);
-    prm.M = (int)M; prm.N = (int)N; prm.K = (int)K;
-    prm.y_dtype = y_dtype; prm.bias_dtype = x_dtype;
-    prm.up = up;
-    // instruction descriptor: fp32 accumulate (bits 4-5 = 1), A and B both fp16 (format 0), both K-major,
-    // N >> 3 at bits 17-22, M >> 4 at bits 24-28
-    prm.rows = rows; prm.bn = bn;
-    prm.idesc = (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kGemmHalf >> 4) << 24);
+    // One launch over the rectangle of weight rows [n0, N) x tokens [m0, M) of the problem, in tiles of
+    // rows x bn, stopping after tile_limit tiles of the enumeration (token block major, weight-row block minor).
+    auto launch_region = [&](int64_t n0, int64_t m0, int rows, int bn, int tile_limit) -> int32_t {
+        const int64_t Ns = N - n0, Ms = M - m0;
+        CUtensorMap tmap;
+        const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)Ms};
+        const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)bn};
+        const cuuint32_t estr[2] = {1, 1};
+        void* xs = static_cast<uint8_t*>(x_f16) + (size_t)m0 * (size_t)K * 2;
+        if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xs, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return OJX_ERR_LAUNCH;
+        GemmParams prm;
+        prm.packed = packed + (size_t)n0 * (size_t)K * 3 / 16;
+        prm.scales = scales + (size_t)n0 * (size_t)K / 32;
+        prm.bias = bias ? static_cast<const uint8_t*>(bias) + (size_t)n0 * dtype_size(x_dtype) : nullptr;
+        prm.y = static_cast<uint8_t*>(y) + ((size_t)m0 * (size_t)N + (size_t)n0) * dtype_size(y_dtype);
+        prm.status = static_cast<int32_t*>(workspace);
+        prm.M = (int)Ms; prm.N = (int)Ns; prm.K = (int)K;
+        prm.y_stride = (int)N;
+        prm.y_dtype = y_dtype; prm.bias_dtype = x_dtype;
+        prm.up = up ? up + m0 : nullptr;
+        prm.rows = rows; prm.bn = bn;
+        // instruction descriptor: fp32 accumulate (bits 4-5 = 1), A and B both fp16 (format 0), both K-major,
+        // N >> 3 at bits 17-22, M >> 4 at bits 24-28
+        prm.idesc = (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kGemmHalf >> 4) << 24);
+        const int64_t all = ((Ns + rows - 1) / rows) * ((Ms + bn - 1) / bn);
+        prm.tile_limit = (int)(all < tile_limit ? all : tile_limit);
+        const int grid = prm.tile_limit < num_sms() ? prm.tile_limit : num_sms();
+        gemm_tcgen05_kernel<<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+        return launch_status();
+    };
 
-    const int tiles = (int)(((N + rows - 1) / rows) * ((M + bn - 1) / bn));
-    const int grid = tiles < num_sms() ? tiles : num_sms();
-    gemm_tcgen05_kernel<<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
-    return launch_status();
+    // Tail splitting: when the last wave of big tiles would leave most SMs idle, the big tiles stop at a whole
+    // number of waves and the remaining rectangle (the end of the last token block) runs as small tiles.
+    const int sms = num_sms();
+    const int64_t n_blocks = (N + rows - 1) / rows, m_blocks = (M + bn - 1) / bn;
+    const int64_t tiles = n_blocks * m_blocks;
+    const int64_t full = (tiles / sms) * sms, leftover = tiles - full;
+    if (rows == kGemmBM && bn == kGemmBN && full > 0 && leftover > 0 && leftover <= n_blocks && 4 * leftover <= 2 * sms) {
+        const int32_t st = launch_region(0, 0, rows, bn, (int)full);
+        if (st != OJX_OK) return st;
+        return launch_region((n_blocks - leftover) * rows, (m_blocks - 1) * bn, kGemmHalf, 128, 1 << 30);
+    }
+    return launch_region(0, 0, rows, bn, 1 << 30);
 }
 
 int32_t gemm_status_impl(const void* workspace, cudaStream_t s) {

@@ -337,3 +337,23 @@ def test_native_op_schema_entry_points(P, oracle):
     assert float((dx - gy @ wd).norm() / (gy @ wd).norm()) <= 1e-5
     with pytest.raises(RuntimeError):
         P.fused_ternary_e8_gemm_fwd(x, pk, sc2, None, 32)
+
+
+def test_gemm_tail_split_matches_dense_product(P):
+    """150 big tiles on 148 SMs: the GEMM runs 148 tiles of 256 x 256 and hands the rest of the last token
+    block to a second launch with small tiles.  Every output is checked against a dense fp32 product
+    (bias included), with a ragged last row block and a ragged last token block."""
+    dev = torch.device(DEV)
+    n, k, m = 256 * 30 - 40, 512, 256 * 5 - 24
+    w = P.ops.generate(n * k, 901, 0.02, torch.float16, dev).view(n, k)
+    pk, sc = P.ops.encode(w, 32)
+    x = P.ops.generate(m * k, 902, 1.0, torch.bfloat16, dev).view(m, k)
+    bias = P.ops.generate(n, 903, 0.1, torch.bfloat16, dev)
+    y = P.ops.linear(x, pk, sc, bias, n, k, 32, force="gemm")
+    P.ops.gemm_status(dev)
+    wd = P.ops.decode(pk, sc, (n, k), torch.float32)
+    ref = x.float() @ wd.t() + bias.float()
+    d = y.float() - ref
+    assert float(d.norm() / ref.norm()) <= 2e-3
+    assert float(d.abs().max()) <= 1e-2 * float(x.float().abs().max()) * k ** 0.5
+    assert torch.isfinite(y.float()).all()
