@@ -281,6 +281,7 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     // ---- issue: every thread copies its chunks of item n into ring stage n mod S ----
     Cursor ic;                                  // cursor of the next item to be issued
     cursor_seek(ic, probs, p0, i0);
+    const Cursor first = ic;                                       // the other two cursors start from the same item
     int issued = 0;
     ItemLoader loader;
     loader.ring = ring; loader.bar_full = bar_full; loader.bar_empty = bar_empty; loader.tid = tid; loader.prob = -1;
@@ -344,8 +345,7 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
 
     uint32_t xf[NB][8][4];
     int cur_prob = -1, cur_chunk = -1;
-    Cursor cc;
-    cursor_seek(cc, probs, p0, i0);
+    Cursor cc = first;
     for (int n = 0; n < nitems; ++n) {
         const int s = n % kGemvStages, b = n % kGemvRed;
         if (issued < nitems) issue_next();                       // keeps kGemvAhead items in flight

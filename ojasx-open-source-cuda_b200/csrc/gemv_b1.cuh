@@ -133,6 +133,7 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const int lr = tid >> 4, ls = tid & 15;
     B1Cursor ic;
     b1_seek(ic, probs, p0, i0);
+    const B1Cursor first = ic;                                     // the other two cursors start from the same item
     int issued = 0;
     auto issue_next = [&]() {
         const int n = issued, s = n % kB1Stages;
@@ -178,8 +179,7 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     __syncthreads();
 
     // ---- reduction of item n by warp n mod 16, kB1RedLag items after it was computed ----
-    B1Cursor rc;
-    b1_seek(rc, probs, p0, i0);
+    B1Cursor rc = first;
     int reduced = 0;
     auto reduce_next = [&]() {
         const int n = reduced, b = n % kB1Red;
@@ -213,8 +213,7 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     uint32_t xh[8][2], xl[8][2];                      // int8 activation fragments (hi, lo) for the 8 steps
     float upscale = 1.f;                              // 2^e of this warp's slice
     int cur_prob = -1, cur_chunk = -1;
-    B1Cursor cc;
-    b1_seek(cc, probs, p0, i0);
+    B1Cursor cc = first;
 
     for (int n = 0; n < nitems; ++n) {
         const int s = n % kB1Stages, b = n % kB1Red;

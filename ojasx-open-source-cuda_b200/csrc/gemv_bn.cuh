@@ -55,11 +55,12 @@ __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
 // as fp16 (x * 2^-e per row and slice, exact for bf16 inputs), sixteen rows per mma.sync.m16n8k16 with fp32
 // accumulation across all eight groups of the slice - so no per-group integer combine, convert and scale
 // multiply remain, which is what the int8 form spends most of its instructions on at 16 rows.
-template <int NBLK, bool kF16>
+template <int NBLK, bool kF16, bool kXF16>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_constant__ ojx_e8t_gemv_problem single,
                int count, int total_items, int M, int y_dtype) {
     using Cfg = BnCfg<NBLK>;
+    static_assert(kF16 || !kXF16, "fp16 activations take the fp16 form");
     const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
     extern __shared__ __align__(128) uint8_t smem[];
     uint32_t* lut = reinterpret_cast<uint32_t*>(smem);
@@ -187,7 +188,7 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
             if (row < rN && col < M) {
                 if (P.partial != nullptr) P.partial[((int64_t)rchunk * M + col) * rN + row] = sum;
                 else {
-                    if (P.bias != nullptr) sum += __bfloat162float(static_cast<const __nv_bfloat16*>(P.bias)[row]);
+                    if (P.bias != nullptr) sum += load_any(P.bias, kXF16 ? OJX_F16 : OJX_BF16, row);
                     store_any(P.y, y_dtype, (int64_t)col * rN + row, sum);
                 }
             }
@@ -249,6 +250,16 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
 #pragma unroll
                         for (int i = 0; i < 4; ++i) amax = max(amax, max((w[i] << 16) & 0x7FFFFFFFu, w[i] & 0x7FFF0000u));
                     }
+                    if constexpr (kXF16) {                         // fp16 activations are MMA operands as they are
+                        upscale[hrow] = 1.0f;
+#pragma unroll
+                        for (int grp = 0; grp < 8; ++grp) {
+                            xa[0][grp][hrow] = q[grp].x; xa[0][grp][2 + hrow] = q[grp].y;
+                            xa[1][grp][hrow] = q[grp].z; xa[1][grp][2 + hrow] = q[grp].w;
+                        }
+                        continue;
+                    }
+                    (void)amax;
                     amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
                     amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));  // the four lanes of activation row m
                     int e = 0;
@@ -416,12 +427,12 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     if (tid == 0 && *abort_flag != 0) atomicCAS(&g_device_status, 0, *abort_flag);
 }
 
-template <int NBLK, bool kF16>
+template <int NBLK, bool kF16, bool kXF16>
 static int32_t launch_gemv_bn(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
                               int M, int y_dtype, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemv_bn_kernel<NBLK, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        const cudaError_t e = cudaFuncSetAttribute(gemv_bn_kernel<NBLK, kF16, kXF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    (int)BnCfg<NBLK>::kSmem);
         if (e != cudaSuccess) { last_cuda_error() = e; return OJX_ERR_LAUNCH; }
         configured = true;
@@ -429,7 +440,7 @@ static int32_t launch_gemv_bn(const ojx_e8t_gemv_problem* probs, const ojx_e8t_g
     const int sms = num_sms();
     const int per = (total + sms - 1) / sms;
     const int grid = (total + per - 1) / per;
-    gemv_bn_kernel<NBLK, kF16><<<grid, kGemvThreads, BnCfg<NBLK>::kSmem, s>>>(probs, single, count, total, M, y_dtype);
+    gemv_bn_kernel<NBLK, kF16, kXF16><<<grid, kGemvThreads, BnCfg<NBLK>::kSmem, s>>>(probs, single, count, total, M, y_dtype);
     return launch_status();
 }
 

@@ -46,16 +46,16 @@ static int32_t launch_gemv(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv
     return launch_status();
 }
 
-// bf16 activations take the int8 tensor-core kernels (one row: gemv_b1, 2..16 rows: gemv_bn); fp16
-// activations the 16-bit kernel.
+// bf16 activations: one row -> gemv_b1 (int8), 2-8 rows -> gemv_bn int8 form, 9-16 rows -> gemv_bn fp16 form.
 static int32_t dispatch_gemv(bool bf16, const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count,
                              int total, int M, int y_dtype, cudaStream_t s) {
     if (bf16 && M == 1) return launch_gemv_b1(probs, single, count, total, y_dtype, s);
-    if (bf16) return M <= 8 ? launch_gemv_bn<1, false>(probs, single, count, total, M, y_dtype, s)
-                            : launch_gemv_bn<2, true>(probs, single, count, total, M, y_dtype, s);
-    // fp16 activations: the exact 16-bit kernel, which walks every 32-row tile as two 16-row halves
+    if (bf16) return M <= 8 ? launch_gemv_bn<1, false, false>(probs, single, count, total, M, y_dtype, s)
+                            : launch_gemv_bn<2, true, false>(probs, single, count, total, M, y_dtype, s);
+    // fp16 activations: 9-16 rows share the scale-folded fp16 kernel (the activations need no conversion);
+    // up to 8 rows take the 16-bit kernel, which walks every 32-row tile as two 16-row halves
     return M <= 8 ? launch_gemv<false, 1>(probs, single, count, 2 * total, M, y_dtype, s)
-                  : launch_gemv<false, 2>(probs, single, count, 2 * total, M, y_dtype, s);
+                  : launch_gemv_bn<2, true, true>(probs, single, count, total, M, y_dtype, s);
 }
 
 int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
