@@ -48,7 +48,8 @@ constexpr int kGemmThreads = 448;          // 4 epilogue + 8 decoder + 1 TMA + 1
 constexpr int kGemmDecoderWarps = 8;
 constexpr uint32_t kXStageBytes = kGemmBN * kGemmBK * 2;      // 32768
 constexpr uint32_t kAStageBytes = kGemmBM * kGemmBK * 2;      // 32768 (rows 0-127, then rows 128-255)
-constexpr uint32_t kGemmLutBytes = 4096 * 8;                  // rank -> eight fp16 high bytes (+1.0 / -1.0 / 0); any 12-bit rank in bounds
+constexpr int kGemmDigitCopies = 16;
+constexpr uint32_t kGemmLutBytes = 16384;                     // digit table: 81 x 16 copies x 8 bytes = 10368; a corrupt rank (up to 4095) stays inside
 constexpr uint32_t kGemmSmemBytes = kGemmStages * (kXStageBytes + kAStageBytes) + kGemmLutBytes + 256 + 1024;
 
 struct GemmParams {
@@ -261,6 +262,11 @@ __device__ __noinline__ void gemm_drain_tile(void* __restrict__ y, int y_dtype, 
     }
 }
 
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -282,11 +288,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    // 64-bit table: byte i = high byte of the fp16 value of coordinate i (0x3C: +1.0, 0xBC: -1.0, 0: 0)
-    for (int i = tid; i < 4096; i += kGemmThreads) {
-        const uint32_t nib = i < kNumPoints ? g_trit_nibbles[i] : 0u;
-        const uint32_t lo = prmt(0x00BC3C00u, 0u, nib), hi = prmt(0x00BC3C00u, 0u, nib >> 16);
-        reinterpret_cast<uint2*>(lut)[i] = make_uint2(lo, hi);
+    // Digit table: entry e < 81 holds the four base-3 digits of e, each minus one, as fp16 (+-1.0 / 0), in sixteen
+    // interleaved copies (one per lane of a half warp, so the 64-bit lookups never meet in a bank).  A rank r is
+    // the base-3 number 2r (even coordinate sums are exactly the even numbers), so its eight coordinates are the
+    // digits of (2r) mod 81 followed by those of (2r) div 81.
+    for (int i = tid; i < 81 * kGemmDigitCopies; i += kGemmThreads) {
+        int e = i / kGemmDigitCopies;
+        uint32_t h[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { const int d = e % 3; e /= 3; h[k] = d == 0 ? 0xBC00u : (d == 1 ? 0u : 0x3C00u); }
+        reinterpret_cast<uint2*>(lut)[i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
     }
     if (tid == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
@@ -374,6 +385,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     } else if (warp >= 4 && (warp - 4) * 32 < p.rows) {
         // ---------------- decoders (warps beyond the tile's rows stay idle) ----------------
         const int r = (warp - 4) * 32 + lane;           // row of the 256-row tile
+        const uint8_t* digit_lane = reinterpret_cast<const uint8_t*>(lut) + (lane & (kGemmDigitCopies - 1)) * 8;
         uint32_t it = 0;
         bool ok = true;
         const int64_t row_bytes = (int64_t)p.K * 3 / 16, row_scales = p.K / 32;
@@ -397,25 +409,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
                     const uint32_t ph = (it / kGemmStages) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 4)) { ok = false; break; }
                     uint8_t* arow = smem + kGemmStages * kXStageBytes + s * kAStageBytes + r * 128;
-                    // All eight table lookups are issued before the first store: the compiler must assume a
-                    // shared-memory store may alias the table, so interleaving them would serialise the ranks.
-                    uint2 hb[8];
+                    // Four ranks at a time: their lookups are issued before the first store (the compiler must
+                    // assume a shared-memory store may alias the table).
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int c = q * 8 + j;                 // rank index inside the 48-byte chunk
-                        const int bit = 12 * c, w = bit >> 5, sh = bit & 31;
-                        uint32_t off;                            // rank * 8 = byte offset into the 64-bit table
-                        if (sh + 12 <= 32) off = sh >= 3 ? (cw[w] >> (sh - 3)) : (cw[w] << (3 - sh));
-                        else off = __funnelshift_r(cw[w], cw[w + 1 < 12 ? w + 1 : 11], sh - 3);
-                        hb[j] = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(lut) + (off & 0x7FF8u));
-                    }
+                    for (int half = 0; half < 2; ++half) {
+                        uint2 lo8[4], hi8[4];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int grp = (q * 8 + j) >> 2;        // scale group inside the chunk
-                        const uint32_t sp = sw[grp >> 1];
-                        const uint32_t s16 = (grp & 1) ? (sp >> 16) : (sp & 0xFFFFu);
-                        const uint4 v = decode_chunk_f16(hb[j], s16 | (s16 << 16));
-                        *reinterpret_cast<uint4*>(arow + ((j ^ (r & 7)) << 4)) = v;
+                        for (int j = 0; j < 4; ++j) {
+                            const int c = q * 8 + half * 4 + j;      // rank index inside the 48-byte chunk
+                            const int bit = 12 * c, w = bit >> 5, sh = bit & 31;
+                            uint32_t R;                              // 2 * rank
+                            if (sh + 12 <= 32) R = sh >= 1 ? (cw[w] >> (sh - 1)) : (cw[w] << 1);
+                            else R = __funnelshift_r(cw[w], cw[w + 1 < 12 ? w + 1 : 11], sh - 1);
+                            R &= 0x1FFEu;
+                            const uint32_t v = (R * 6473u) >> 19;    // R div 81 (exact for R < 6562)
+                            const uint32_t u = R - 81u * v;
+                            lo8[j] = *reinterpret_cast<const uint2*>(digit_lane + u * (kGemmDigitCopies * 8));   // coordinates 0-3
+                            hi8[j] = *reinterpret_cast<const uint2*>(digit_lane + v * (kGemmDigitCopies * 8));   // coordinates 4-7
+                        }
+                        // the four ranks of a half are one scale group (32 k)
+                        const uint32_t sp = sw[q];
+                        const uint32_t sc2 = prmt(sp, 0u, half == 0 ? 0x1010u : 0x3232u);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int jj = half * 4 + j;
+                            const uint4 v = make_uint4(hmul2_u32(lo8[j].x, sc2), hmul2_u32(lo8[j].y, sc2),
+                                                       hmul2_u32(hi8[j].x, sc2), hmul2_u32(hi8[j].y, sc2));
+                            *reinterpret_cast<uint4*>(arow + ((jj ^ (r & 7)) << 4)) = v;
+                        }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> async proxy (UMMA)
                     __syncwarp();
