@@ -154,9 +154,10 @@ int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count
  * replaces the reference's TileLang builder (ojasx2/tilelang_kernels.py:277-363) and the
  * unpack + F.linear path (lattice.py:613-624).  Requires K % 256 == 0, group 32, bf16 or fp16 x.
  * `workspace` (256-byte aligned, size from ojx_e8t_gemm_workspace_bytes) holds a status block and,
- * for bf16 activations, their fp16 copy x * 2^-e (e = 0 unless max|x| >= 32768; the result is scaled
- * back by 2^e): the tensor cores need both operands in one 16-bit format and the weights are only
- * exact in fp16.
+ * for bf16 activations, one power-of-two factor per token row and the fp16 copy of the activations
+ * scaled by it (each row's largest magnitude is brought into [2^14, 2^15); the row's outputs are
+ * scaled back): the tensor cores need both operands in one 16-bit format and the weights are only
+ * exact in fp16.  Calls that share a workspace must not overlap on the GPU.
  * ojx_e8t_gemm_status reads back (synchronising the stream) whether any bounded wait inside the
  * last gemm on that workspace expired.
  */
