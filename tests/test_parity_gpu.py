@@ -357,3 +357,20 @@ def test_gemm_tail_split_matches_dense_product(P):
     assert float(d.norm() / ref.norm()) <= 2e-3
     assert float(d.abs().max()) <= 1e-2 * float(x.float().abs().max()) * k ** 0.5
     assert torch.isfinite(y.float()).all()
+
+
+def test_gemm_long_rows_take_the_two_pass_normalisation(P):
+    """K = 16640 is longer than the activation pre-pass keeps in registers (16384): the row is read twice."""
+    dev = torch.device(DEV)
+    n, k, m = 256, 16640, 40
+    w = P.ops.generate(n * k, 911, 0.02, torch.float16, dev).view(n, k)
+    pk, sc = P.ops.encode(w, 32)
+    x = P.ops.generate(m * k, 912, 1.0, torch.bfloat16, dev).view(m, k)
+    x[3] *= 3.0e4                                    # rows of very different magnitude: per-row factors matter
+    x[7] *= 1.0e-6
+    y = P.ops.linear(x, pk, sc, None, n, k, 32, force="gemm")
+    P.ops.gemm_status(dev)
+    ref = x.float() @ P.ops.decode(pk, sc, (n, k), torch.float32).t()
+    for row in (0, 3, 7, 39):
+        d = y[row].float() - ref[row]
+        assert float(d.norm() / ref[row].norm()) <= 2e-3, row
