@@ -440,7 +440,7 @@ def run_case(args):
 
 def run_extras(torch, ops, dev, groups, packed_store, hbm_peak, tf_peak):
     """Per-(shape, batch) decode numbers, the prefill GEMM and the encoder, each timed with CUDA events."""
-    out = {"decode_detail": [], "prefill": [], "encoder": None}
+    out = {"decode_detail": [], "prefill": [], "encoder": None, "decoder": None}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)       # > L2
 
@@ -489,6 +489,10 @@ def run_extras(torch, ops, dev, groups, packed_store, hbm_peak, tf_peak):
     gbs = n * k * 2.25 / (ms * 1e-3) / 1e9
     out["encoder"] = {"rows": n, "cols": k, "dtype": "f16", "ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak,
                       "Gweights_per_s": n * k / (ms * 1e-3) / 1e9}
+    # decoder (unpack): packed codes + scales -> dense fp16 weights, 0.25 B read + 2 B written per weight
+    ms = timed(lambda: ops.decode(pk, sc, (n, k), torch.float16, out=w), 3)
+    gbs = n * k * 2.25 / (ms * 1e-3) / 1e9
+    out["decoder"] = {"rows": n, "cols": k, "dtype": "f16", "ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak}
     return out
 
 
