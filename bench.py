@@ -193,6 +193,8 @@ def main():
     ap.add_argument("--rotation", type=int, default=64, help="distinct matrices per shape")
     ap.add_argument("--no-extras", action="store_true", help="skip prefill/encoder/per-shape extras")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: kernels store their column shard into every rank's output window (fused), or NCCL all-gather")
     ap.add_argument("--case", default=None, choices=["gemv", "gemm", "encode", "decode"],
                     help="run a few launches of ONE kernel on a small case and exit (used for ncu captures)")
     ap.add_argument("--K", type=int, default=4096)
@@ -217,9 +219,13 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dist = None
+    json_out = sys.stdout
     if world > 1:
-        # NCCL writes its version banner and debug lines to stdout by default; stdout carries the one JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        # NCCL prints its version banner with printf: everything that goes to file descriptor 1 from here on is
+        # sent to stderr, and the one JSON line is written to the saved descriptor at the end
+        sys.stdout.flush()
+        json_out = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -237,6 +243,26 @@ def main():
     bytes_per_step = 0
     h2d_per_step = 0
     d2h_per_step = 0
+    # N > 1, fused gather: one peer-mapped output window per (shape, batch).  Any rank that cannot map its peers'
+    # memory sends every rank back to the NCCL all-gather.
+    fused, windows = False, {}
+    if world > 1 and args.gather == "fused":
+        good = 1
+        try:
+            for si, (k, n) in enumerate(SHAPES):
+                n0, n1 = sharding.shard_rows(n, world, rank)
+                for b in BATCHES:
+                    windows[(si, b)] = sharding.PeerWindow(world * R * b * (n1 - n0), torch.bfloat16, dev)
+        except Exception as exc:                                  # noqa: BLE001
+            print(f"[bench] rank {rank}: peer windows unavailable ({exc}); using NCCL all-gather", file=sys.stderr)
+            good = 0
+        flag = torch.tensor([good], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        fused = int(flag.item()) == 1
+        if fused:      # equal shard sizes are what makes the windows line up
+            fused = all(sharding.shard_rows(n, world, r)[1] - sharding.shard_rows(n, world, r)[0] ==
+                        sharding.shard_rows(n, world, 0)[1] - sharding.shard_rows(n, world, 0)[0]
+                        for (k, n) in SHAPES for r in range(world))
     tmp = torch.empty(max(k * n for k, n in SHAPES), dtype=torch.float16, device=dev)
     for si, (k, n) in enumerate(SHAPES):
         n0, n1 = sharding.shard_rows(n, world, rank)
@@ -251,11 +277,19 @@ def main():
         for b in BATCHES:
             x = ops.generate(b * k, 7 + b + si, 1.0, torch.bfloat16, dev).view(b, k)
             xs[(si, b)] = x
-            y_all = torch.zeros((R, b, nl), dtype=torch.bfloat16, device=dev)
+            if fused:
+                # every rank's window holds all ranks' shards: [world, R, b, nl]; this rank's kernels fill slot `rank`
+                # of every window themselves
+                window = windows[(si, b)]
+                y_all = window.local.view(world, R, b, nl)[rank]
+                delta = window.delta
+            else:
+                y_all = torch.zeros((R, b, nl), dtype=torch.bfloat16, device=dev)
+                delta = None
             entries = [(x, pk, sc, None, y_all[r]) for r, (pk, sc) in enumerate(mats)]
-            groups[(si, b)] = ops.GroupedGemv(entries, [(nl, k)] * R)
+            groups[(si, b)] = ops.GroupedGemv(entries, [(nl, k)] * R, peer_delta=delta)
             launches_per_step += 1 + groups[(si, b)].needs_reduce
-            gathered = torch.empty((world, R, b, nl), dtype=torch.bfloat16, device=dev) if world > 1 else None
+            gathered = torch.empty((world, R, b, nl), dtype=torch.bfloat16, device=dev) if (world > 1 and not fused) else None
             gathers[(si, b)] = (y_all, gathered)
             bytes_per_step += R * (n * k // 4) // 1            # whole-job packed bytes (all ranks)
             h2d_per_step += b * k * 2
@@ -264,17 +298,20 @@ def main():
     torch.cuda.synchronize()
 
     def step():
-        # The groups are independent, so each all-gather (own buffers, NCCL's stream) overlaps the next group's
-        # kernel; the compute stream joins all of them at the end of the pass.
+        # Fused: the kernels write every rank's window; the ranks meet once at the end of the pass.
+        # NCCL: the groups are independent, so each all-gather (own buffers, NCCL's stream) overlaps the next
+        # group's kernel; the compute stream joins all of them at the end of the pass.
         pending = []
         for b in BATCHES:
             for si in range(len(SHAPES)):
                 groups[(si, b)]()
-                if world > 1:
+                if world > 1 and not fused:
                     y_all, gathered = gathers[(si, b)]
                     pending.append(dist.all_gather_into_tensor(gathered.view(world, -1), y_all.view(1, -1).squeeze(0), async_op=True))
         for work in pending:
             work.wait()
+        if fused:
+            windows[(0, BATCHES[0])].fence()
 
     def barrier():
         if world > 1:
@@ -323,13 +360,15 @@ def main():
         for key in keys:
             cur.wait_event(ev_x[key])
             groups[key]()
-            if world > 1:
+            if world > 1 and not fused:
                 y_all, gathered = gathers[key]
                 dist.all_gather_into_tensor(gathered.view(world, -1), y_all.view(-1))
             ev_y[key].record(cur)
             with torch.cuda.stream(down_stream):
                 down_stream.wait_event(ev_y[key])
                 y_host[key].copy_(gathers[key][0], non_blocking=True)
+        if fused:
+            windows[(0, BATCHES[0])].fence()
         torch.cuda.synchronize()
 
     for _ in range(2):
@@ -365,7 +404,8 @@ def main():
             "config": {"workload": "decode GEMV sweep, Llama-3-8B linear shapes (K->N 4096->4096, 4096->1024, 4096->14336, 14336->4096), "
                                    "batch 1/4/16, bf16 activations, bf16 outputs",
                        "rotation": R, "l2": "inputs larger than L2: %.2f GB of packed weights per pass, a matrix is revisited only after the whole sweep" % (bytes_per_step / 3 / 1e9),
-                       "parallelism": "output-column shards + NCCL all-gather" if world > 1 else "single GPU",
+                       "parallelism": ("output-column shards, kernels store into every rank's output window over NVLink (one fence per pass)" if fused
+                                       else "output-column shards + NCCL all-gather") if world > 1 else "single GPU",
                        "launches_per_step": launches_per_step},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s", "frac": achieved / (hbm_peak * world),
                          "traffic": TRAFFIC_PER_LAUNCH, "traffic_per_kernel": NCU_TRAFFIC,
@@ -382,8 +422,12 @@ def main():
             cb.pop("seconds", None)
             line["cpu_baseline"] = cb
         line.update(extras)
-        print(json.dumps(line))
+        json_out.write(json.dumps(line) + "\n")
+        json_out.flush()
     if world > 1:
+        for w in windows.values():
+            w.close()
+        barrier()
         dist.destroy_process_group()
 
 

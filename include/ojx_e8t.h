@@ -150,6 +150,26 @@ int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count
                              int64_t M, int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce, void* stream);
 
 /*
+ * Grouped decode-shape launch whose results go straight into EVERY rank's output window (fused
+ * all-gather for output-column sharding; no counterpart in the reference, which is single-device).
+ * Every rank holds an identically laid out output window; problems[i].y points into THIS rank's
+ * window at the place of this rank's shard, and peer_delta[r] (r < world, world <= 8) is the byte
+ * distance from this rank's window to rank r's window as mapped into this process (0 for this rank;
+ * e.g. from CUDA IPC handles).  The kernel stores each result `world` times - plain stores over
+ * NVLink, no device-side waiting, no multicast loads.  The caller orders the exchange: a peer may
+ * read its window only after this launch has completed on this rank's stream and the ranks have met
+ * (one small collective or barrier per step instead of one all-gather per launch).
+ */
+int32_t ojx_e8t_gemv_grouped_peers(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles,
+                                   int64_t M, int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
+                                   const int64_t* peer_delta, int32_t world, void* stream);
+/* Lets kernels of the current device address memory that lives on `peer_device` (same node, NVLink or PCIe
+ * peer): OJX_OK when access is (already) enabled, OJX_ERR_UNSUPPORTED when the two devices cannot be peers.
+ * Required once per peer before ojx_e8t_gemv_grouped_peers stores into that peer's window.  No counterpart in
+ * the reference. */
+int32_t ojx_e8t_enable_peer_access(int32_t peer_device);
+
+/*
  * Prefill-shape linear (large M) on the tcgen05 tensor cores.  Same contract as ojx_e8t_gemv;
  * replaces the reference's TileLang builder (ojasx2/tilelang_kernels.py:277-363) and the
  * unpack + F.linear path (lattice.py:613-624).  Requires K % 256 == 0, group 32, bf16 or fp16 x.

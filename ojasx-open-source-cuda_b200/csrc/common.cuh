@@ -138,7 +138,7 @@ int32_t gemv_static_scratch_impl(const void* x, int x_dtype, int64_t M, const ui
 int32_t gemv_tiles_impl(int64_t N, int64_t K);
 int32_t gemv_kchunks_impl(int64_t K);
 int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
-                          int x_dtype, int y_dtype, int needs_reduce, cudaStream_t s);
+                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world, cudaStream_t s);
 size_t  gemm_workspace_bytes_impl(int64_t M, int64_t N, int64_t K);
 int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                   const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,

@@ -70,6 +70,21 @@ __device__ __forceinline__ void store_any(void* y, int y_dtype, int64_t idx, flo
     else if (y_dtype == OJX_F16) static_cast<__half*>(y)[idx] = __float2half_rn(v);
     else static_cast<float*>(y)[idx] = v;
 }
+// Output-column sharding across GPUs: every rank owns an identically laid out output window, and a kernel
+// can store its results into all of them (its own at offset 0, the peers' through their mapped addresses)
+// instead of leaving the exchange to a separate all-gather.  delta[r] is the byte distance from this GPU's
+// window to rank r's; world == 1 with delta[0] == 0 is the single-GPU case.
+struct PeerMap {
+    int64_t delta[8];
+    int world;
+    int pad;
+};
+inline PeerMap peer_map_self() { PeerMap m = {}; m.world = 1; return m; }
+// The copies for the other ranks (delta != 0), kept out of line: rare, and the callers run at the register cap.
+__device__ __noinline__ void store_peers(const PeerMap& pm, void* y, int y_dtype, int64_t idx, float v) {
+    for (int r = 0; r < pm.world; ++r)
+        if (pm.delta[r] != 0) store_any(static_cast<uint8_t*>(y) + pm.delta[r], y_dtype, idx, v);
+}
 template <bool kBf16> __device__ __forceinline__ float load_act(const void* p, int64_t idx) {
     if (kBf16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
     return __half2float(static_cast<const __half*>(p)[idx]);
@@ -230,7 +245,7 @@ template <int NB, int COPIES> constexpr size_t gemv_smem_bytes() {
 template <bool kBf16, int NB, int COPIES>
 __global__ void __launch_bounds__(kGemvBlock, 1)
 gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_constant__ ojx_e8t_gemv_problem single,
-                int count, int total_items, int M, int y_dtype) {
+                int count, int total_items, int M, int y_dtype, const __grid_constant__ PeerMap peers) {
     // A single problem travels by value in the kernel parameters; a list lives in device memory.
     const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -322,6 +337,7 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
                         } else {
                             if (P.bias != nullptr) v += load_act<kBf16>(P.bias, row);
                             store_any(P.y, y_dtype, (int64_t)col * rc.N + row, v);
+                            if (peers.world > 1) store_peers(peers, P.y, y_dtype, (int64_t)col * rc.N + row, v);
                         }
                     }
                 }
@@ -451,9 +467,9 @@ gemv_mma_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
 
 // Sums the K-chunk partials of every problem that has them (fixed order), adds bias, casts.
 template <bool kBf16>
-__global__ void __launch_bounds__(256) gemv_reduce_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev,
+__global__ void __launch_bounds__(256, 3) gemv_reduce_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev,
                                                            const __grid_constant__ ojx_e8t_gemv_problem single,
-                                                           int count, int M, int y_dtype) {
+                                                           int count, int M, int y_dtype, const __grid_constant__ PeerMap peers) {
     const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
     for (int p = blockIdx.y; p < count; p += gridDim.y) {
         const ojx_e8t_gemv_problem& P = probs[p];
@@ -466,6 +482,9 @@ __global__ void __launch_bounds__(256) gemv_reduce_kernel(const ojx_e8t_gemv_pro
             for (int c = 0; c < kc; ++c) s += P.partial[(int64_t)c * total + i];
             if (P.bias != nullptr) s += load_act<kBf16>(P.bias, i % P.N);
             store_any(P.y, y_dtype, i, s);
+#pragma unroll 1
+            for (int r = 0; r < peers.world; ++r)                  // the other ranks' windows (nothing when world == 1)
+                if (peers.delta[r] != 0) store_any(static_cast<uint8_t*>(P.y) + peers.delta[r], y_dtype, i, s);
         }
     }
 }

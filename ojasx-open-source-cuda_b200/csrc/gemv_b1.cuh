@@ -94,7 +94,7 @@ __device__ __forceinline__ void b1_next(B1Cursor& c, const ojx_e8t_gemv_problem*
 
 __global__ void __launch_bounds__(kGemvThreads, 1)
 gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_constant__ ojx_e8t_gemv_problem single,
-               int count, int total_items, int y_dtype) {
+               int count, int total_items, int y_dtype, const __grid_constant__ PeerMap peers) {
     const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
     extern __shared__ __align__(128) uint8_t smem[];
     uint32_t* lut = reinterpret_cast<uint32_t*>(smem);
@@ -196,6 +196,7 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
                 else {
                     if (P.bias != nullptr) sum += __bfloat162float(static_cast<const __nv_bfloat16*>(P.bias)[row]);
                     store_any(P.y, y_dtype, row, sum);
+                    if (peers.world > 1) store_peers(peers, P.y, y_dtype, row, sum);
                 }
             }
             __syncwarp();
@@ -338,7 +339,7 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
 }
 
 static int32_t launch_gemv_b1(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
-                              int y_dtype, cudaStream_t s) {
+                              int y_dtype, const PeerMap& peers, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(gemv_b1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kB1SmemBytes);
@@ -348,7 +349,7 @@ static int32_t launch_gemv_b1(const ojx_e8t_gemv_problem* probs, const ojx_e8t_g
     const int sms = num_sms();
     const int per = (total + sms - 1) / sms;
     const int grid = (total + per - 1) / per;
-    gemv_b1_kernel<<<grid, kGemvThreads, kB1SmemBytes, s>>>(probs, single, count, total, y_dtype);
+    gemv_b1_kernel<<<grid, kGemvThreads, kB1SmemBytes, s>>>(probs, single, count, total, y_dtype, peers);
     return launch_status();
 }
 

@@ -58,7 +58,7 @@ __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
 template <int NBLK, bool kF16, bool kXF16>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_constant__ ojx_e8t_gemv_problem single,
-               int count, int total_items, int M, int y_dtype) {
+               int count, int total_items, int M, int y_dtype, const __grid_constant__ PeerMap peers) {
     using Cfg = BnCfg<NBLK>;
     static_assert(kF16 || !kXF16, "fp16 activations take the fp16 form");
     const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
@@ -190,6 +190,7 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
                 else {
                     if (P.bias != nullptr) sum += load_any(P.bias, kXF16 ? OJX_F16 : OJX_BF16, row);
                     store_any(P.y, y_dtype, (int64_t)col * rN + row, sum);
+                    if (peers.world > 1) store_peers(peers, P.y, y_dtype, (int64_t)col * rN + row, sum);
                 }
             }
         }
@@ -429,7 +430,7 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
 
 template <int NBLK, bool kF16, bool kXF16>
 static int32_t launch_gemv_bn(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
-                              int M, int y_dtype, cudaStream_t s) {
+                              int M, int y_dtype, const PeerMap& peers, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(gemv_bn_kernel<NBLK, kF16, kXF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -440,7 +441,7 @@ static int32_t launch_gemv_bn(const ojx_e8t_gemv_problem* probs, const ojx_e8t_g
     const int sms = num_sms();
     const int per = (total + sms - 1) / sms;
     const int grid = (total + per - 1) / per;
-    gemv_bn_kernel<NBLK, kF16, kXF16><<<grid, kGemvThreads, BnCfg<NBLK>::kSmem, s>>>(probs, single, count, total, M, y_dtype);
+    gemv_bn_kernel<NBLK, kF16, kXF16><<<grid, kGemvThreads, BnCfg<NBLK>::kSmem, s>>>(probs, single, count, total, M, y_dtype, peers);
     return launch_status();
 }
 

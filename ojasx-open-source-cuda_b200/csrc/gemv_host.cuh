@@ -30,7 +30,7 @@ size_t gemv_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
 
 template <bool kBf16, int NB>
 static int32_t launch_gemv(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
-                           int M, int y_dtype, cudaStream_t s) {
+                           int M, int y_dtype, const PeerMap& peers, cudaStream_t s) {
     static bool configured = false;
     constexpr int COPIES = 4;
     const size_t smem = gemv_smem_bytes<NB, COPIES>();
@@ -42,24 +42,30 @@ static int32_t launch_gemv(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv
     const int sms = num_sms();
     const int per = (total + sms - 1) / sms;
     const int grid = (total + per - 1) / per;
-    gemv_mma_kernel<kBf16, NB, COPIES><<<grid, kGemvBlock, smem, s>>>(probs, single, count, total, M, y_dtype);
+    gemv_mma_kernel<kBf16, NB, COPIES><<<grid, kGemvBlock, smem, s>>>(probs, single, count, total, M, y_dtype, peers);
     return launch_status();
 }
 
 // bf16 activations: one row -> gemv_b1 (int8), 2-8 rows -> gemv_bn int8 form, 9-16 rows -> gemv_bn fp16 form.
 static int32_t dispatch_gemv(bool bf16, const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count,
-                             int total, int M, int y_dtype, cudaStream_t s) {
-    if (bf16 && M == 1) return launch_gemv_b1(probs, single, count, total, y_dtype, s);
-    if (bf16) return M <= 8 ? launch_gemv_bn<1, false, false>(probs, single, count, total, M, y_dtype, s)
-                            : launch_gemv_bn<2, true, false>(probs, single, count, total, M, y_dtype, s);
+                             int total, int M, int y_dtype, const PeerMap& peers, cudaStream_t s) {
+    if (bf16 && M == 1) return launch_gemv_b1(probs, single, count, total, y_dtype, peers, s);
+    if (bf16) return M <= 8 ? launch_gemv_bn<1, false, false>(probs, single, count, total, M, y_dtype, peers, s)
+                            : launch_gemv_bn<2, true, false>(probs, single, count, total, M, y_dtype, peers, s);
     // fp16 activations: 9-16 rows share the scale-folded fp16 kernel (the activations need no conversion);
     // up to 8 rows take the 16-bit kernel, which walks every 32-row tile as two 16-row halves
-    return M <= 8 ? launch_gemv<false, 1>(probs, single, count, 2 * total, M, y_dtype, s)
-                  : launch_gemv_bn<2, true, true>(probs, single, count, total, M, y_dtype, s);
+    return M <= 8 ? launch_gemv<false, 1>(probs, single, count, 2 * total, M, y_dtype, peers, s)
+                  : launch_gemv_bn<2, true, true>(probs, single, count, total, M, y_dtype, peers, s);
 }
 
 int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
-                          int x_dtype, int y_dtype, int needs_reduce, cudaStream_t s) {
+                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world, cudaStream_t s) {
+    OJX_RETURN_IF(world < 1 || world > 8 || (world > 1 && !peer_delta), OJX_ERR_SHAPE);
+    PeerMap peers = peer_map_self();
+    if (peer_delta != nullptr) {
+        peers.world = world;
+        for (int r = 0; r < world; ++r) peers.delta[r] = peer_delta[r];
+    }
     OJX_RETURN_IF(!problems, OJX_ERR_NULL);
     OJX_RETURN_IF(count <= 0 || total_tiles <= 0 || M < 1 || M > 16, OJX_ERR_SHAPE);
     OJX_RETURN_IF(x_dtype != OJX_BF16 && x_dtype != OJX_F16, OJX_ERR_DTYPE);
@@ -67,13 +73,13 @@ int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int t
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
     const bool bf = x_dtype == OJX_BF16;
     ojx_e8t_gemv_problem none = {};
-    const int32_t st = dispatch_gemv(bf, problems, none, count, total_tiles, (int)M, y_dtype, s);
+    const int32_t st = dispatch_gemv(bf, problems, none, count, total_tiles, (int)M, y_dtype, peers, s);
     OJX_RETURN_IF(st != OJX_OK, st);
     if (!needs_reduce) return OJX_OK;
     // Problems whose K spans several chunks carry a partial buffer; the reduce pass skips the rest.
     dim3 grid(64, count > 64 ? 64 : count);
-    if (bf) gemv_reduce_kernel<true><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype);
-    else gemv_reduce_kernel<false><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype);
+    if (bf) gemv_reduce_kernel<true><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype, peers);
+    else gemv_reduce_kernel<false><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype, peers);
     return launch_status();
 }
 
@@ -98,12 +104,12 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         h.N = (int)N; h.K = (int)K; h.tile_begin = 0; h.reserved = 0;
         const int total = gemv_row_tiles32((int)N) * kc;
         const bool bf = x_dtype == OJX_BF16;
-        const int32_t st = dispatch_gemv(bf, nullptr, h, 1, total, (int)M, y_dtype, s);
+        const int32_t st = dispatch_gemv(bf, nullptr, h, 1, total, (int)M, y_dtype, peer_map_self(), s);
         OJX_RETURN_IF(st != OJX_OK, st);
         if (kc > 1) {
             dim3 grid(64, 1);
-            if (bf) gemv_reduce_kernel<true><<<grid, 256, 0, s>>>(nullptr, h, 1, (int)M, y_dtype);
-            else gemv_reduce_kernel<false><<<grid, 256, 0, s>>>(nullptr, h, 1, (int)M, y_dtype);
+            if (bf) gemv_reduce_kernel<true><<<grid, 256, 0, s>>>(nullptr, h, 1, (int)M, y_dtype, peer_map_self());
+            else gemv_reduce_kernel<false><<<grid, 256, 0, s>>>(nullptr, h, 1, (int)M, y_dtype, peer_map_self());
         }
         return launch_status();
     }

@@ -85,7 +85,26 @@ int32_t ojx_e8t_gemv_kchunks(int64_t K) { return ojx::gemv_kchunks_impl(K); }
 
 int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles, int64_t M,
                              int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce, void* stream) {
-    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, (cudaStream_t)stream);
+    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, nullptr, 1, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_gemv_grouped_peers(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles, int64_t M,
+                                   int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
+                                   const int64_t* peer_delta, int32_t world, void* stream) {
+    OJX_RETURN_IF(!peer_delta, OJX_ERR_NULL);
+    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, peer_delta, world, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_enable_peer_access(int32_t peer_device) {
+    int cur = -1, can = 0;
+    if (cudaGetDevice(&cur) != cudaSuccess) { ojx::last_cuda_error() = cudaGetLastError(); return OJX_ERR_LAUNCH; }
+    if (peer_device == cur) return OJX_OK;
+    if (cudaDeviceCanAccessPeer(&can, cur, peer_device) != cudaSuccess) { ojx::last_cuda_error() = cudaGetLastError(); return OJX_ERR_LAUNCH; }
+    if (!can) return OJX_ERR_UNSUPPORTED;
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) { (void)cudaGetLastError(); return OJX_OK; }
+    if (e != cudaSuccess) { ojx::last_cuda_error() = e; (void)cudaGetLastError(); return OJX_ERR_LAUNCH; }
+    return OJX_OK;
 }
 
 size_t ojx_e8t_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) { return ojx::gemm_workspace_bytes_impl(M, N, K); }

@@ -85,3 +85,56 @@ class ColumnShardedLinear:
         return torch.cat([buf[r, :, : s] for r, s in enumerate(self.sizes)], dim=1)
 
     __call__ = forward
+
+
+class PeerWindow:
+    """One buffer of the same size on every rank of a single-node process group, each rank holding a mapping of
+    every other rank's copy (CUDA IPC), for kernels that store their shard of a result into all ranks' buffers
+    themselves - the fused form of "compute a column shard, then all-gather"
+    (see ``GroupedGemv(..., peer_delta=window.delta)``).
+
+    ``local`` is this rank's buffer, laid out ``[world, ...]`` by the caller (slot r belongs to rank r);
+    ``delta[r]`` is the byte distance from ``local`` to rank r's copy as mapped here (0 for this rank).
+    The ranks must meet (``fence()``) between the kernels that write a window and anyone reading it.
+    Construction is collective; it raises if the device memory cannot be shared between the ranks.
+    """
+
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device, group=None):
+        import torch.distributed as dist
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        from . import _cabi
+        my_index = device.index if device.index is not None else torch.cuda.current_device()
+        self.local = torch.zeros(numel, dtype=dtype, device=device)
+        handle = self.local.untyped_storage()._share_cuda_()
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self._peer_storages = []
+        self.delta = []
+        with torch.cuda.device(device):
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.delta.append(0)
+                    continue
+                # Kernels of THIS device will store into the peer's memory: peer access must be on in that direction,
+                # and the handle is opened with this device current (h[0] is the exporter's device index).
+                _cabi.check(_cabi.lib().ojx_e8t_enable_peer_access(int(h[0])), "ojx_e8t_enable_peer_access")
+                storage = torch.UntypedStorage._new_shared_cuda(my_index, *h[1:])
+                self._peer_storages.append(storage)             # keeps the mapping alive
+                self.delta.append(int(storage.data_ptr()) - int(self.local.data_ptr()))
+        self._token = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def close(self) -> None:
+        """Drops this rank's mappings of the peers' buffers.  Collective by convention: every rank closes before any
+        rank frees its own buffer or exits."""
+        self._peer_storages.clear()
+        self.delta = [0] * len(self.delta)
+
+    def fence(self) -> None:
+        """All ranks' earlier kernels on their current streams have completed once this returns on the stream
+        (one tiny all-reduce: stream-ordered, no host synchronisation)."""
+        import torch.distributed as dist
+        dist.all_reduce(self._token, group=self.group)

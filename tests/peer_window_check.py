@@ -1,0 +1,61 @@
+"""Two or more ranks on one node: the grouped GEMV that stores its column shard into every rank's output window
+must leave every window equal to an NCCL all-gather of the shards.  Run by tests/test_multi_gpu.py under torchrun."""
+
+import importlib
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    dist.init_process_group("nccl", device_id=dev)
+    P = importlib.import_module("ojasx-open-source-cuda_b200")
+    ops, sharding = P.ops, importlib.import_module("ojasx-open-source-cuda_b200.sharding")
+    ok = True
+    for (k, n, m, mats) in [(4096, 1024, 1, 3), (4096, 4096, 4, 2), (14336, 1024, 16, 2)]:
+        n0, n1 = sharding.shard_rows(n, world, rank)
+        nl = n1 - n0
+        assert all(sharding.shard_rows(n, world, r)[1] - sharding.shard_rows(n, world, r)[0] == nl for r in range(world))
+        window = sharding.PeerWindow(world * mats * m * nl, torch.bfloat16, dev)
+        slots = window.local.view(world, mats, m, nl)
+        x = ops.generate(m * k, 11, 1.0, torch.bfloat16, dev).view(m, k)
+        entries, plain = [], []
+        y_plain = torch.zeros((mats, m, nl), dtype=torch.bfloat16, device=dev)
+        for j in range(mats):
+            w = ops.generate(nl * k, 100 + j, 0.02, torch.float16, dev, start=n0 * k).view(nl, k)
+            pk, sc = ops.encode(w, 32)
+            entries.append((x, pk, sc, None, slots[rank, j]))
+            plain.append((x, pk, sc, None, y_plain[j]))
+        fused = ops.GroupedGemv(entries, [(nl, k)] * mats, peer_delta=window.delta)
+        ref = ops.GroupedGemv(plain, [(nl, k)] * mats)
+        for _ in range(2):
+            fused()
+            window.fence()
+        ref()
+        gathered = torch.empty((world, mats, m, nl), dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(gathered.view(world, -1), y_plain.view(-1))
+        torch.cuda.synchronize()
+        same = torch.equal(slots, gathered)
+        window.close()
+        dist.barrier()
+        if not same:
+            ok = False
+            print(f"rank {rank}: mismatch at K={k} N={n} M={m}", flush=True)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("PEER_WINDOW_OK" if int(flag.item()) == 1 else "PEER_WINDOW_MISMATCH", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
