@@ -156,7 +156,7 @@ int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count
  * window at the place of this rank's shard, and peer_delta[r] (r < world, world <= 8) is the byte
  * distance from this rank's window to rank r's window as mapped into this process (0 for this rank;
  * e.g. from CUDA IPC handles).  The kernel stores each result `world` times - plain stores over
- * NVLink, no device-side waiting, no multicast loads.  The caller orders the exchange: a peer may
+ * NVLink, no device-side waiting, nothing is loaded from a peer.  The caller orders the exchange: a peer may
  * read its window only after this launch has completed on this rank's stream and the ranks have met
  * (one small collective or barrier per step instead of one all-gather per launch).
  */
