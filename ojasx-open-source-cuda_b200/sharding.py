@@ -86,6 +86,40 @@ class ColumnShardedLinear:
 
     __call__ = forward
 
+    # ---- fused form: the decode kernel stores this rank's columns into every rank's output window ----
+    def enable_fused_gather(self, device: torch.device, x_dtype: torch.dtype = torch.bfloat16,
+                            y_dtype: torch.dtype = torch.bfloat16, max_rows: int = 16) -> None:
+        """Collective.  Builds two alternating peer-mapped output windows ``[world, max_rows, N / world]`` (a window
+        is rewritten only two calls later, after every rank has passed the fence of the call in between) for
+        ``forward_fused``.  Needs equal shards, K % 256 == 0 and group 32."""
+        if len(set(self.sizes)) != 1 or self.K % 256 != 0 or self.g != 32:
+            raise ValueError("fused gather needs equal column shards, K % 256 == 0 and group_size 32")
+        self._fg = {"dev": device, "xd": x_dtype, "yd": y_dtype, "rows": int(max_rows), "calls": 0, "groups": {},
+                    "windows": [PeerWindow(self.world * max_rows * self.sizes[0], y_dtype, device, self.group) for _ in range(2)]}
+
+    def forward_fused(self, x2d: torch.Tensor) -> torch.Tensor:
+        """``[M, N]`` on every rank for M <= max_rows: one kernel launch that writes all ranks' windows, one fence.
+        The result is a view of this rank's window: use it before the call after next."""
+        from . import ops
+        fg, m, nl = self._fg, int(x2d.shape[0]), self.sizes[0]
+        if not (1 <= m <= fg["rows"]) or x2d.dtype != fg["xd"]:
+            raise ValueError("forward_fused: row count or dtype outside what enable_fused_gather set up")
+        which = fg["calls"] % 2
+        fg["calls"] += 1
+        key = (m, which)
+        if key not in fg["groups"]:
+            window = fg["windows"][which]
+            x_stage = torch.empty((m, self.K), dtype=fg["xd"], device=fg["dev"])
+            slot = window.local.view(self.world, fg["rows"], nl)[self.rank, :m]
+            fg["groups"][key] = (x_stage, ops.GroupedGemv([(x_stage, self.packed, self.scales, self.bias, slot)],
+                                                          [(nl, self.K)], peer_delta=window.delta))
+        x_stage, group = fg["groups"][key]
+        x_stage.copy_(x2d)
+        group()
+        window = fg["windows"][which]
+        window.fence()
+        return window.local.view(self.world, fg["rows"], nl)[:, :m].permute(1, 0, 2).reshape(m, self.N)
+
 
 class PeerWindow:
     """One buffer of the same size on every rank of a single-node process group, each rank holding a mapping of

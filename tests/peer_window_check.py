@@ -49,6 +49,24 @@ def main():
         if not same:
             ok = False
             print(f"rank {rank}: mismatch at K={k} N={n} M={m}", flush=True)
+    # the module form: ColumnShardedLinear.forward_fused against its NCCL forward, several calls in a row
+    n, k = 2048, 4096
+    w = ops.generate(n * k, 77, 0.02, torch.float16, dev).view(n, k)
+    pk, sc = ops.encode(w, 32)
+    bias = ops.generate(n, 78, 0.1, torch.bfloat16, dev)
+    lin = sharding.ColumnShardedLinear(pk, sc, bias, n, k, 32, rank=rank, world_size=world)
+    lin.enable_fused_gather(dev)
+    for call, m in enumerate([1, 4, 16, 4, 1]):
+        x = ops.generate(m * k, 200 + call, 1.0, torch.bfloat16, dev).view(m, k)
+        y_fused = lin.forward_fused(x).clone()
+        y_nccl = lin.forward(x)
+        torch.cuda.synchronize()
+        if not torch.equal(y_fused, y_nccl):
+            ok = False
+            print(f"rank {rank}: module mismatch at call {call} (M={m})", flush=True)
+    for wdw in lin._fg["windows"]:
+        wdw.close()
+    dist.barrier()
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
