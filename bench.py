@@ -533,11 +533,73 @@ def run_extras(torch, ops, dev, groups, packed_store, hbm_peak, tf_peak):
     gbs = n * k * 2.25 / (ms * 1e-3) / 1e9
     out["encoder"] = {"rows": n, "cols": k, "dtype": "f16", "ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak,
                       "Gweights_per_s": n * k / (ms * 1e-3) / 1e9}
+    out["stack"] = run_stack(torch, ops, dev, timed, hbm_peak)
     # decoder (unpack): packed codes + scales -> dense fp16 weights, 0.25 B read + 2 B written per weight
     ms = timed(lambda: ops.decode(pk, sc, (n, k), torch.float16, out=w), 3)
     gbs = n * k * 2.25 / (ms * 1e-3) / 1e9
     out["decoder"] = {"rows": n, "cols": k, "dtype": "f16", "ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak}
     return out
+
+
+def run_stack(torch, ops, dev, timed, hbm_peak, layers=32):
+    """The linears of a Llama-3-8B-shaped decoder stack (32 layers x {q, k, v, o, gate, up, down} = 224 matrices,
+    1.74 GB packed) run as a chain with real data flow - q,k,v <- h; a <- o(q); g,u <- a; h <- down(g + u) - four
+    launches per layer (q/k/v grouped, o, gate/up grouped, down).  Attention, norms and activations are not part
+    of the path and are left out; every matrix is distinct, so the weights always come from HBM."""
+    H, KV, F = 4096, 1024, 14336
+    w = torch.empty(F * H, dtype=torch.float16, device=dev)
+
+    def make(n, k, seed):
+        ops.generate(n * k, seed, 0.02, torch.float16, dev, out=w[: n * k])
+        return ops.encode(w[: n * k].view(n, k), 32)
+
+    mats = [[make(*shape, 5000 + 10 * layer + j) for j, shape in enumerate([(H, H), (KV, H), (KV, H), (H, H), (F, H), (F, H), (H, F)])]
+            for layer in range(layers)]
+    packed_bytes = layers * sum(n * k // 4 for n, k in [(H, H), (KV, H), (KV, H), (H, H), (F, H), (F, H), (H, F)])
+    results = []
+    for b in (1, 16):
+        h = ops.generate(b * H, 9, 1.0, torch.bfloat16, dev).view(b, H)
+        q = torch.empty((b, H), dtype=torch.bfloat16, device=dev)
+        kk, v = (torch.empty((b, KV), dtype=torch.bfloat16, device=dev) for _ in range(2))
+        a = torch.empty((b, H), dtype=torch.bfloat16, device=dev)
+        g, u, mid = (torch.empty((b, F), dtype=torch.bfloat16, device=dev) for _ in range(3))
+        steps = []
+        for m in mats:
+            steps.append(ops.GroupedGemv([(h, m[0][0], m[0][1], None, q), (h, m[1][0], m[1][1], None, kk), (h, m[2][0], m[2][1], None, v)],
+                                         [(H, H), (KV, H), (KV, H)]))
+            steps.append(ops.GroupedGemv([(q, m[3][0], m[3][1], None, a)], [(H, H)]))
+            steps.append(ops.GroupedGemv([(a, m[4][0], m[4][1], None, g), (a, m[5][0], m[5][1], None, u)], [(F, H), (F, H)]))
+            steps.append(ops.GroupedGemv([(mid, m[6][0], m[6][1], None, h)], [(H, F)]))
+
+        def forward():
+            for i, st in enumerate(steps):
+                if i % 4 == 3:
+                    torch.add(g, u, out=mid)
+                st()
+
+        ms_eager = timed(forward, 3)
+        # the same chain replayed from a CUDA graph: no per-launch host work
+        ms = ms_eager
+        mode = "eager"
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                forward()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                forward()
+            ms = timed(graph.replay, 3)
+            mode = "cuda graph"
+        except Exception as exc:                                  # noqa: BLE001
+            print(f"[bench] layer-stack graph capture unavailable: {exc}", file=sys.stderr)
+        gbs = packed_bytes / (ms * 1e-3) / 1e9
+        results.append({"batch": b, "layers": layers, "matrices": 7 * layers, "launches": 4 * layers, "ms": ms, "mode": mode,
+                        "ms_eager": ms_eager,
+                        "packed_GBps": gbs, "frac_hbm": gbs / hbm_peak, "tokens_per_s_linears_only": b / (ms * 1e-3)})
+    return results
 
 
 if __name__ == "__main__":

@@ -16,7 +16,7 @@ constexpr int kNumPoints = 3281;
 // (ojx_e8t.cu includes every kernel file), so file-scope statics are shared by all kernels.
 //   g_trit_nibbles[rank]  eight 4-bit fields, field i = coordinate i as {0: 0, 1: +1, 2: -1}
 //   g_raw_to_rank[raw]    base-3 raw value -> rank
-#define OJX_TABLE_QUAL static __device__
+#define OJX_TABLE_QUAL static __device__ __align__(16)
 #define OJX_TABLE_NAME(x) g_##x
 #include "e8t_tables.inc"
 #undef OJX_TABLE_QUAL

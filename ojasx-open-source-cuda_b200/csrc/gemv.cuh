@@ -118,6 +118,7 @@ __device__ __forceinline__ void cursor_load_problem(Cursor& c, const ojx_e8t_gem
 // table walked entry by entry cost the last CTAs ~40 us at the start of every grouped launch).  Every thread of
 // the CTA must call this.
 __device__ __forceinline__ int find_problem(const ojx_e8t_gemv_problem* probs, int count, int item, int scale) {
+    if (count == 1) return 0;                                  // single-problem launches (a layer at a time) skip the pass
     int found = 0;
     for (int base = 0; base < count; base += (int)blockDim.x) {
         const int t = base + (int)threadIdx.x;

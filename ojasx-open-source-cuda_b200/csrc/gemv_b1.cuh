@@ -104,6 +104,7 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const uint32_t bar_full = smem_u32(tail), bar_empty = bar_full + 8 * kB1Stages;
     const uint32_t bar_rfull = bar_empty + 8 * kB1Stages, bar_rempty = bar_rfull + 8 * kB1Red;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 16 * kB1Stages + 16 * kB1Red);
+    const uint32_t bar_lut = smem_u32(tail) + 16 * kB1Stages + 16 * kB1Red + 16;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -117,8 +118,13 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
             mbar_init(bar_rfull + 8 * b, kGemvWarps);       // every warp has parked its partial sums
             mbar_init(bar_rempty + 8 * b, 1);               // the summing warp is done with the buffer
         }
+        mbar_init(bar_lut, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the lookup table's shared-memory image (every entry four times) arrives as ONE bulk copy while the kernel
+        // sets itself up; nobody builds it
+        mbar_expect_tx(bar_lut, kNumPoints * 16);
+        bulk_load(smem_u32(lut), g_lut_i8x4, kNumPoints * 16, bar_lut);
     }
     __syncthreads();
 
@@ -159,24 +165,6 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     };
     for (int n = 0; n < kB1Ahead && n < nitems; ++n) issue_next();
 
-    // The lookup table is built while the first items are in flight: one global read per rank, stored as its
-    // kB1Copies interleaved copies with a single 16-byte store.
-    static_assert(kB1Copies == 4, "one uint4 per table entry");
-    {
-        constexpr int kPerThread = (kNumPoints + kGemvThreads - 1) / kGemvThreads;
-        uint32_t v[kPerThread];
-#pragma unroll
-        for (int j = 0; j < kPerThread; ++j) {                 // all loads first: one global latency, not seven
-            const int e = tid + j * kGemvThreads;
-            v[j] = e < kNumPoints ? g_trit_nibbles[e] : 0u;
-        }
-#pragma unroll
-        for (int j = 0; j < kPerThread; ++j) {
-            const int e = tid + j * kGemvThreads;
-            if (e < kNumPoints) reinterpret_cast<uint4*>(lut)[e] = make_uint4(v[j], v[j], v[j], v[j]);
-        }
-    }
-    __syncthreads();
 
     // ---- reduction of item n by warp n mod 16, kB1RedLag items after it was computed ----
     B1Cursor rc = first;
@@ -216,6 +204,7 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     int cur_prob = -1, cur_chunk = -1;
     B1Cursor cc = first;
 
+    b1_wait(bar_lut, 0u, abort_flag, 35);                          // the table has landed
     for (int n = 0; n < nitems; ++n) {
         const int s = n % kB1Stages, b = n % kB1Red;
         if (issued < nitems) issue_next();                         // keeps kB1Ahead items in flight

@@ -75,6 +75,7 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     const int g = lane >> 2, t = lane & 3;
     constexpr uint32_t kItemDescOffset = kB1Rows * kGemvMaxCodePitch - 16;      // free: row pitches end in 16 bytes of padding
     const uint32_t red_desc = smem_u32(tail) + 128;                              // one 16-byte item descriptor per reduction buffer
+    const uint32_t bar_lut = smem_u32(tail) + 176;
 
     if (tid == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) {
@@ -85,8 +86,12 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
             mbar_init(bar_rfull + 8 * b, kGemvWarps);       // every warp has parked its partial sums
             mbar_init(bar_rempty + 8 * b, kGemvWarps);      // every warp has summed its share of the outputs
         }
+        mbar_init(bar_lut, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the lookup table's shared-memory image arrives as ONE bulk copy while the kernel sets itself up
+        mbar_expect_tx(bar_lut, kNumPoints * 16);
+        bulk_load(smem_u32(lut), kF16 ? g_lut_f16sel : g_lut_i8x4, kNumPoints * 16, bar_lut);
     }
     __syncthreads();
 
@@ -130,40 +135,6 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     };
     for (int n = 0; n < Cfg::kAhead && n < nitems; ++n) issue_next();
 
-    // The lookup table is built while the first items are in flight: one global read per rank, stored as its
-    // interleaved copies with a single 16-byte store.
-    static_assert(Cfg::kCopies == 4, "one uint4 per table entry");
-    {
-        constexpr int kPerThread = (kNumPoints + kGemvThreads - 1) / kGemvThreads;
-        uint32_t nib[kPerThread];
-#pragma unroll
-        for (int j = 0; j < kPerThread; ++j) {                 // all loads first: one global latency, not seven
-            const int e = tid + j * kGemvThreads;
-            nib[j] = e < kNumPoints ? g_trit_nibbles[e] : 0u;
-        }
-#pragma unroll
-        for (int j = 0; j < kPerThread; ++j) {
-            const int e = tid + j * kGemvThreads;
-            if (e >= kNumPoints) continue;
-            const uint32_t v = nib[j];
-            if constexpr (!kF16) {
-                reinterpret_cast<uint4*>(lut)[e] = make_uint4(v, v, v, v);
-            } else {
-                // two copies of a 64-bit entry: four 16-bit permute selectors, one per pair of coordinates; a
-                // coordinate code c (0: zero, 1: plus, 2: minus) selects low byte c of the first pool word and high
-                // byte c of the second (index 4 + c)
-                uint32_t sel[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t ca = (v >> (8 * q)) & 0xFu, cb = (v >> (8 * q + 4)) & 0xFu;
-                    sel[q] = ca | ((ca + 4) << 4) | (cb << 8) | ((cb + 4) << 12);
-                }
-                const uint32_t w0 = sel[0] | (sel[1] << 16), w1 = sel[2] | (sel[3] << 16);
-                reinterpret_cast<uint4*>(lut)[e] = make_uint4(w0, w1, w0, w1);
-            }
-        }
-    }
-    __syncthreads();
 
     // ---- reduction: every warp sums 16 * NBLK of the item's 256 * NBLK outputs over the 16 warps, in warp order ----
     int reduced = 0;
@@ -220,6 +191,7 @@ gemv_bn_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
     struct { int prob, chunk, tile, act, K; } cc;
     cc.K = 0;
 
+    b1_wait(bar_lut, 0u, abort_flag, 45);                          // the table has landed
     for (int n = 0; n < nitems; ++n) {
         const int s = n % Cfg::kStages, b = n % Cfg::kRed;
         if (issued < nitems) issue_next();
