@@ -210,24 +210,23 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
         if (issued < nitems) issue_next();                         // keeps kB1Ahead items in flight
 
         if (cc.prob != cur_prob || cc.chunk != cur_chunk) {
-            // quantise this warp's 256 activations: lane (g, t) with g >> 1 == t holds x[64t + 32(g&1) + 0..31]
+            // Quantise this warp's 256 activations.  Every lane converts the eight it loads (one 16-byte load) and
+            // the MMA fragments are then handed out by shuffles: lane (g, t) with g >> 1 == t owns
+            // x[64t + 32(g&1) + 0..31], i.e. what lanes 8t + 4(g&1) + 0..3 converted.
             cur_prob = cc.prob;
             cur_chunk = cc.chunk;
-            const bool mine = warp < cc.act && (g >> 1) == t;
-            const uint16_t* xp = static_cast<const uint16_t*>(probs[cc.prob].x) + (cc.chunk * cc.act + warp) * 256 + t * 64 + (g & 1) * 32;
-            float v[32];
+            const bool live = warp < cc.act;
+            const uint16_t* xp = static_cast<const uint16_t*>(probs[cc.prob].x) + (cc.chunk * cc.act + warp) * 256 + lane * 8;
+            uint4 q = make_uint4(0, 0, 0, 0);
+            if (live) q = __ldg(reinterpret_cast<const uint4*>(xp));
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+            float v[8];
             float amax = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 q = make_uint4(0, 0, 0, 0);
-                if (mine) q = __ldg(reinterpret_cast<const uint4*>(xp + j * 8));
-                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    v[j * 8 + 2 * i] = __uint_as_float(w[i] << 16);
-                    v[j * 8 + 2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-                    amax = fmaxf(amax, fmaxf(fabsf(v[j * 8 + 2 * i]), fabsf(v[j * 8 + 2 * i + 1])));
-                }
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+                amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
@@ -235,19 +234,25 @@ gemv_b1_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_
             if (amax > 0.f) e = max(-100, min(100, (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127 - 12));
             const float down = __uint_as_float((uint32_t)(127 - e) << 23);
             upscale = __uint_as_float((uint32_t)(127 + e) << 23);
+            uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const bool on = mine && ((j >> 2) == (g & 1));     // steps 0-3 feed group 2t, steps 4-7 group 2t+1
-                uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
+            for (int i = 0; i < 8; ++i) {
+                const int X = __float2int_rn(v[i] * down);                         // |X| < 8192
+                const int hi = (X + 64) >> 7, lo = X - (hi << 7);                 // X = 128 hi + lo, lo in [-64, 63]
+                hw[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
+                lw[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
+            }
+            const bool owner = (g >> 1) == t;
+            const int src = 8 * t + 4 * (g & 1);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int X = __float2int_rn(v[(j & 3) * 8 + i] * down);     // |X| < 8192
-                    const int hi = (X + 64) >> 7, lo = X - (hi << 7);             // X = 128 hi + lo, lo in [-64, 63]
-                    hw[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
-                    lw[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
-                }
-                xh[j][0] = on ? hw[0] : 0u; xh[j][1] = on ? hw[1] : 0u;
-                xl[j][0] = on ? lw[0] : 0u; xl[j][1] = on ? lw[1] : 0u;
+            for (int j = 0; j < 4; ++j) {                                          // steps 0-3 feed group 2t, steps 4-7 group 2t+1
+                const uint32_t h0 = __shfl_sync(0xFFFFFFFFu, hw[0], src + j), h1 = __shfl_sync(0xFFFFFFFFu, hw[1], src + j);
+                const uint32_t l0 = __shfl_sync(0xFFFFFFFFu, lw[0], src + j), l1 = __shfl_sync(0xFFFFFFFFu, lw[1], src + j);
+                const bool lo_half = owner && (g & 1) == 0, hi_half = owner && (g & 1) == 1;
+                xh[j][0] = lo_half ? h0 : 0u; xh[j][1] = lo_half ? h1 : 0u;
+                xl[j][0] = lo_half ? l0 : 0u; xl[j][1] = lo_half ? l1 : 0u;
+                xh[j + 4][0] = hi_half ? h0 : 0u; xh[j + 4][1] = hi_half ? h1 : 0u;
+                xl[j + 4][0] = hi_half ? l0 : 0u; xl[j + 4][1] = hi_half ? l1 : 0u;
             }
         }
 
