@@ -44,6 +44,19 @@ NCU_TRAFFIC = {
 TRAFFIC_PER_LAUNCH = NCU_TRAFFIC["gemv_bn_kernel<2,true,false> (16 rows)"]["dram_bytes"]
 
 
+class _SubWindow:
+    """A slice of a peer-mapped arena: same offsets on every rank, so the arena's deltas apply."""
+
+    def __init__(self, arena, offset, numel):
+        self.arena, self.local, self.delta = arena, arena.local[offset: offset + numel], arena.delta
+
+    def fence(self):
+        self.arena.fence()
+
+    def close(self):
+        self.arena.close()
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -193,6 +206,10 @@ def main():
     ap.add_argument("--rotation", type=int, default=64, help="distinct matrices per shape")
     ap.add_argument("--no-extras", action="store_true", help="skip prefill/encoder/per-shape extras")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--merge", default="off", choices=["auto", "on", "off"],
+                    help="fused gather only: one grouped launch per batch size over all shapes instead of one per shape and "
+                         "batch (auto: from 4 GPUs up); slower at 1 and 2 GPUs, where uneven item sizes cost more than the "
+                         "saved launch start-ups")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: kernels store their column shard into every rank's output window (fused), or NCCL all-gather")
     ap.add_argument("--case", default=None, choices=["gemv", "gemm", "encode", "decode"],
@@ -249,10 +266,14 @@ def main():
     if world > 1 and args.gather == "fused":
         good = 1
         try:
-            for si, (k, n) in enumerate(SHAPES):
-                n0, n1 = sharding.shard_rows(n, world, rank)
-                for b in BATCHES:
-                    windows[(si, b)] = sharding.PeerWindow(world * R * b * (n1 - n0), torch.bfloat16, dev)
+            # ONE peer-mapped arena holds the windows of all (shape, batch) pairs, so every launch shares one delta list
+            sizes = {(si, b): world * R * b * (sharding.shard_rows(n, world, rank)[1] - sharding.shard_rows(n, world, rank)[0])
+                     for si, (k, n) in enumerate(SHAPES) for b in BATCHES}
+            arena = sharding.PeerWindow(sum(sizes.values()), torch.bfloat16, dev)
+            off = 0
+            for key, size in sizes.items():
+                windows[key] = _SubWindow(arena, off, size)
+                off += size
         except Exception as exc:                                  # noqa: BLE001
             print(f"[bench] rank {rank}: peer windows unavailable ({exc}); using NCCL all-gather", file=sys.stderr)
             good = 0
@@ -294,6 +315,18 @@ def main():
             bytes_per_step += R * (n * k // 4) // 1            # whole-job packed bytes (all ranks)
             h2d_per_step += b * k * 2
             d2h_per_step += R * b * n * 2
+    merged = fused and (args.merge == "on" or (args.merge == "auto" and world >= 4))
+    sweep = {}
+    if merged:
+        for b in BATCHES:
+            ents, shps = [], []
+            for si, (k, n) in enumerate(SHAPES):
+                n0, n1 = sharding.shard_rows(n, world, rank)
+                y_all = gathers[(si, b)][0]
+                ents += [(xs[(si, b)], pk, sc, None, y_all[r]) for r, (pk, sc) in enumerate(packed_store[si])]
+                shps += [(n1 - n0, k)] * R
+            sweep[b] = ops.GroupedGemv(ents, shps, peer_delta=windows[(0, b)].delta)
+        launches_per_step = sum(1 + sweep[b].needs_reduce for b in BATCHES)
     del tmp
     torch.cuda.synchronize()
 
@@ -302,6 +335,11 @@ def main():
         # NCCL: the groups are independent, so each all-gather (own buffers, NCCL's stream) overlaps the next
         # group's kernel; the compute stream joins all of them at the end of the pass.
         pending = []
+        if merged:
+            for b in BATCHES:
+                sweep[b]()
+            windows[(0, BATCHES[0])].fence()
+            return
         for b in BATCHES:
             for si in range(len(SHAPES)):
                 groups[(si, b)]()
@@ -404,7 +442,8 @@ def main():
             "config": {"workload": "decode GEMV sweep, Llama-3-8B linear shapes (K->N 4096->4096, 4096->1024, 4096->14336, 14336->4096), "
                                    "batch 1/4/16, bf16 activations, bf16 outputs",
                        "rotation": R, "l2": "inputs larger than L2: %.2f GB of packed weights per pass, a matrix is revisited only after the whole sweep" % (bytes_per_step / 3 / 1e9),
-                       "parallelism": ("output-column shards, kernels store into every rank's output window over NVLink (one fence per pass)" if fused
+                       "parallelism": (("output-column shards, kernels store into every rank's output window over NVLink (one fence per pass)"
+                                        + (", one grouped launch per batch size" if merged else "")) if fused
                                        else "output-column shards + NCCL all-gather") if world > 1 else "single GPU",
                        "launches_per_step": launches_per_step},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s", "frac": achieved / (hbm_peak * world),
