@@ -88,6 +88,13 @@ int32_t ojx_e8t_decode(const uint8_t* packed, const uint16_t* scales, int64_t ro
  * Decode-shape linear (small M): y[M, N] = x[M, K] . W^T (+ bias), W given packed.
  * Replaces _FusedE8GEMMFunction.forward for small batches (ojasx2/math/lattice.py:551-640) and the
  * reference's native fused kernel (ojasx_math_core.hpp:580-634).  fp32 accumulation.
+ * Numerics of the tensor-core path (M <= 16, K % 256 == 0, group 32, bf16 or fp16 x): the weights enter the
+ * MMAs as exact fp16 values coord * scale; fp16 activations are used as they are; bf16 activations are
+ * multiplied by a power of two per (row, 256-wide slice of K) so that the slice maximum lies in [2^14, 2^15)
+ * and converted to fp16 - exact for every element within 2^-29 of its slice maximum, so an activation
+ * outlier does not degrade its neighbours; products are exact and accumulate in fp32.  Inf and NaN in x reach
+ * every output of that activation row (0 * Inf = NaN, as in a dense product).  Other shapes and fp32
+ * activations run a plain fp32 kernel.
  *   x, y       row-major, dtypes x_dtype / y_dtype (bf16, fp16 or fp32)
  *   bias       [N] in x_dtype, or null
  *   group      must be 32 and K % 32 == 0 (every row owns whole groups)
@@ -163,6 +170,23 @@ int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count
 int32_t ojx_e8t_gemv_grouped_peers(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles,
                                    int64_t M, int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
                                    const int64_t* peer_delta, int32_t world, void* stream);
+/*
+ * The general form of the two grouped launches above (they call it with flags = 0; peer_delta may be null,
+ * which means a single rank).  Flags:
+ *   OJX_GEMV_STATIC_WEIGHTS  the caller promises that no kernel still running or queued ahead of this launch in
+ *       `stream` WRITES the packed codes or scales of any problem (they were produced earlier and the producer
+ *       has finished, the normal case for inference).  The launch is then allowed to start while its
+ *       predecessor in the stream drains: it sets itself up and starts streaming weights, and waits for the
+ *       predecessor only before its first read of x and its first write of y (programmatic dependent launch).
+ *       Activations, outputs, bias and partial buffers may depend on the predecessor as usual.  Without the flag
+ *       the launch is ordered like any other kernel.  Works inside stream capture.
+ * No counterpart in the reference.
+ */
+#define OJX_GEMV_STATIC_WEIGHTS 1
+int32_t ojx_e8t_gemv_grouped_ex(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles,
+                                int64_t M, int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
+                                const int64_t* peer_delta, int32_t world, int32_t flags, void* stream);
+
 /* Lets kernels of the current device address memory that lives on `peer_device` (same node, NVLink or PCIe
  * peer): OJX_OK when access is (already) enabled, OJX_ERR_UNSUPPORTED when the two devices cannot be peers.
  * Required once per peer before ojx_e8t_gemv_grouped_peers stores into that peer's window.  No counterpart in

@@ -20,11 +20,12 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libojx_e8t.so")
 
 OJX_F32, OJX_F16, OJX_BF16 = 0, 1, 2
+OJX_GEMV_STATIC_WEIGHTS = 1
 
 EXPORTED_SYMBOLS = (
     "ojx_e8t_version", "ojx_e8t_status_string", "ojx_e8t_encode", "ojx_e8t_decode",
     "ojx_e8t_gemv_workspace_bytes", "ojx_e8t_gemv", "ojx_e8t_gemv_tiles", "ojx_e8t_gemv_kchunks",
-    "ojx_e8t_gemv_grouped", "ojx_e8t_gemv_grouped_peers", "ojx_e8t_enable_peer_access", "ojx_e8t_gemm_workspace_bytes", "ojx_e8t_gemm", "ojx_e8t_gemm_status",
+    "ojx_e8t_gemv_grouped", "ojx_e8t_gemv_grouped_peers", "ojx_e8t_gemv_grouped_ex", "ojx_e8t_enable_peer_access", "ojx_e8t_gemm_workspace_bytes", "ojx_e8t_gemm", "ojx_e8t_gemm_status",
     "ojx_e8t_generate", "ojx_e8t_last_cuda_error", "ojx_e8t_device_status",
     "ojx_e8t_gemv_static_scratch", "ojx_e8t_gemv_static_scratch_capacity",
 )
@@ -111,6 +112,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ojx_e8t_enable_peer_access.argtypes = [i32]
     lib.ojx_e8t_gemv_grouped_peers.restype = i32
     lib.ojx_e8t_gemv_grouped_peers.argtypes = [vp, i32, i32, i64, i32, i32, i32, vp, i32, vp]
+    lib.ojx_e8t_gemv_grouped_ex.restype = i32
+    lib.ojx_e8t_gemv_grouped_ex.argtypes = [vp, i32, i32, i64, i32, i32, i32, vp, i32, i32, vp]
     lib.ojx_e8t_gemm_workspace_bytes.restype = sz
     lib.ojx_e8t_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     lib.ojx_e8t_gemm.restype = i32
@@ -133,7 +136,7 @@ def lib() -> ctypes.CDLL:
             if _lib is None:
                 if not os.path.exists(LIB_PATH):
                     raise RuntimeError(
-                        f"{LIB_PATH} is missing. Build it with __graft_entry__.build() (needs nvcc); "
+                        f"{LIB_PATH} is missing. Build it with this module's build() (needs nvcc); "
                         "this package has no CPU or PyTorch fallback.")
                 handle = ctypes.CDLL(LIB_PATH)
                 _declare(handle)

@@ -11,35 +11,72 @@ namespace ojx {
 
 // ---------------------------------------------------------------------------------------------
 // Encoder: one thread per scale group.
+//
+// Facts the kernels rely on (all checked by the bit-exact tests against the reference's output):
+//   * a ternary vector is valid when its coordinate sum is even, i.e. when raw = sum (q_i + 1) 3^i is even,
+//     so the rank of a valid raw value (its position among the valid ones) is raw / 2: no table;
+//   * clamp(rint(v), -1, 1) and the "other candidate" alt_i share one sign t = (v >= 0 ? +1 : -1): for
+//     q = 0 the candidate is t and the penalty (t - v)^2 - v^2; for q = +-1 (= t) the candidate is 0 and the
+//     penalty is the exact negation v^2 - (t - v)^2 - every operation rounded as the reference rounds it;
+//   * x / scale, correctly rounded, equals fma(fma(-scale, q0, x), r, q0) with r = RN(1 / scale) and
+//     q0 = RN(x r) (one reciprocal per group instead of a division per weight); groups whose scale is
+//     outside [1e-7, 1e30] (all-zero groups, overflowing inputs) take true divisions.
 // ---------------------------------------------------------------------------------------------
 
-// Code of eight consecutive values given the unrounded fp32 group scale.
+struct Block8 {
+    float rawf;        // sum q_i 3^i               (exact: |.| <= 3280)
+    float sumq;        // sum q_i                   (exact)
+    float best;        // smallest penalty so far
+    float delta;       // (alt - q) 3^i of that coordinate
+};
+
+// One coordinate of an 8-block.  kFirst: coordinate 0 (takes the penalty unconditionally: first index wins ties).
+template <bool kFirst>
+__device__ __forceinline__ void encode_coord(Block8& b, float v, float p3) {
+    const float q = fminf(fmaxf(rintf(v), -1.0f), 1.0f);
+    const float t = (v >= 0.0f) ? 1.0f : -1.0f;
+    const float a = __fsub_rn(t, v);
+    const float pen0 = __fsub_rn(__fmul_rn(a, a), __fmul_rn(v, v));
+    const bool qz = (q == 0.0f);
+    const float pen = qz ? pen0 : -pen0;
+    const float dsel = qz ? t : -t;                    // alt - q
+    b.rawf = __fmaf_rn(q, p3, b.rawf);
+    b.sumq = __fadd_rn(b.sumq, q);
+    if (kFirst || pen < b.best) { b.best = pen; b.delta = __fmul_rn(dsel, p3); }
+}
+
+__device__ __forceinline__ uint32_t block8_rank(const Block8& b) {
+    const int odd = ((int)b.sumq) & 1;
+    const float raw = __fadd_rn(__fadd_rn(b.rawf, 3280.0f), odd ? b.delta : 0.0f);     // sum (q_i + 1) 3^i
+    return (uint32_t)((int)raw >> 1);
+}
+
+// Code of eight consecutive values given the unrounded fp32 group scale (true divisions).
 __device__ __forceinline__ uint32_t encode_block8(const float* x, float scale) {
-    float v[8], q[8], alt[8];
-    int sum = 0;
-    float best = 0.f;
-    int worst = 0;
+    Block8 b = {0.f, 0.f, 0.f, 0.f};
+    float p3 = 1.0f;
+    encode_coord<true>(b, __fdiv_rn(x[0], scale), p3);
+#pragma unroll
+    for (int i = 1; i < 8; ++i) {
+        p3 *= 3.0f;
+        encode_coord<false>(b, __fdiv_rn(x[i], scale), p3);
+    }
+    return block8_rank(b);
+}
+
+// Same, with the group's reciprocal: two fused multiply-adds per quotient.
+__device__ __forceinline__ uint32_t encode_block8_rcp(const float* x, float scale, float rcp) {
+    Block8 b = {0.f, 0.f, 0.f, 0.f};
+    float p3 = 1.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        v[i] = __fdiv_rn(x[i], scale);
-        float r = rintf(v[i]);
-        q[i] = fminf(fmaxf(r, -1.0f), 1.0f);
-        sum += (int)q[i];
-        alt[i] = (q[i] == 0.0f) ? (v[i] >= 0.0f ? 1.0f : -1.0f) : 0.0f;
-        float da = __fsub_rn(alt[i], v[i]);
-        float dq = __fsub_rn(q[i], v[i]);
-        float pen = __fsub_rn(__fmul_rn(da, da), __fmul_rn(dq, dq));
-        if (i == 0 || pen < best) { best = pen; worst = i; }   // first index wins ties
+        const float q0 = __fmul_rn(x[i], rcp);
+        const float v = __fmaf_rn(__fmaf_rn(-scale, q0, x[i]), rcp, q0);
+        if (i == 0) encode_coord<true>(b, v, p3);
+        else encode_coord<false>(b, v, p3);
+        p3 *= 3.0f;
     }
-    const bool odd = (sum & 1) != 0;
-    uint32_t raw = 0, p3 = 1;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float qi = (odd && i == worst) ? alt[i] : q[i];
-        raw += (uint32_t)((int)qi + 1) * p3;
-        p3 *= 3;
-    }
-    return g_raw_to_rank[raw];
+    return block8_rank(b);
 }
 
 template <typename T, int GROUP>
@@ -76,7 +113,12 @@ __global__ void __launch_bounds__(128) encode_kernel(const T* __restrict__ w, in
 #pragma unroll
             for (int d = 0; d < GROUP; d += 8)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(xr[d + j], xr[d + j]));
+                for (int j = 0; j < 8; ++j) {
+                    // the square of a 16-bit float is exact in fp32, so one fused multiply-add rounds exactly
+                    // like the reference's separately rounded product and sum
+                    if (sizeof(T) == 2) acc[j] = __fmaf_rn(xr[d + j], xr[d + j], acc[j]);
+                    else acc[j] = __fadd_rn(acc[j], __fmul_rn(xr[d + j], xr[d + j]));
+                }
         } else {
             for (int d = 0; d < group; d += 8)
 #pragma unroll
@@ -92,27 +134,45 @@ __global__ void __launch_bounds__(128) encode_kernel(const T* __restrict__ w, in
         scales[gi] = __half_as_ushort(__float2half_rn(scale));
 
         uint8_t* out = packed + gi * (int64_t)(group / 16) * 3;
+        if (GROUP == 32) {
+            uint32_t c[4];
+            if (scale >= 1e-7f && scale <= 1e30f) {
+                const float rcp = __frcp_rn(scale);
+#pragma unroll
+                for (int h = 0; h < 4; ++h) c[h] = encode_block8_rcp(&xr[h * 8], scale, rcp);
+            } else {
+#pragma unroll
+                for (int h = 0; h < 4; ++h) c[h] = encode_block8(&xr[h * 8], scale);
+            }
+            // six bytes per group: two triplets b0 = c0 & 0xFF, b1 = (c0 >> 8) | ((c1 & 0xF) << 4), b2 = c1 >> 4
+            const uint32_t h0 = (c[0] | (c[1] << 12)) & 0xFFFFu, h1 = ((c[1] >> 4) | (c[2] << 8)) & 0xFFFFu,
+                           h2 = ((c[2] >> 8) | (c[3] << 4)) & 0xFFFFu;
+            if ((reinterpret_cast<uintptr_t>(out) & 1) == 0) {
+                uint16_t* o16 = reinterpret_cast<uint16_t*>(out);
+                o16[0] = (uint16_t)h0; o16[1] = (uint16_t)h1; o16[2] = (uint16_t)h2;
+            } else {
+                out[0] = (uint8_t)h0; out[1] = (uint8_t)(h0 >> 8); out[2] = (uint8_t)h1;
+                out[3] = (uint8_t)(h1 >> 8); out[4] = (uint8_t)h2; out[5] = (uint8_t)(h2 >> 8);
+            }
+        } else {
 #pragma unroll
         for (int b = 0; b < group; b += 16) {
             uint32_t c[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                if (GROUP > 0) {
-                    c[h] = encode_block8(&xr[(GROUP > 0 ? b : 0) + h * 8], scale);
-                } else {
-                    float t[8];
+                float t[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        int64_t idx = base + b + h * 8 + i;
-                        t[i] = idx < total ? to_f32<T>(w[idx]) : 0.f;
-                    }
-                    c[h] = encode_block8(t, scale);
+                for (int i = 0; i < 8; ++i) {
+                    int64_t idx = base + b + h * 8 + i;
+                    t[i] = idx < total ? to_f32<T>(w[idx]) : 0.f;
                 }
+                c[h] = encode_block8(t, scale);
             }
             out[0] = (uint8_t)(c[0] & 0xFF);
             out[1] = (uint8_t)(((c[0] >> 8) & 0x0F) | ((c[1] & 0x0F) << 4));
             out[2] = (uint8_t)((c[1] >> 4) & 0xFF);
             out += 3;
+        }
         }
     }
 }

@@ -15,7 +15,6 @@ constexpr int kNumPoints = 3281;
 // Device copies of the generated tables.  The whole library is one translation unit
 // (ojx_e8t.cu includes every kernel file), so file-scope statics are shared by all kernels.
 //   g_trit_nibbles[rank]  eight 4-bit fields, field i = coordinate i as {0: 0, 1: +1, 2: -1}
-//   g_raw_to_rank[raw]    base-3 raw value -> rank
 #define OJX_TABLE_QUAL static __device__ __align__(16)
 #define OJX_TABLE_NAME(x) g_##x
 #include "e8t_tables.inc"
@@ -138,7 +137,8 @@ int32_t gemv_static_scratch_impl(const void* x, int x_dtype, int64_t M, const ui
 int32_t gemv_tiles_impl(int64_t N, int64_t K);
 int32_t gemv_kchunks_impl(int64_t K);
 int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
-                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world, cudaStream_t s);
+                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world, int flags,
+                          cudaStream_t s);
 size_t  gemm_workspace_bytes_impl(int64_t M, int64_t N, int64_t K);
 int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                   const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,

@@ -1,0 +1,360 @@
+// Decode-shape linear for 1..16 activation rows (bf16 or fp16) on fp16 tensor cores, weights as the
+// row ("A") operand of mma.sync.m16n8k16.
+//
+//   y[m, n] = sum_k x[m, k] * coord[n, k] * scale[n, k / 32]  (+ bias)      fp32 accumulation
+//
+// Replaces the reference's scalar fused kernel (ojasx2/math/csrc/ojasx_math_core.hpp:580-634) and, for
+// small batches, _FusedE8GEMMFunction.forward (ojasx2/math/lattice.py:551-640).
+//
+// Work decomposition: a CTA of 16 warps walks a contiguous range of work items; an item is 32 weight
+// rows x one K chunk (up to 16 slices of 256 k), warp w owns slice w.  Items stream HBM -> shared memory
+// through a ring of 16-byte cp.async copies issued by all threads (row pitch padded by 16 bytes so that
+// the eight rows one shared-memory load touches fall on distinct banks); completion is counted on one
+// mbarrier per stage.  ONE block-wide barrier per item both releases the item's stage and publishes the
+// warps' partial sums, which the first 256 (512 for 9-16 rows) threads then add up in warp order
+// (deterministic) while the other warps already decode the next item.  The alternative without a block-wide
+// barrier - "empty" / "partials parked" / "partials summed" mbarriers and a reduction one item late, as the
+// one-row int8 kernel does - was measured with this arithmetic and lost (163 vs 145 us for the profiled launch
+// at 4 rows, 263 vs 190 us at 16 rows where its extra state spills).
+//
+// What one lane does: lane (g, t) of a warp owns ranks 8t..8t+7 of its slice for weight rows g and g + 8
+// of a 16-row tile: 12 contiguous bytes per row, i.e. 64 consecutive k = two scale groups.  A rank becomes
+// four operand registers (eight EXACT fp16 weights coord * scale) with four byte permutes: the permute
+// selectors come from one 64-bit shared-memory lookup (3281 entries, two interleaved copies), the permuted
+// bytes from two "pools" {0, lo, lo, 0} / {0, hi, hi ^ 0x80, 0} of the group's fp16 scale, built once per
+// (row, group).  The activations sit in registers as fp16 "B" fragments (64 k x 8 rows per lane and block of
+// eight activation rows) for as long as the CTA stays inside one problem and K chunk; bf16 activations are
+// rescaled per (row, slice) by a power of two so that the slice maximum lands in [2^14, 2^15) - exact for
+// every element within 2^-29 of the maximum, Inf / NaN pass through - and the partial sums are scaled back
+// before they are combined.  Because the scale is folded into the weights, fp32 accumulation runs across the
+// whole slice and nothing is left to do per group.
+//
+// A conflict-free alternative to the 3281-entry table was built and measured: a rank r is the base-3 number
+// 2r, so its low and high four digits can index one 81-entry table stored once per lane.  It removed every
+// bank conflict (14.3 M -> 8 k per launch) but needs a multiply-high and two multiply-adds per rank, and ran
+// 3-10 % slower; the kernels here are bound by instruction issue, not by shared-memory wavefronts.
+#pragma once
+
+#include <type_traits>
+
+#include "gemv.cuh"
+
+namespace ojx {
+
+constexpr int kA16Rows = 32;                                              // weight rows per work item
+constexpr int kA16StageBytes = kA16Rows * (kGemvMaxCodePitch + kGemvMaxScalePitch);   // 33792
+constexpr uint32_t kA16ScaleOff = kA16Rows * kGemvMaxCodePitch;           // scales follow the 32 padded code rows
+constexpr uint32_t kA16DescOff = kA16ScaleOff - 16;                       // free: every code row ends in 16 bytes of padding
+
+__host__ __device__ inline int a16_row_tiles(int N) { return (N + kA16Rows - 1) / kA16Rows; }
+
+template <int NB> struct A16Cfg {
+    static constexpr int kStages = NB == 1 ? 4 : 3;                       // all but one are in flight while an item is decoded
+    static constexpr int kRed = 2;                                        // reduction buffers (written at item n, n + 2, ...)
+    static constexpr int kLutBytes = ((kNumPoints * 16 + 1023) / 1024) * 1024;   // two interleaved copies of 8-byte entries
+    static constexpr int kRedFloats = kGemvWarps * 256 * NB;              // per buffer: 16 warps x 32 rows x 8 NB columns
+    static constexpr size_t kSmem = (size_t)kLutBytes + (size_t)kStages * kA16StageBytes + (size_t)kRed * kRedFloats * sizeof(float) + 256;
+};
+
+__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// fp16 MMA with fp32 accumulation: D (16 x 8) += A (16 x 16, row-major) * B (16 x 8, column-major).
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Slow path of a bounded wait, kept out of line so the loop body stays small.
+__device__ __noinline__ void a16_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (*abort_flag != 0) return;               // some wait already gave up: run on so that barrier counts stay matched
+    mbar_wait(bar, parity, abort_flag, code);
+}
+__device__ __forceinline__ void a16_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (!mbar_try_wait(bar, parity)) a16_wait_slow(bar, parity, abort_flag, code);
+}
+
+// Rank J (0..7) of a lane's 96-bit window, moved so that it starts at bit POS (bits outside the field are junk).
+template <int J, int POS>
+__device__ __forceinline__ uint32_t a16_field(uint32_t w0, uint32_t w1, uint32_t w2) {
+    constexpr int bit = 12 * J, word = bit >> 5, off = bit & 31;
+    const uint32_t lo = word == 0 ? w0 : (word == 1 ? w1 : w2);
+    if constexpr (off + 12 <= 32) {
+        if constexpr (off > POS) return lo >> (off - POS);
+        else if constexpr (off < POS) return lo << (POS - off);
+        else return lo;
+    } else {
+        const uint32_t hi = word == 0 ? w1 : w2;
+        return __funnelshift_r(lo, hi, off - POS);
+    }
+}
+
+// The four operand registers of rank J: weights {0,1}, {2,3}, {4,5}, {6,7}, each an fp16 pair coord * scale.
+// `lut` is the table's shared-memory address plus this lane's copy offset is OR-ed into the entry address.
+template <int J>
+__device__ __forceinline__ void a16_decode(uint32_t (&a)[4], uint32_t w0, uint32_t w1, uint32_t w2, uint32_t pa, uint32_t pb,
+                                           uint32_t lut, uint32_t lane_or) {
+    const uint32_t addr = (a16_field<J, 4>(w0, w1, w2) & 0xFFF0u) | lane_or;
+    const uint2 sel = lds_u64(lut + addr);
+    a[0] = prmt(pa, pb, sel.x); a[1] = prmt(pa, pb, sel.x >> 16);
+    a[2] = prmt(pa, pb, sel.y); a[3] = prmt(pa, pb, sel.y >> 16);
+}
+
+template <int NB, bool kXF16>
+__global__ void __launch_bounds__(kGemvThreads, 1)
+gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_constant__ ojx_e8t_gemv_problem single,
+                int count, int total_items, int M, int y_dtype, int overlap, const __grid_constant__ PeerMap peers) {
+    using Cfg = A16Cfg<NB>;
+    constexpr int S = Cfg::kStages;
+    const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t lut = smem_u32(smem);
+    const uint32_t ring = lut + Cfg::kLutBytes;
+    float* red = reinterpret_cast<float*>(smem + Cfg::kLutBytes + S * kA16StageBytes);
+    uint8_t* tail = smem + Cfg::kLutBytes + S * kA16StageBytes + Cfg::kRed * Cfg::kRedFloats * sizeof(float);
+    const uint32_t bar_full = smem_u32(tail), bar_lut = bar_full + 8 * S;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 64);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(bar_full + 8 * s, kGemvThreads);      // every thread's cp.async arrive
+        mbar_init(bar_lut, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the lookup table's shared-memory image arrives as ONE bulk copy while the kernel sets itself up
+        mbar_expect_tx(bar_lut, kNumPoints * 16);
+        bulk_load(lut, g_lut_f16sel, kNumPoints * 16, bar_lut);
+    }
+    __syncthreads();
+
+    const int64_t per = ((int64_t)total_items + gridDim.x - 1) / gridDim.x;
+    const int i0 = (int)min((int64_t)total_items, per * blockIdx.x);
+    const int i1 = (int)min((int64_t)total_items, per * (blockIdx.x + 1));
+    // the launch that follows in the stream may start its own set-up once every CTA of this one is past this point
+    if (overlap) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (i0 >= i1) return;
+    const int nitems = i1 - i0;
+    const int p0 = find_problem(probs, count, i0, 1);
+
+    // ---- loader: thread (lr, ls) copies chunks ls, ls+16, ls+32 of row lr's codes and chunk ls of its scales.
+    // The plan of a (problem, K chunk) - source pointers of this thread's chunks, destination offsets, which
+    // chunks exist - is made once; from one row tile to the next only the two pointers move. ----
+    const int lr = tid >> 4, ls = tid & 15;
+    int l_prob = p0, l_chunk, l_tile, l_tiles = 1, l_kchunks = 1, l_act = 1, l_N = 0;
+    const uint8_t* l_pc = nullptr;
+    const uint8_t* l_ps = nullptr;
+    int l_step_c = 0, l_step_s = 0;
+    uint32_t l_dc = 0, l_ds = 0;
+    bool l_c0 = false, l_c1 = false, l_c2 = false, l_cs = false;
+    auto plan = [&]() {
+        const ojx_e8t_gemv_problem& P = probs[l_prob];
+        l_N = P.N;
+        const int K = P.K;
+        l_act = gemv_active_warps(K);
+        l_tiles = a16_row_tiles(l_N);
+        l_kchunks = (K / 256) / l_act;
+        const uint32_t cb = l_act * 48, sb = l_act * 16;
+        const int64_t rowc = K * 3 / 16, rows = K / 16;
+        l_pc = P.packed + (int64_t)(l_tile * kA16Rows + lr) * rowc + (int64_t)l_chunk * cb + ls * 16;
+        l_ps = reinterpret_cast<const uint8_t*>(P.scales) + (int64_t)(l_tile * kA16Rows + lr) * rows + (int64_t)l_chunk * sb + ls * 16;
+        l_step_c = (int)(kA16Rows * rowc);
+        l_step_s = (int)(kA16Rows * rows);
+        l_dc = lr * (cb + 16) + ls * 16;
+        l_ds = kA16ScaleOff + lr * (sb + 16) + ls * 16;
+        l_c0 = ls < 3 * l_act; l_c1 = ls + 16 < 3 * l_act; l_c2 = ls + 32 < 3 * l_act; l_cs = ls < l_act;
+    };
+    {
+        const int local = i0 - probs[p0].tile_begin;
+        const int tiles0 = a16_row_tiles(probs[p0].N);
+        l_chunk = local / tiles0;
+        l_tile = local - l_chunk * tiles0;
+        plan();
+    }
+    int issued = 0, istage = 0;
+    auto issue_next = [&]() {                                      // the caller knows that stage `istage` is free
+        const uint32_t stage = ring + istage * kA16StageBytes;
+        if (l_tile * kA16Rows + lr < l_N) {
+            if (l_c0) cp_async16(stage + l_dc, l_pc);
+            if (l_c1) cp_async16(stage + l_dc + 256, l_pc + 256);
+            if (l_c2) cp_async16(stage + l_dc + 512, l_pc + 512);
+            if (l_cs) cp_async16(stage + l_ds, l_ps);
+        }
+        // the item's coordinates travel with its data, so only the loader keeps a cursor
+        if (tid == 0) sts_u128(stage + kA16DescOff, make_uint4((uint32_t)l_prob, (uint32_t)l_chunk, (uint32_t)l_tile, (uint32_t)l_act));
+        cp_async_arrive(bar_full + 8 * istage);
+        ++issued;
+        if (++istage == S) istage = 0;
+        if (++l_tile < l_tiles) {
+            l_pc += l_step_c;
+            l_ps += l_step_s;
+        } else {
+            l_tile = 0;
+            if (++l_chunk == l_kchunks) {
+                l_chunk = 0;
+                if (l_prob + 1 < count) ++l_prob;
+            }
+            plan();
+        }
+    };
+    // packed weights never depend on the previous launch: their copies start before that launch has drained
+    for (int n = 0; n < S - 1 && n < nitems; ++n) issue_next();
+    // activations (and the output buffers) do
+    if (overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const uint32_t lane_or = (uint32_t)((lane & 1) << 3);
+    uint32_t xb[NB][8][4];                      // B fragments: [block][rank j][k 0-1, 2-3, 4-5, 6-7 of the rank]
+    float up[NB][2];                            // 2^e of activation rows 2t, 2t+1 of the block (this lane's output columns)
+    int cur_prob = -1, cur_chunk = -1, cur_K = 0;
+
+    a16_wait(bar_lut, 0u, abort_flag, 55);                          // the table has landed
+    int cstage = 0;
+    uint32_t cparity = 0;
+    for (int n = 0; n < nitems; ++n) {
+        if (issued < nitems) issue_next();                          // into the stage the previous item's barrier released
+        a16_wait(bar_full + 8 * cstage, cparity, abort_flag, 52);
+        const uint32_t stage = ring + cstage * kA16StageBytes;
+        const uint4 desc = lds_u128(stage + kA16DescOff);
+        const int prob = (int)desc.x, chunk = (int)desc.y, tile = (int)desc.z, act = (int)desc.w;
+        if (++cstage == S) { cstage = 0; cparity ^= 1u; }
+
+        if (prob != cur_prob || chunk != cur_chunk) {
+            if (prob != cur_prob) cur_K = probs[prob].K;
+            cur_prob = prob;
+            cur_chunk = chunk;
+            const uint16_t* xp = static_cast<const uint16_t*>(probs[prob].x);
+            const int slice = chunk * act + warp;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                const int m = nb * 8 + g;
+                const bool on = warp < act && m < M;
+                const uint4* xrow = reinterpret_cast<const uint4*>(xp + (int64_t)m * cur_K + slice * 256 + t * 64);
+                float upg = 1.0f;
+                if constexpr (kXF16) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 q = make_uint4(0, 0, 0, 0);
+                        if (on) q = __ldg(xrow + j);
+                        xb[nb][j][0] = q.x; xb[nb][j][1] = q.y; xb[nb][j][2] = q.z; xb[nb][j][3] = q.w;
+                    }
+                } else {
+                    // two passes over the lane's 128 bytes (the second one hits the cache): maximum first, then convert,
+                    // so that the raw words never have to be held beside the converted ones
+                    uint32_t amax = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 q = make_uint4(0, 0, 0, 0);
+                        if (on) q = __ldg(xrow + j);
+                        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) amax = max(amax, max((w[i] << 16) & 0x7FFFFFFFu, w[i] & 0x7FFF0000u));
+                    }
+                    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+                    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));      // the four lanes of activation row m
+                    int e = 0;
+                    const int ex = (int)((amax >> 23) & 0xFFu);
+                    if (ex != 0 && ex != 0xFF) e = max(-100, min(100, ex - 127 - 14));   // slice maximum -> [2^14, 2^15)
+                    const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+                    upg = __uint_as_float((uint32_t)(127 + e) << 23);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 q = make_uint4(0, 0, 0, 0);
+                        if (on) q = __ldg(xrow + j);
+                        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const __half2 v = __floats2half2_rn(__uint_as_float(w[i] << 16) * down, __uint_as_float(w[i] & 0xFFFF0000u) * down);
+                            xb[nb][j][i] = *reinterpret_cast<const uint32_t*>(&v);
+                        }
+                    }
+                }
+                up[nb][0] = __shfl_sync(0xFFFFFFFFu, upg, 8 * t);          // lane (g' = 2t, *) holds activation row 2t
+                up[nb][1] = __shfl_sync(0xFFFFFFFFu, upg, 8 * t + 4);
+            }
+        }
+
+
+        // buffer n & 1 was last read after the barrier of item n - 2, which every thread has passed
+        float* rbuf = red + (size_t)(n & 1) * Cfg::kRedFloats + warp * (256 * NB);
+
+        if (warp < act) {
+            const uint32_t cpitch = act * 48 + 16, spitch = act * 16 + 16;
+#pragma unroll
+            for (int tl = 0; tl < 2; ++tl) {
+                // this lane's words of the tile: rows g and g + 8, three code words and one scale word (groups 2t, 2t+1) each
+                const uint32_t ca = stage + (tl * 16 + g) * cpitch + warp * 48 + t * 12, cb2 = ca + 8 * cpitch;
+                const uint32_t sa = stage + kA16ScaleOff + (tl * 16 + g) * spitch + warp * 16 + t * 4;
+                const uint32_t a0 = lds_u32(ca), a1 = lds_u32(ca + 4), a2 = lds_u32(ca + 8);
+                const uint32_t b0 = lds_u32(cb2), b1 = lds_u32(cb2 + 4), b2 = lds_u32(cb2 + 8);
+                const uint32_t ssa = lds_u32(sa), ssb = lds_u32(sa + 8 * spitch);
+                float acc[NB][4];
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f;
+
+                auto rank_pair = [&](auto jtag, uint32_t paa, uint32_t pba, uint32_t pab, uint32_t pbb) {
+                    constexpr int J = decltype(jtag)::value;
+                    uint32_t ra[4], rb[4];
+                    a16_decode<J>(ra, a0, a1, a2, paa, pba, lut, lane_or);
+                    a16_decode<J>(rb, b0, b1, b2, pab, pbb, lut, lane_or);
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        mma_f16(acc[nb], ra[0], rb[0], ra[1], rb[1], xb[nb][J][0], xb[nb][J][1]);
+                        mma_f16(acc[nb], ra[2], rb[2], ra[3], rb[3], xb[nb][J][2], xb[nb][J][3]);
+                    }
+                };
+                {   // group 2t: byte pools {0, lo, lo, 0} and {0, hi, hi ^ 0x80, 0} of the scale in the low half
+                    const uint32_t paa = prmt(ssa, 0u, 0x4004u), pba = prmt(ssa, 0u, 0x4114u) ^ 0x00800000u;
+                    const uint32_t pab = prmt(ssb, 0u, 0x4004u), pbb = prmt(ssb, 0u, 0x4114u) ^ 0x00800000u;
+                    rank_pair(std::integral_constant<int, 0>{}, paa, pba, pab, pbb);
+                    rank_pair(std::integral_constant<int, 1>{}, paa, pba, pab, pbb);
+                    rank_pair(std::integral_constant<int, 2>{}, paa, pba, pab, pbb);
+                    rank_pair(std::integral_constant<int, 3>{}, paa, pba, pab, pbb);
+                }
+                {   // group 2t + 1: the scale in the high half
+                    const uint32_t paa = prmt(ssa, 0u, 0x4224u), pba = prmt(ssa, 0u, 0x4334u) ^ 0x00800000u;
+                    const uint32_t pab = prmt(ssb, 0u, 0x4224u), pbb = prmt(ssb, 0u, 0x4334u) ^ 0x00800000u;
+                    rank_pair(std::integral_constant<int, 4>{}, paa, pba, pab, pbb);
+                    rank_pair(std::integral_constant<int, 5>{}, paa, pba, pab, pbb);
+                    rank_pair(std::integral_constant<int, 6>{}, paa, pba, pab, pbb);
+                    rank_pair(std::integral_constant<int, 7>{}, paa, pba, pab, pbb);
+                }
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+                    *reinterpret_cast<float4*>(rbuf + ((tl * NB + nb) * 32 + lane) * 4) =
+                        make_float4(acc[nb][0] * up[nb][0], acc[nb][1] * up[nb][1], acc[nb][2] * up[nb][0], acc[nb][3] * up[nb][1]);
+            }
+        }
+        __syncthreads();           // the stage is free again and every warp's partial sums are visible
+
+        // ---- sum over the warps in warp order; thread tid owns element tid of the 256 NB fragment values ----
+        if (tid < 256 * NB) {
+            const float* rb = red + (size_t)(n & 1) * Cfg::kRedFloats + tid;
+            const int comp = tid & 3, lp = (tid >> 2) & 31, nb = (tid >> 7) % NB, tl = tid / (128 * NB);
+            const int row = tile * kA16Rows + tl * 16 + (lp >> 2) + ((comp >> 1) << 3);
+            const int col = nb * 8 + ((lp & 3) << 1) + (comp & 1);
+            const ojx_e8t_gemv_problem& P = probs[prob];
+            const int rN = P.N;
+            if (row < rN && col < M) {                               // activation rows beyond M hold zeros: nothing to add up
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; ++w)
+                    if (w < act) sum += rb[w * 256 * NB];
+                if (P.partial != nullptr) P.partial[((int64_t)chunk * M + col) * rN + row] = sum;
+                else {
+                    if (P.bias != nullptr) sum += load_any(P.bias, kXF16 ? OJX_F16 : OJX_BF16, row);
+                    store_any(P.y, y_dtype, (int64_t)col * rN + row, sum);
+                    if (peers.world > 1) store_peers(peers, P.y, y_dtype, (int64_t)col * rN + row, sum);
+                }
+            }
+        }
+    }
+
+    if (tid == 0 && *abort_flag != 0) atomicCAS(&g_device_status, 0, *abort_flag);
+}
+
+}  // namespace ojx

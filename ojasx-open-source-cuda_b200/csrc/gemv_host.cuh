@@ -1,11 +1,12 @@
-// Host-side routing of the decode-shape entry points to the kernels in gemv.cuh / gemv_e4m3.cuh.
+// Host-side routing of the decode-shape entry points to the kernels in gemv.cuh and gemv_a16.cuh.
 #pragma once
 
+#include <atomic>
 #include <mutex>
+#include <utility>
 
 #include "gemv.cuh"
-#include "gemv_b1.cuh"
-#include "gemv_bn.cuh"
+#include "gemv_a16.cuh"
 
 namespace ojx {
 
@@ -15,51 +16,79 @@ inline bool gemv_fast_ok(int64_t M, int64_t N, int64_t K, int group, int x_dtype
 }
 
 int32_t gemv_tiles_impl(int64_t N, int64_t K) {
-    if (N <= 0 || K <= 0 || K % 256 != 0) return 0;
+    if (N <= 0 || K <= 0 || K % 256 != 0 || N >= (1 << 30) || K >= (1 << 30)) return 0;
     return gemv_row_tiles32((int)N) * gemv_kchunks((int)K);
 }
-int32_t gemv_kchunks_impl(int64_t K) { return (K > 0 && K % 256 == 0) ? gemv_kchunks((int)K) : 0; }
+int32_t gemv_kchunks_impl(int64_t K) { return (K > 0 && K % 256 == 0 && K < (1 << 30)) ? gemv_kchunks((int)K) : 0; }
 
 // Scratch of the single-problem entry point: fp32 partials [kchunks][M][N], needed only when K
 // spans more than one chunk of the CTA's 16 slices.
 size_t gemv_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
-    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 256 != 0) return 0;
+    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 256 != 0 || N >= (1 << 30) || K >= (1 << 30)) return 0;
     const int kc = gemv_kchunks((int)K);
     return kc > 1 ? (size_t)kc * M * N * sizeof(float) : 0;
 }
 
-template <bool kBf16, int NB>
-static int32_t launch_gemv(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
-                           int M, int y_dtype, const PeerMap& peers, cudaStream_t s) {
-    static bool configured = false;
-    constexpr int COPIES = 4;
-    const size_t smem = gemv_smem_bytes<NB, COPIES>();
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<kBf16, NB, COPIES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { last_cuda_error() = e; return OJX_ERR_LAUNCH; }
-        configured = true;
-    }
+// Opting in to more than 48 KB of dynamic shared memory is a per-device (per-context) attribute of a kernel:
+// `done` keeps one bit per device ordinal.
+template <typename Kernel>
+static int32_t ensure_dynamic_smem(Kernel kernel, size_t bytes, std::atomic<uint64_t>& done) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return OJX_ERR_LAUNCH;
+    const uint64_t bit = 1ull << dev;
+    if (done.load(std::memory_order_acquire) & bit) return OJX_OK;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) { last_cuda_error() = e; return OJX_ERR_LAUNCH; }
+    done.fetch_or(bit, std::memory_order_release);
+    return OJX_OK;
+}
+
+// Launch with the "programmatic stream serialization" attribute when `overlap` is set: the kernel may then start
+// (and run up to its griddepcontrol.wait) while the previous kernel of the stream is still draining.
+template <typename... Params, typename... Args>
+static int32_t launch_maybe_overlapped(void (*kernel)(Params...), int grid, int block, size_t smem, cudaStream_t s, bool overlap,
+                                       Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+    if (e != cudaSuccess) { last_cuda_error() = e; (void)cudaGetLastError(); return OJX_ERR_LAUNCH; }
+    return OJX_OK;
+}
+
+template <int NB, bool kXF16>
+static int32_t launch_gemv_a16(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
+                               int M, int y_dtype, const PeerMap& peers, bool overlap, cudaStream_t s) {
+    static std::atomic<uint64_t> configured{0};
+    using Cfg = A16Cfg<NB>;
+    const int32_t st = ensure_dynamic_smem(gemv_a16_kernel<NB, kXF16>, Cfg::kSmem, configured);
+    OJX_RETURN_IF(st != OJX_OK, st);
     const int sms = num_sms();
     const int per = (total + sms - 1) / sms;
     const int grid = (total + per - 1) / per;
-    gemv_mma_kernel<kBf16, NB, COPIES><<<grid, kGemvBlock, smem, s>>>(probs, single, count, total, M, y_dtype, peers);
-    return launch_status();
+    return launch_maybe_overlapped(gemv_a16_kernel<NB, kXF16>, grid, kGemvThreads, Cfg::kSmem, s, overlap,
+                                   probs, single, count, total, M, y_dtype, overlap ? 1 : 0, peers);
 }
 
-// bf16 activations: one row -> gemv_b1 (int8), 2-8 rows -> gemv_bn int8 form, 9-16 rows -> gemv_bn fp16 form.
+// One to eight activation rows take one block of eight columns per MMA, nine to sixteen take two.
 static int32_t dispatch_gemv(bool bf16, const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count,
-                             int total, int M, int y_dtype, const PeerMap& peers, cudaStream_t s) {
-    if (bf16 && M == 1) return launch_gemv_b1(probs, single, count, total, y_dtype, peers, s);
-    if (bf16) return M <= 8 ? launch_gemv_bn<1, false, false>(probs, single, count, total, M, y_dtype, peers, s)
-                            : launch_gemv_bn<2, true, false>(probs, single, count, total, M, y_dtype, peers, s);
-    // fp16 activations: 9-16 rows share the scale-folded fp16 kernel (the activations need no conversion);
-    // up to 8 rows take the 16-bit kernel, which walks every 32-row tile as two 16-row halves
-    return M <= 8 ? launch_gemv<false, 1>(probs, single, count, 2 * total, M, y_dtype, peers, s)
-                  : launch_gemv_bn<2, true, true>(probs, single, count, total, M, y_dtype, peers, s);
+                             int total, int M, int y_dtype, const PeerMap& peers, bool overlap, cudaStream_t s) {
+    if (bf16) return M <= 8 ? launch_gemv_a16<1, false>(probs, single, count, total, M, y_dtype, peers, overlap, s)
+                            : launch_gemv_a16<2, false>(probs, single, count, total, M, y_dtype, peers, overlap, s);
+    return M <= 8 ? launch_gemv_a16<1, true>(probs, single, count, total, M, y_dtype, peers, overlap, s)
+                  : launch_gemv_a16<2, true>(probs, single, count, total, M, y_dtype, peers, overlap, s);
 }
 
 int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
-                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world, cudaStream_t s) {
+                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world, int flags,
+                          cudaStream_t s) {
     OJX_RETURN_IF(world < 1 || world > 8 || (world > 1 && !peer_delta), OJX_ERR_SHAPE);
     PeerMap peers = peer_map_self();
     if (peer_delta != nullptr) {
@@ -73,7 +102,9 @@ int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int t
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
     const bool bf = x_dtype == OJX_BF16;
     ojx_e8t_gemv_problem none = {};
-    const int32_t st = dispatch_gemv(bf, problems, none, count, total_tiles, (int)M, y_dtype, peers, s);
+    OJX_RETURN_IF((flags & ~OJX_GEMV_STATIC_WEIGHTS) != 0, OJX_ERR_UNSUPPORTED);
+    const bool overlap = (flags & OJX_GEMV_STATIC_WEIGHTS) != 0;
+    const int32_t st = dispatch_gemv(bf, problems, none, count, total_tiles, (int)M, y_dtype, peers, overlap, s);
     OJX_RETURN_IF(st != OJX_OK, st);
     if (!needs_reduce) return OJX_OK;
     // Problems whose K spans several chunks carry a partial buffer; the reduce pass skips the rest.
@@ -104,7 +135,7 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         h.N = (int)N; h.K = (int)K; h.tile_begin = 0; h.reserved = 0;
         const int total = gemv_row_tiles32((int)N) * kc;
         const bool bf = x_dtype == OJX_BF16;
-        const int32_t st = dispatch_gemv(bf, nullptr, h, 1, total, (int)M, y_dtype, peer_map_self(), s);
+        const int32_t st = dispatch_gemv(bf, nullptr, h, 1, total, (int)M, y_dtype, peer_map_self(), false, s);
         OJX_RETURN_IF(st != OJX_OK, st);
         if (kc > 1) {
             dim3 grid(64, 1);
@@ -158,7 +189,10 @@ int32_t gemv_static_scratch_impl(const void* x, int x_dtype, int64_t M, const ui
                                  const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s) {
     OJX_RETURN_IF(!x || !packed || !scales || !y, OJX_ERR_NULL);
     OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0, OJX_ERR_SHAPE);
-    const size_t need = gemv_workspace_bytes_impl(M, N, K);
+    // scratch is only needed on the tensor-core route (same test as in gemv_impl); the plain kernel uses none
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) |
+                           reinterpret_cast<uintptr_t>(scales)) & 15) == 0;
+    const size_t need = (gemv_fast_ok(M, N, K, effective_group(group), x_dtype) && aligned) ? gemv_workspace_bytes_impl(M, N, K) : 0;
     // larger problems do not fit the built-in array: the caller has to use ojx_e8t_gemv with its own scratch
     OJX_RETURN_IF(need > kStaticScratchFloats * sizeof(float), OJX_ERR_WORKSPACE);
     float* scratch = nullptr;

@@ -3,8 +3,7 @@
 #include "common.cuh"
 #include "codec.cuh"
 #include "gemv.cuh"
-#include "gemv_b1.cuh"
-#include "gemv_bn.cuh"
+#include "gemv_a16.cuh"
 #include "gemv_host.cuh"
 #include "gemm_tcgen05.cuh"
 
@@ -85,14 +84,21 @@ int32_t ojx_e8t_gemv_kchunks(int64_t K) { return ojx::gemv_kchunks_impl(K); }
 
 int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles, int64_t M,
                              int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce, void* stream) {
-    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, nullptr, 1, (cudaStream_t)stream);
+    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, nullptr, 1, 0, (cudaStream_t)stream);
 }
 
 int32_t ojx_e8t_gemv_grouped_peers(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles, int64_t M,
                                    int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
                                    const int64_t* peer_delta, int32_t world, void* stream) {
     OJX_RETURN_IF(!peer_delta, OJX_ERR_NULL);
-    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, peer_delta, world, (cudaStream_t)stream);
+    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, peer_delta, world, 0, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_gemv_grouped_ex(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles, int64_t M,
+                                int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
+                                const int64_t* peer_delta, int32_t world, int32_t flags, void* stream) {
+    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, peer_delta,
+                                  peer_delta ? world : 1, flags, (cudaStream_t)stream);
 }
 
 int32_t ojx_e8t_enable_peer_access(int32_t peer_device) {

@@ -220,10 +220,13 @@ class GroupedGemv:
     """
 
     def __init__(self, entries: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor], torch.Tensor]],
-                 shapes: Sequence[Tuple[int, int]], peer_delta: Optional[Sequence[int]] = None):
+                 shapes: Sequence[Tuple[int, int]], peer_delta: Optional[Sequence[int]] = None,
+                 static_weights: bool = False):
         # entries: (x[M,K], packed, scales, bias-or-None, y[M,N]);  shapes: (N, K)
         # peer_delta: byte distances from this rank's output window to every rank's (see sharding.PeerWindow);
         #             when given, each result is stored into all ranks' windows by the kernel itself
+        # static_weights: promise that nothing queued ahead of a call in its stream writes the packed buffers; the
+        #             launch may then begin (set-up, first weight copies) while the previous kernel drains
         if not entries:
             raise ValueError("empty problem list")
         lib = _cabi.lib()
@@ -272,6 +275,7 @@ class GroupedGemv:
         raw = bytes(arr)
         self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self.device)
         self.packed_bytes = sum(n * k // 4 for n, k in shapes)
+        self.flags = _cabi.OJX_GEMV_STATIC_WEIGHTS if static_weights else 0
         self._peers = None
         if peer_delta is not None:
             if not (1 <= len(peer_delta) <= 8):
@@ -280,13 +284,9 @@ class GroupedGemv:
 
     def __call__(self) -> None:
         with torch.cuda.device(self.device):
-            if self._peers is None:
-                st = _cabi.lib().ojx_e8t_gemv_grouped(self.table.data_ptr(), self.count, self.total_tiles, self.M,
-                                                      _dtype_code(self.x_dtype), _dtype_code(self.y_dtype),
-                                                      self.needs_reduce, _stream_ptr(self.device))
-            else:
-                st = _cabi.lib().ojx_e8t_gemv_grouped_peers(self.table.data_ptr(), self.count, self.total_tiles, self.M,
-                                                            _dtype_code(self.x_dtype), _dtype_code(self.y_dtype),
-                                                            self.needs_reduce, ctypes.addressof(self._peers),
-                                                            len(self._peers), _stream_ptr(self.device))
-        _cabi.check(st, "ojx_e8t_gemv_grouped")
+            st = _cabi.lib().ojx_e8t_gemv_grouped_ex(
+                self.table.data_ptr(), self.count, self.total_tiles, self.M, _dtype_code(self.x_dtype),
+                _dtype_code(self.y_dtype), self.needs_reduce,
+                ctypes.addressof(self._peers) if self._peers is not None else None,
+                len(self._peers) if self._peers is not None else 1, self.flags, _stream_ptr(self.device))
+        _cabi.check(st, "ojx_e8t_gemv_grouped_ex")

@@ -95,8 +95,11 @@ def special_inputs():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("OJASX_REFERENCE_DIR"),
+                    help="checkout of the reference project (or set OJASX_REFERENCE_DIR)")
     args = ap.parse_args()
+    if not args.ref or not os.path.isdir(args.ref):
+        ap.error("pass --ref /path/to/reference (or set OJASX_REFERENCE_DIR)")
     os.environ.setdefault("OJASX_DISABLE_UPDATE_CHECK", "1")
     logging.disable(logging.CRITICAL)
     sys.path.insert(0, args.ref)
@@ -152,6 +155,30 @@ def main():
         arrays["special/" + name + "/decoded"] = dec.numpy()
         meta["special"].append(dict(name=name, group=group, rows=int(w.shape[0]), cols=int(w.shape[1])))
         print("special", name, sha(packed.numpy())[:16])
+
+    # Walsh-Hadamard rotation (lattice.py:91-102) in the three dtypes, and one layer packed and run with
+    # use_hadamard=True (lattice.py:564-567,807,825): weights are rotated before packing, activations in forward
+    xw = torch.from_numpy(O.gen_normal(77, 6 * 96, 1.0).reshape(6, 96).copy())
+    for tag, dt in (("f32", torch.float32), ("f16", torch.float16), ("bf16", torch.bfloat16)):
+        xin = xw.to(dt)
+        out = L.fwht_block32(xin)
+        arrays["fwht/" + tag + "/input"] = xin.float().numpy()
+        arrays["fwht/" + tag + "/output"] = out.float().numpy()
+    lin = torch.nn.Linear(256, 48, bias=True)
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(O.gen_normal(78, 48 * 256, 0.02).reshape(48, 256).copy()))
+        lin.bias.copy_(torch.from_numpy(O.gen_normal(79, 48, 0.1).copy()))
+    layer = L.E8LatticeLinear.from_linear(lin, rank=0, bitrate=1.5, group_size=32, use_hadamard=True)
+    xh = torch.from_numpy(O.gen_normal(80, 5 * 256, 1.0).reshape(5, 256).copy())
+    with torch.no_grad():
+        yh = layer(xh)
+    arrays["hadamard/packed"] = layer.packed_weight.numpy()
+    arrays["hadamard/scales"] = layer.block_scales.view(torch.int16).numpy().view(np.uint16)
+    arrays["hadamard/unpacked"] = layer.unpack_weights(torch.float32).numpy()
+    arrays["hadamard/y"] = yh.numpy()
+    meta["hadamard"] = dict(in_features=256, out_features=48, weight_seed=78, bias_seed=79, x_seed=80, batch=5,
+                            sha_packed=sha(layer.packed_weight.numpy()))
+    print("hadamard", meta["hadamard"]["sha_packed"][:16])
 
     # decode of every code: all 3281 ranks (padded to an even count) with unit scales
     ranks = np.arange(3282, dtype=np.int64) % 3281

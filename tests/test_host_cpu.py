@@ -124,6 +124,17 @@ def test_luts_and_fwht_match_oracle(P, oracle):
     assert torch.allclose(h.abs(), torch.full((32, 32), 32 ** -0.5))
 
 
+def test_fwht_equals_reference_output_bit_for_bit(P, golden):
+    """fwht_block32 against outputs of the reference's own function (ojasx2/math/lattice.py:91-102) stored by
+    tests/golden/make_golden.py, in the three dtypes the packer is fed with."""
+    _, arrays = golden
+    for tag, dt in (("f32", torch.float32), ("f16", torch.float16), ("bf16", torch.bfloat16)):
+        x = torch.from_numpy(arrays[f"fwht/{tag}/input"]).to(dt)
+        y = P.fwht_block32(x)
+        assert y.dtype == dt
+        assert np.array_equal(y.float().numpy().view(np.uint32), arrays[f"fwht/{tag}/output"].view(np.uint32)), tag
+
+
 def test_shard_rows_cover_everything(P):
     from importlib import import_module
     sh = import_module(P.__name__ + ".sharding")
