@@ -58,13 +58,24 @@ int32_t ojx_e8t_version(void);
 const char* ojx_e8t_status_string(int32_t status);
 
 /*
- * Diagnostics.  ojx_e8t_last_cuda_error: text of the last CUDA runtime error that made an entry point
- * return OJX_ERR_LAUNCH on the calling thread.  ojx_e8t_device_status: synchronises the device and
- * returns OJX_ERR_TIMEOUT if a bounded wait inside a decode-shape kernel ever gave up, else OJX_OK.
- * No counterpart in the reference.
+ * Diagnostics (no counterpart in the reference).
+ * ojx_e8t_last_cuda_error: text of the last CUDA runtime error that made an entry point return
+ *   OJX_ERR_LAUNCH on the calling thread.
+ * Every wait inside the kernels (on a copy in flight, on another rank) is bounded; a kernel whose wait runs
+ * out stops working on its inputs, returns, and records the fact in two places:
+ * ojx_e8t_device_status: synchronises the current device, returns OJX_ERR_TIMEOUT if a wait gave up since the
+ *   last call, else OJX_OK, and clears the record.
+ * ojx_e8t_poll_status: the same answer WITHOUT synchronising - the kernels also write into a page of pinned
+ *   host memory that belongs to the library - so a wrapper can check it cheaply at the start of every call
+ *   and raise; it reports launches that have already run into the limit, and clears the record.
+ *   (The page is pinned on the first decode-shape call of the process: make that call before a stream capture.)
+ * ojx_e8t_set_wait_limit: polls before a wait on a copy gives up (0 restores the default of 2^24, seconds);
+ *   for tests of the error path.
  */
 const char* ojx_e8t_last_cuda_error(void);
 int32_t ojx_e8t_device_status(void);
+int32_t ojx_e8t_poll_status(void);
+void    ojx_e8t_set_wait_limit(uint32_t polls);
 
 /*
  * Encoder.  Replaces TernaryE8LatticePacker.pack (ojasx2/math/lattice.py:338-384); bit-exact.
@@ -148,7 +159,9 @@ typedef struct {
     float*          partial;  /* scratch [kchunks, M, N] fp32 when kchunks > 1, else null */
     int32_t         N, K;
     int32_t         tile_begin;   /* exclusive prefix sum of tiles over the problem list */
-    int32_t         reserved;
+    int32_t         ldy;          /* distance in elements between consecutive rows of y; 0 means N.  A larger value lets
+                                     y be a column block of a wider [M, ldy] matrix (the place of one rank's shard in
+                                     the full output of a column-sharded linear) */
 } ojx_e8t_gemv_problem;
 
 int32_t ojx_e8t_gemv_tiles(int64_t N, int64_t K);
@@ -171,8 +184,16 @@ int32_t ojx_e8t_gemv_grouped_peers(const ojx_e8t_gemv_problem* problems, int32_t
                                    int64_t M, int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
                                    const int64_t* peer_delta, int32_t world, void* stream);
 /*
- * The general form of the two grouped launches above (they call it with flags = 0; peer_delta may be null,
- * which means a single rank).  Flags:
+ * The general form of the two grouped launches above (they call it with peer_sync = null and flags = 0;
+ * peer_delta may be null, which means a single rank).  No counterpart in the reference.
+ *
+ * peer_sync (optional) points at an ojx_e8t_peer_sync block that lives INSIDE the peer-mapped output window
+ * (same offset on every rank, so the deltas of the window reach every rank's block) and is zeroed once by
+ * its owner.  It lets a chain of column-sharded launches - each one reading, as its activations, the full
+ * output its predecessor stored into this rank's window from all ranks - run without a collective or a host
+ * round trip in between: every rank must issue the same sequence of launches on the block.
+ *
+ * Flags:
  *   OJX_GEMV_STATIC_WEIGHTS  the caller promises that no kernel still running or queued ahead of this launch in
  *       `stream` WRITES the packed codes or scales of any problem (they were produced earlier and the producer
  *       has finished, the normal case for inference).  The launch is then allowed to start while its
@@ -180,12 +201,41 @@ int32_t ojx_e8t_gemv_grouped_peers(const ojx_e8t_gemv_problem* problems, int32_t
  *       predecessor only before its first read of x and its first write of y (programmatic dependent launch).
  *       Activations, outputs, bias and partial buffers may depend on the predecessor as usual.  Without the flag
  *       the launch is ordered like any other kernel.  Works inside stream capture.
- * No counterpart in the reference.
+ *   OJX_GEMV_SIGNAL_PEERS    (needs peer_sync and peer_delta) once every result of the launch has been stored into
+ *       every rank's window, this rank publishes its next epoch into flag[this rank] of every rank's block
+ *       (release at system scope, plain stores over NVLink) and advances its own epoch.
+ *   OJX_GEMV_WAIT_PEERS      (needs peer_sync) before the first read of x every CTA waits until flag[q] of the
+ *       local block has reached this rank's current epoch for every rank q, i.e. until all ranks have finished
+ *       the launch that produced x.  The wait is bounded (spin_limit polls per rank, default about a second):
+ *       when it runs out the kernel records OJX_ERR_TIMEOUT in the block's status word and in the device
+ *       status (ojx_e8t_device_status), finishes on whatever x holds, and returns - nothing hangs.
+ * Nothing is ever loaded from a peer's memory.
  */
+typedef struct {
+    int32_t epoch;       /* signalled launches of the chain completed on this rank */
+    int32_t arrived;     /* CTAs of the running launch that have stored their results */
+    int32_t status;      /* 0, or OJX_ERR_TIMEOUT after a wait that gave up */
+    int32_t spin_limit;  /* polls per awaited rank before giving up; 0 selects the default */
+    int32_t flag[8];     /* flag[q]: the epoch rank q has published into this rank's window */
+} ojx_e8t_peer_sync;
+
 #define OJX_GEMV_STATIC_WEIGHTS 1
+#define OJX_GEMV_SIGNAL_PEERS   2
+#define OJX_GEMV_WAIT_PEERS     4
+#define OJX_GEMV_TEST_LOSE_COPY 8   /* tests only: the first work item's copies are never reported complete, so the
+                                       wait on them runs into its limit (set a small one) and the error path runs */
 int32_t ojx_e8t_gemv_grouped_ex(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles,
                                 int64_t M, int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
-                                const int64_t* peer_delta, int32_t world, int32_t flags, void* stream);
+                                const int64_t* peer_delta, int32_t world, ojx_e8t_peer_sync* peer_sync,
+                                int32_t flags, void* stream);
+
+/*
+ * The wait of OJX_GEMV_WAIT_PEERS on its own, for work of another library that reads a window (an element-wise
+ * kernel between two sharded linears, say): everything enqueued in `stream` after this call runs once every rank
+ * has published the launch this rank signalled last.  Bounded like the wait inside the kernels.  No counterpart in
+ * the reference.
+ */
+int32_t ojx_e8t_peer_wait(ojx_e8t_peer_sync* peer_sync, int32_t world, void* stream);
 
 /* Lets kernels of the current device address memory that lives on `peer_device` (same node, NVLink or PCIe
  * peer): OJX_OK when access is (already) enabled, OJX_ERR_UNSUPPORTED when the two devices cannot be peers.

@@ -20,13 +20,14 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libojx_e8t.so")
 
 OJX_F32, OJX_F16, OJX_BF16 = 0, 1, 2
-OJX_GEMV_STATIC_WEIGHTS = 1
+OJX_GEMV_STATIC_WEIGHTS, OJX_GEMV_SIGNAL_PEERS, OJX_GEMV_WAIT_PEERS, OJX_GEMV_TEST_LOSE_COPY = 1, 2, 4, 8
+PEER_SYNC_BYTES = 48        # sizeof(ojx_e8t_peer_sync): epoch, arrived, status, spin_limit, flag[8]
 
 EXPORTED_SYMBOLS = (
     "ojx_e8t_version", "ojx_e8t_status_string", "ojx_e8t_encode", "ojx_e8t_decode",
     "ojx_e8t_gemv_workspace_bytes", "ojx_e8t_gemv", "ojx_e8t_gemv_tiles", "ojx_e8t_gemv_kchunks",
-    "ojx_e8t_gemv_grouped", "ojx_e8t_gemv_grouped_peers", "ojx_e8t_gemv_grouped_ex", "ojx_e8t_enable_peer_access", "ojx_e8t_gemm_workspace_bytes", "ojx_e8t_gemm", "ojx_e8t_gemm_status",
-    "ojx_e8t_generate", "ojx_e8t_last_cuda_error", "ojx_e8t_device_status",
+    "ojx_e8t_gemv_grouped", "ojx_e8t_gemv_grouped_peers", "ojx_e8t_gemv_grouped_ex", "ojx_e8t_peer_wait", "ojx_e8t_enable_peer_access", "ojx_e8t_gemm_workspace_bytes", "ojx_e8t_gemm", "ojx_e8t_gemm_status",
+    "ojx_e8t_generate", "ojx_e8t_last_cuda_error", "ojx_e8t_device_status", "ojx_e8t_poll_status", "ojx_e8t_set_wait_limit",
     "ojx_e8t_gemv_static_scratch", "ojx_e8t_gemv_static_scratch_capacity",
 )
 
@@ -80,7 +81,7 @@ class GemvProblem(ctypes.Structure):
     _fields_ = [
         ("x", ctypes.c_void_p), ("packed", ctypes.c_void_p), ("scales", ctypes.c_void_p),
         ("bias", ctypes.c_void_p), ("y", ctypes.c_void_p), ("partial", ctypes.c_void_p),
-        ("N", ctypes.c_int32), ("K", ctypes.c_int32), ("tile_begin", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("N", ctypes.c_int32), ("K", ctypes.c_int32), ("tile_begin", ctypes.c_int32), ("ldy", ctypes.c_int32),
     ]
 
 
@@ -113,7 +114,9 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ojx_e8t_gemv_grouped_peers.restype = i32
     lib.ojx_e8t_gemv_grouped_peers.argtypes = [vp, i32, i32, i64, i32, i32, i32, vp, i32, vp]
     lib.ojx_e8t_gemv_grouped_ex.restype = i32
-    lib.ojx_e8t_gemv_grouped_ex.argtypes = [vp, i32, i32, i64, i32, i32, i32, vp, i32, i32, vp]
+    lib.ojx_e8t_gemv_grouped_ex.argtypes = [vp, i32, i32, i64, i32, i32, i32, vp, i32, vp, i32, vp]
+    lib.ojx_e8t_peer_wait.restype = i32
+    lib.ojx_e8t_peer_wait.argtypes = [vp, i32, vp]
     lib.ojx_e8t_gemm_workspace_bytes.restype = sz
     lib.ojx_e8t_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     lib.ojx_e8t_gemm.restype = i32
@@ -124,6 +127,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ojx_e8t_last_cuda_error.argtypes = []
     lib.ojx_e8t_device_status.restype = i32
     lib.ojx_e8t_device_status.argtypes = []
+    lib.ojx_e8t_poll_status.restype = i32
+    lib.ojx_e8t_poll_status.argtypes = []
+    lib.ojx_e8t_set_wait_limit.restype = None
+    lib.ojx_e8t_set_wait_limit.argtypes = [ctypes.c_uint32]
     lib.ojx_e8t_generate.restype = i32
     lib.ojx_e8t_generate.argtypes = [vp, i32, i64, u64, i64, ctypes.c_float, vp]
 
@@ -146,6 +153,13 @@ def lib() -> ctypes.CDLL:
 
 def status_name(code: int) -> str:
     return lib().ojx_e8t_status_string(int(code)).decode()
+
+
+def raise_pending() -> None:
+    """Raises if a kernel launched earlier ran into the limit of one of its bounded waits (read from the library's
+    pinned status word: no synchronisation).  Called by the wrappers at the start of every decode-shape call."""
+    if lib().ojx_e8t_poll_status() != 0:
+        raise OjxError("an earlier launch gave up on a bounded device-side wait (OJX_ERR_TIMEOUT): its outputs are invalid")
 
 
 def check(code: int, what: str) -> None:

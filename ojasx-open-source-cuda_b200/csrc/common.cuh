@@ -84,8 +84,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is reached or
 // another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity, volatile int* abort_flag, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity, volatile int* abort_flag, int code,
+                                          uint32_t limit = kSpinLimit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(addr, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag != 0) return false;
     }
@@ -102,6 +103,14 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 
 // Device-side status word: a bounded wait that gave up records its code here (0 = none).
 static __device__ int g_device_status = 0;
+
+// The same event for the host, without a synchronisation: one page of host memory that is part of the
+// library image, pinned and mapped on first use, into which a kernel that gave up on a wait writes its code.
+// Kernels receive its device address as an argument (null when the mapping failed: then only
+// g_device_status is written).
+int* host_status_device_ptr();
+int  host_status_take();                       // returns the recorded code (0: none) and clears it
+uint32_t& wait_limit_override();               // 0: the built-in limit; set by ojx_e8t_set_wait_limit (tests)
 
 // Validates the device once per process per device: kernels are built for sm_100a only.
 int check_arch();
@@ -137,8 +146,9 @@ int32_t gemv_static_scratch_impl(const void* x, int x_dtype, int64_t M, const ui
 int32_t gemv_tiles_impl(int64_t N, int64_t K);
 int32_t gemv_kchunks_impl(int64_t K);
 int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
-                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world, int flags,
-                          cudaStream_t s);
+                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world,
+                          ojx_e8t_peer_sync* peer_sync, int flags, cudaStream_t s);
+int32_t peer_wait_impl(ojx_e8t_peer_sync* peer_sync, int world, cudaStream_t s);
 size_t  gemm_workspace_bytes_impl(int64_t M, int64_t N, int64_t K);
 int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                   const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,

@@ -49,14 +49,73 @@ __device__ __forceinline__ void store_any(void* y, int y_dtype, int64_t idx, flo
 struct PeerMap {
     int64_t delta[8];
     int world;
-    int pad;
+    int mode;                      // OJX_GEMV_SIGNAL_PEERS | OJX_GEMV_WAIT_PEERS, only with a sync block
+    ojx_e8t_peer_sync* sync;       // this rank's block inside the window (peers' blocks at + delta[r]), or null
+    // not about peers, but travelling in the same kernel argument:
+    int* host_status;              // mapped host word that receives the code of a wait that gave up (may be null)
+    uint32_t wait_limit;           // polls before a wait on a copy gives up
+    int lose_copy;                 // tests: never report the first item's copies complete
 };
-inline PeerMap peer_map_self() { PeerMap m = {}; m.world = 1; return m; }
+inline PeerMap peer_map_self() { PeerMap m = {}; m.world = 1; m.wait_limit = kSpinLimit; return m; }
 // The copies for the other ranks (delta != 0), kept out of line: rare, and the callers run at the register cap.
 __device__ __noinline__ void store_peers(const PeerMap& pm, void* y, int y_dtype, int64_t idx, float v) {
     for (int r = 0; r < pm.world; ++r)
         if (pm.delta[r] != 0) store_any(static_cast<uint8_t*>(y) + pm.delta[r], y_dtype, idx, v);
 }
+
+// ---- device-side ordering between the ranks of a column-sharded chain (see ojx_e8t_gemv_grouped_ex) ----
+constexpr int kPeerSpinDefault = 1 << 21;                      // polls of a system-scope load: about a second
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Called by ONE thread of every CTA after the CTA's last result store (and a __syncthreads): the CTA that
+// arrives last publishes this rank's next epoch into every rank's block.
+__device__ __noinline__ void peer_signal(const PeerMap& pm) {
+    __threadfence_system();                                    // the CTA's stores, local and remote, before the count
+    ojx_e8t_peer_sync* sy = pm.sync;
+    if (atomicAdd(&sy->arrived, 1) != (int)gridDim.x * (int)gridDim.y - 1) return;
+    __threadfence_system();                                    // every CTA's stores before the flags
+    sy->arrived = 0;
+    const int e = sy->epoch + 1;
+    int self = 0;
+    for (int r = 0; r < pm.world; ++r)
+        if (pm.delta[r] == 0) self = r;
+    for (int r = 0; r < pm.world; ++r) {
+        ojx_e8t_peer_sync* dst = reinterpret_cast<ojx_e8t_peer_sync*>(reinterpret_cast<uint8_t*>(sy) + pm.delta[r]);
+        st_release_sys(&dst->flag[self], e);
+    }
+    st_release_sys(&sy->epoch, e);
+}
+
+// Called by ONE thread of every CTA before the CTA's first read of x (followed by a __syncthreads).  Returns false
+// when a wait ran out; the failure is recorded and the kernel carries on.
+__device__ __noinline__ bool peer_wait(const PeerMap& pm) {
+    ojx_e8t_peer_sync* sy = pm.sync;
+    const int e = ld_acquire_sys(&sy->epoch);
+    const int limit = sy->spin_limit > 0 ? sy->spin_limit : kPeerSpinDefault;
+    bool ok = true;
+    for (int q = 0; q < pm.world && ok; ++q) {
+        int i = 0;
+        while (ld_acquire_sys(&sy->flag[q]) - e < 0) {
+            if (++i >= limit) { ok = false; break; }
+            __nanosleep(64);
+        }
+    }
+    if (!ok) {
+        atomicCAS(&sy->status, 0, (int)OJX_ERR_TIMEOUT);
+        atomicCAS(&g_device_status, 0, 60);
+        if (pm.host_status != nullptr) *reinterpret_cast<volatile int*>(pm.host_status) = 60;
+    }
+    return ok;
+}
+
 template <bool kBf16> __device__ __forceinline__ float load_act(const void* p, int64_t idx) {
     if (kBf16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
     return __half2float(static_cast<const __half*>(p)[idx]);
@@ -121,12 +180,18 @@ __global__ void __launch_bounds__(256, 3) gemv_reduce_kernel(const ojx_e8t_gemv_
              i += (int64_t)gridDim.x * blockDim.x) {
             float s = 0.f;
             for (int c = 0; c < kc; ++c) s += P.partial[(int64_t)c * total + i];
-            if (P.bias != nullptr) s += load_act<kBf16>(P.bias, i % P.N);
-            store_any(P.y, y_dtype, i, s);
+            const int64_t col = i / P.N, row = i - col * P.N;
+            if (P.bias != nullptr) s += load_act<kBf16>(P.bias, row);
+            const int64_t at = col * (P.ldy > 0 ? P.ldy : P.N) + row;
+            store_any(P.y, y_dtype, at, s);
 #pragma unroll 1
             for (int r = 0; r < peers.world; ++r)                  // the other ranks' windows (nothing when world == 1)
-                if (peers.delta[r] != 0) store_any(static_cast<uint8_t*>(P.y) + peers.delta[r], y_dtype, i, s);
+                if (peers.delta[r] != 0) store_any(static_cast<uint8_t*>(P.y) + peers.delta[r], y_dtype, at, s);
         }
+    }
+    if (peers.sync != nullptr && (peers.mode & OJX_GEMV_SIGNAL_PEERS)) {
+        __syncthreads();
+        if (threadIdx.x == 0) peer_signal(peers);
     }
 }
 

@@ -70,12 +70,12 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
 }
 
 // Slow path of a bounded wait, kept out of line so the loop body stays small.
-__device__ __noinline__ void a16_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    if (*abort_flag != 0) return;               // some wait already gave up: run on so that barrier counts stay matched
-    mbar_wait(bar, parity, abort_flag, code);
+__device__ __noinline__ void a16_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit) {
+    if (*abort_flag != 0) return;               // some wait already gave up: the CTA is only running out its loop
+    mbar_wait(bar, parity, abort_flag, code, limit);
 }
-__device__ __forceinline__ void a16_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    if (!mbar_try_wait(bar, parity)) a16_wait_slow(bar, parity, abort_flag, code);
+__device__ __forceinline__ void a16_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit) {
+    if (!mbar_try_wait(bar, parity)) a16_wait_slow(bar, parity, abort_flag, code, limit);
 }
 
 // Rank J (0..7) of a lane's 96-bit window, moved so that it starts at bit POS (bits outside the field are junk).
@@ -138,7 +138,15 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     const int i1 = (int)min((int64_t)total_items, per * (blockIdx.x + 1));
     // the launch that follows in the stream may start its own set-up once every CTA of this one is past this point
     if (overlap) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (i0 >= i1) return;
+    // with partial sums the outputs are stored (and signalled) by the reduce kernel that follows
+    const bool signal = peers.sync != nullptr && (peers.mode & OJX_GEMV_SIGNAL_PEERS) != 0 && (peers.mode & 0x100) == 0;
+    if (i0 >= i1) {
+        if (signal && tid == 0) {
+            if (overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+            peer_signal(peers);
+        }
+        return;
+    }
     const int nitems = i1 - i0;
     const int p0 = find_problem(probs, count, i0, 1);
 
@@ -187,7 +195,7 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
         }
         // the item's coordinates travel with its data, so only the loader keeps a cursor
         if (tid == 0) sts_u128(stage + kA16DescOff, make_uint4((uint32_t)l_prob, (uint32_t)l_chunk, (uint32_t)l_tile, (uint32_t)l_act));
-        cp_async_arrive(bar_full + 8 * istage);
+        if (!(peers.lose_copy && issued == 0 && tid == 0)) cp_async_arrive(bar_full + 8 * istage);
         ++issued;
         if (++istage == S) istage = 0;
         if (++l_tile < l_tiles) {
@@ -206,24 +214,33 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     for (int n = 0; n < S - 1 && n < nitems; ++n) issue_next();
     // activations (and the output buffers) do
     if (overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // ... and, in a column-sharded chain, on the same launch of every other rank
+    if (peers.sync != nullptr && (peers.mode & OJX_GEMV_WAIT_PEERS)) {
+        if (tid == 0) peer_wait(peers);
+        __syncthreads();
+    }
 
     const uint32_t lane_or = (uint32_t)((lane & 1) << 3);
     uint32_t xb[NB][8][4];                      // B fragments: [block][rank j][k 0-1, 2-3, 4-5, 6-7 of the rank]
     float up[NB][2];                            // 2^e of activation rows 2t, 2t+1 of the block (this lane's output columns)
     int cur_prob = -1, cur_chunk = -1, cur_K = 0;
 
-    a16_wait(bar_lut, 0u, abort_flag, 55);                          // the table has landed
+    a16_wait(bar_lut, 0u, abort_flag, 55, peers.wait_limit);        // the table has landed
     int cstage = 0;
     uint32_t cparity = 0;
     for (int n = 0; n < nitems; ++n) {
         if (issued < nitems) issue_next();                          // into the stage the previous item's barrier released
-        a16_wait(bar_full + 8 * cstage, cparity, abort_flag, 52);
+        a16_wait(bar_full + 8 * cstage, cparity, abort_flag, 52, peers.wait_limit);
+        // Once a wait has given up nothing in shared memory can be trusted (not even the item's coordinates): the
+        // warp then only keeps the block-wide barriers matched until the loop ends.
+        const bool dead = __any_sync(0xFFFFFFFFu, *abort_flag != 0);
         const uint32_t stage = ring + cstage * kA16StageBytes;
-        const uint4 desc = lds_u128(stage + kA16DescOff);
-        const int prob = (int)desc.x, chunk = (int)desc.y, tile = (int)desc.z, act = (int)desc.w;
+        uint4 desc = make_uint4(0, 0, 0, 0);
+        if (!dead) desc = lds_u128(stage + kA16DescOff);
+        const int prob = (int)desc.x, chunk = (int)desc.y, tile = (int)desc.z, act = dead ? 0 : (int)desc.w;
         if (++cstage == S) { cstage = 0; cparity ^= 1u; }
 
-        if (prob != cur_prob || chunk != cur_chunk) {
+        if (!dead && (prob != cur_prob || chunk != cur_chunk)) {
             if (prob != cur_prob) cur_K = probs[prob].K;
             cur_prob = prob;
             cur_chunk = chunk;
@@ -239,7 +256,7 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         uint4 q = make_uint4(0, 0, 0, 0);
-                        if (on) q = __ldg(xrow + j);
+                        if (on) q = __ldcg(xrow + j);            // L2: in a sharded chain x was written by other GPUs
                         xb[nb][j][0] = q.x; xb[nb][j][1] = q.y; xb[nb][j][2] = q.z; xb[nb][j][3] = q.w;
                     }
                 } else {
@@ -249,7 +266,7 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         uint4 q = make_uint4(0, 0, 0, 0);
-                        if (on) q = __ldg(xrow + j);
+                        if (on) q = __ldcg(xrow + j);            // L2: in a sharded chain x was written by other GPUs
                         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                         for (int i = 0; i < 4; ++i) amax = max(amax, max((w[i] << 16) & 0x7FFFFFFFu, w[i] & 0x7FFF0000u));
@@ -264,7 +281,7 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         uint4 q = make_uint4(0, 0, 0, 0);
-                        if (on) q = __ldg(xrow + j);
+                        if (on) q = __ldcg(xrow + j);            // L2: in a sharded chain x was written by other GPUs
                         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -332,7 +349,7 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
         __syncthreads();           // the stage is free again and every warp's partial sums are visible
 
         // ---- sum over the warps in warp order; thread tid owns element tid of the 256 NB fragment values ----
-        if (tid < 256 * NB) {
+        if (tid < 256 * NB && !dead) {
             const float* rb = red + (size_t)(n & 1) * Cfg::kRedFloats + tid;
             const int comp = tid & 3, lp = (tid >> 2) & 31, nb = (tid >> 7) % NB, tl = tid / (128 * NB);
             const int row = tile * kA16Rows + tl * 16 + (lp >> 2) + ((comp >> 1) << 3);
@@ -347,14 +364,23 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
                 if (P.partial != nullptr) P.partial[((int64_t)chunk * M + col) * rN + row] = sum;
                 else {
                     if (P.bias != nullptr) sum += load_any(P.bias, kXF16 ? OJX_F16 : OJX_BF16, row);
-                    store_any(P.y, y_dtype, (int64_t)col * rN + row, sum);
-                    if (peers.world > 1) store_peers(peers, P.y, y_dtype, (int64_t)col * rN + row, sum);
+                    const int64_t at = (int64_t)col * (P.ldy > 0 ? P.ldy : rN) + row;
+                    store_any(P.y, y_dtype, at, sum);
+                    if (peers.world > 1) store_peers(peers, P.y, y_dtype, at, sum);
                 }
             }
         }
     }
 
-    if (tid == 0 && *abort_flag != 0) atomicCAS(&g_device_status, 0, *abort_flag);
+    asm volatile("cp.async.wait_all;" ::: "memory");               // nothing of this thread is still in flight into shared memory
+    if (tid == 0 && *abort_flag != 0) {
+        atomicCAS(&g_device_status, 0, *abort_flag);
+        if (peers.host_status != nullptr) *reinterpret_cast<volatile int*>(peers.host_status) = *abort_flag;
+    }
+    if (signal) {
+        __syncthreads();
+        if (tid == 0) peer_signal(peers);
+    }
 }
 
 }  // namespace ojx

@@ -65,7 +65,10 @@ static int32_t launch_maybe_overlapped(void (*kernel)(Params...), int grid, int 
 
 template <int NB, bool kXF16>
 static int32_t launch_gemv_a16(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
-                               int M, int y_dtype, const PeerMap& peers, bool overlap, cudaStream_t s) {
+                               int M, int y_dtype, const PeerMap& peers_in, bool overlap, cudaStream_t s) {
+    PeerMap peers = peers_in;
+    peers.host_status = host_status_device_ptr();
+    peers.wait_limit = wait_limit_override() != 0 ? wait_limit_override() : kSpinLimit;
     static std::atomic<uint64_t> configured{0};
     using Cfg = A16Cfg<NB>;
     const int32_t st = ensure_dynamic_smem(gemv_a16_kernel<NB, kXF16>, Cfg::kSmem, configured);
@@ -87,8 +90,8 @@ static int32_t dispatch_gemv(bool bf16, const ojx_e8t_gemv_problem* probs, const
 }
 
 int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int total_tiles, int64_t M,
-                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world, int flags,
-                          cudaStream_t s) {
+                          int x_dtype, int y_dtype, int needs_reduce, const int64_t* peer_delta, int world,
+                          ojx_e8t_peer_sync* peer_sync, int flags, cudaStream_t s) {
     OJX_RETURN_IF(world < 1 || world > 8 || (world > 1 && !peer_delta), OJX_ERR_SHAPE);
     PeerMap peers = peer_map_self();
     if (peer_delta != nullptr) {
@@ -102,7 +105,17 @@ int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int t
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
     const bool bf = x_dtype == OJX_BF16;
     ojx_e8t_gemv_problem none = {};
-    OJX_RETURN_IF((flags & ~OJX_GEMV_STATIC_WEIGHTS) != 0, OJX_ERR_UNSUPPORTED);
+    constexpr int kKnown = OJX_GEMV_STATIC_WEIGHTS | OJX_GEMV_SIGNAL_PEERS | OJX_GEMV_WAIT_PEERS | OJX_GEMV_TEST_LOSE_COPY;
+    OJX_RETURN_IF((flags & ~kKnown) != 0, OJX_ERR_UNSUPPORTED);
+    const int sync_mode = flags & (OJX_GEMV_SIGNAL_PEERS | OJX_GEMV_WAIT_PEERS);
+    OJX_RETURN_IF(sync_mode != 0 && peer_sync == nullptr, OJX_ERR_NULL);
+    OJX_RETURN_IF((reinterpret_cast<uintptr_t>(peer_sync) & 3) != 0, OJX_ERR_ALIGN);
+    if (peer_sync != nullptr) {
+        peers.sync = peer_sync;
+        // bit 8 tells the main kernel that a reduce kernel follows and stores (and signals) in its place
+        peers.mode = sync_mode | (needs_reduce ? 0x100 : 0);
+    }
+    peers.lose_copy = (flags & OJX_GEMV_TEST_LOSE_COPY) ? 1 : 0;
     const bool overlap = (flags & OJX_GEMV_STATIC_WEIGHTS) != 0;
     const int32_t st = dispatch_gemv(bf, problems, none, count, total_tiles, (int)M, y_dtype, peers, overlap, s);
     OJX_RETURN_IF(st != OJX_OK, st);
@@ -111,6 +124,24 @@ int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int t
     dim3 grid(64, count > 64 ? 64 : count);
     if (bf) gemv_reduce_kernel<true><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype, peers);
     else gemv_reduce_kernel<false><<<grid, 256, 0, s>>>(problems, none, count, (int)M, y_dtype, peers);
+    return launch_status();
+}
+
+__global__ void peer_wait_kernel(const __grid_constant__ PeerMap peers) {
+    if (threadIdx.x == 0) peer_wait(peers);
+}
+
+// Orders everything that follows in `s` after the launch that every rank signalled last (bounded, see peer_wait).
+int32_t peer_wait_impl(ojx_e8t_peer_sync* peer_sync, int world, cudaStream_t s) {
+    OJX_RETURN_IF(!peer_sync, OJX_ERR_NULL);
+    OJX_RETURN_IF(world < 1 || world > 8, OJX_ERR_SHAPE);
+    OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
+    PeerMap peers = peer_map_self();
+    peers.world = world;
+    peers.sync = peer_sync;
+    peers.mode = OJX_GEMV_WAIT_PEERS;
+    peers.host_status = host_status_device_ptr();
+    peer_wait_kernel<<<1, 32, 0, s>>>(peers);
     return launch_status();
 }
 
@@ -132,7 +163,7 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         h.x = x; h.packed = packed; h.scales = scales; h.bias = bias; h.y = y;
         const int kc = gemv_kchunks((int)K);
         h.partial = kc > 1 ? static_cast<float*>(workspace) : nullptr;
-        h.N = (int)N; h.K = (int)K; h.tile_begin = 0; h.reserved = 0;
+        h.N = (int)N; h.K = (int)K; h.tile_begin = 0; h.ldy = 0;
         const int total = gemv_row_tiles32((int)N) * kc;
         const bool bf = x_dtype == OJX_BF16;
         const int32_t st = dispatch_gemv(bf, nullptr, h, 1, total, (int)M, y_dtype, peer_map_self(), false, s);

@@ -1,5 +1,7 @@
 // The whole library is this one translation unit: C ABI entry points (declared in
 // include/ojx_e8t.h) in front of the kernel files included below.  Built for sm_100a only.
+#include <mutex>
+
 #include "common.cuh"
 #include "codec.cuh"
 #include "gemv.cuh"
@@ -22,11 +24,47 @@ int check_arch() {
     return cached[dev] == 1 ? OJX_OK : OJX_ERR_ARCH;
 }
 
+alignas(4096) static volatile int g_host_status_page[1024];
+
+int* host_status_device_ptr() {
+    static std::once_flag once;
+    static bool registered = false;
+    std::call_once(once, [] {
+        const cudaError_t e = cudaHostRegister(const_cast<int*>(g_host_status_page), sizeof(g_host_status_page), cudaHostRegisterMapped);
+        registered = (e == cudaSuccess || e == cudaErrorHostMemoryAlreadyRegistered);
+        (void)cudaGetLastError();
+    });
+    if (!registered) return nullptr;
+    static int* cached[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cached[dev] == nullptr) {
+        int* p = nullptr;
+        if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&p), const_cast<int*>(g_host_status_page), 0) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        cached[dev] = p;
+    }
+    return cached[dev];
+}
+
+int host_status_take() {
+    const int v = g_host_status_page[0];
+    if (v != 0) g_host_status_page[0] = 0;
+    return v;
+}
+
+uint32_t& wait_limit_override() {
+    static uint32_t v = 0;
+    return v;
+}
+
 }  // namespace ojx
 
 extern "C" {
 
-int32_t ojx_e8t_version(void) { return 100; }
+int32_t ojx_e8t_version(void) { return 200; }
 
 const char* ojx_e8t_status_string(int32_t st) {
     switch (st) {
@@ -48,9 +86,17 @@ const char* ojx_e8t_last_cuda_error(void) { return cudaGetErrorString(ojx::last_
 
 int32_t ojx_e8t_device_status(void) {
     int h = 0;
+    const int zero = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) { ojx::last_cuda_error() = cudaGetLastError(); return OJX_ERR_LAUNCH; }
     if (cudaMemcpyFromSymbol(&h, ojx::g_device_status, sizeof(int)) != cudaSuccess) return OJX_ERR_LAUNCH;
+    if (h != 0 && cudaMemcpyToSymbol(ojx::g_device_status, &zero, sizeof(int)) != cudaSuccess) return OJX_ERR_LAUNCH;
+    (void)ojx::host_status_take();
     return h == 0 ? OJX_OK : OJX_ERR_TIMEOUT;
 }
+
+int32_t ojx_e8t_poll_status(void) { return ojx::host_status_take() == 0 ? OJX_OK : OJX_ERR_TIMEOUT; }
+
+void ojx_e8t_set_wait_limit(uint32_t polls) { ojx::wait_limit_override() = polls; }
 
 int32_t ojx_e8t_encode(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
                        uint8_t* packed_out, uint16_t* scales_out, void* stream) {
@@ -84,21 +130,26 @@ int32_t ojx_e8t_gemv_kchunks(int64_t K) { return ojx::gemv_kchunks_impl(K); }
 
 int32_t ojx_e8t_gemv_grouped(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles, int64_t M,
                              int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce, void* stream) {
-    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, nullptr, 1, 0, (cudaStream_t)stream);
+    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, nullptr, 1, nullptr, 0, (cudaStream_t)stream);
 }
 
 int32_t ojx_e8t_gemv_grouped_peers(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles, int64_t M,
                                    int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
                                    const int64_t* peer_delta, int32_t world, void* stream) {
     OJX_RETURN_IF(!peer_delta, OJX_ERR_NULL);
-    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, peer_delta, world, 0, (cudaStream_t)stream);
+    return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, peer_delta, world, nullptr, 0, (cudaStream_t)stream);
 }
 
 int32_t ojx_e8t_gemv_grouped_ex(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles, int64_t M,
                                 int32_t x_dtype, int32_t y_dtype, int32_t needs_reduce,
-                                const int64_t* peer_delta, int32_t world, int32_t flags, void* stream) {
+                                const int64_t* peer_delta, int32_t world, ojx_e8t_peer_sync* peer_sync, int32_t flags,
+                                void* stream) {
     return ojx::gemv_grouped_impl(problems, count, total_tiles, M, x_dtype, y_dtype, needs_reduce, peer_delta,
-                                  peer_delta ? world : 1, flags, (cudaStream_t)stream);
+                                  peer_delta ? world : 1, peer_sync, flags, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_peer_wait(ojx_e8t_peer_sync* peer_sync, int32_t world, void* stream) {
+    return ojx::peer_wait_impl(peer_sync, world, (cudaStream_t)stream);
 }
 
 int32_t ojx_e8t_enable_peer_access(int32_t peer_device) {

@@ -164,6 +164,7 @@ def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: 
     """
     n, k = int(out_features), int(in_features)
     dev, x2d, pk, sc, b = _prep_linear(x2d, packed, scales, bias, n, k)
+    _cabi.raise_pending()
     m = int(x2d.shape[0])
     ydt = out_dtype or x2d.dtype
     y = torch.empty((m, n), dtype=ydt, device=dev)
@@ -221,12 +222,16 @@ class GroupedGemv:
 
     def __init__(self, entries: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor], torch.Tensor]],
                  shapes: Sequence[Tuple[int, int]], peer_delta: Optional[Sequence[int]] = None,
-                 static_weights: bool = False):
+                 static_weights: bool = False, peer_sync: Optional[int] = None, wait_peers: bool = False,
+                 signal_peers: bool = False, extra_flags: int = 0):
         # entries: (x[M,K], packed, scales, bias-or-None, y[M,N]);  shapes: (N, K)
         # peer_delta: byte distances from this rank's output window to every rank's (see sharding.PeerWindow);
         #             when given, each result is stored into all ranks' windows by the kernel itself
         # static_weights: promise that nothing queued ahead of a call in its stream writes the packed buffers; the
         #             launch may then begin (set-up, first weight copies) while the previous kernel drains
+        # peer_sync:  device address of this rank's ojx_e8t_peer_sync block inside the peer window (PeerWindow.sync_ptr);
+        #             wait_peers: wait on the device until every rank has published the launch that produced x;
+        #             signal_peers: publish this launch to every rank once all results are stored
         if not entries:
             raise ValueError("empty problem list")
         lib = _cabi.lib()
@@ -247,9 +252,11 @@ class GroupedGemv:
                 raise ValueError("grouped launch needs K % 256 == 0")
             if x.shape != (self.M, k) or y.shape != (self.M, n) or x.dtype != self.x_dtype or y.dtype != self.y_dtype:
                 raise ValueError("inconsistent shapes or dtypes in the problem list")
+            if y.stride(1) != 1 or (self.M > 1 and y.stride(0) < n):
+                raise ValueError("y must have unit column stride (it may be a column block of a wider matrix)")
             if pk.numel() != n * k * 3 // 16 or sc.numel() != n * k // 32:
                 raise ValueError("packed/scales sizes do not match (N, K)")
-            for t in (x, pk, sc, y):
+            for t in (x, pk, sc):
                 if not t.is_contiguous() or t.data_ptr() % 16 != 0:
                     raise ValueError("buffers must be contiguous and 16-byte aligned")
             kc = lib.ojx_e8t_gemv_kchunks(k)
@@ -266,7 +273,8 @@ class GroupedGemv:
             p.x, p.packed, p.scales, p.y = x.data_ptr(), pk.data_ptr(), sc.data_ptr(), y.data_ptr()
             p.bias = bb.data_ptr() if bb is not None else None
             p.partial = (self.partials.data_ptr() + offsets[i]) if offsets[i] >= 0 else None
-            p.N, p.K, p.tile_begin, p.reserved = n, k, tile_begin, 0
+            p.N, p.K, p.tile_begin = n, k, tile_begin
+            p.ldy = int(y.stride(0)) if (self.M > 1 and y.stride(0) != n) else 0
             tile_begin += lib.ojx_e8t_gemv_tiles(n, k)
             self._keep.extend([x, pk, sc, y])
         self.count = len(entries)
@@ -275,7 +283,14 @@ class GroupedGemv:
         raw = bytes(arr)
         self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self.device)
         self.packed_bytes = sum(n * k // 4 for n, k in shapes)
-        self.flags = _cabi.OJX_GEMV_STATIC_WEIGHTS if static_weights else 0
+        if (wait_peers or signal_peers) and peer_sync is None:
+            raise ValueError("wait_peers / signal_peers need the peer_sync block of the output window")
+        if signal_peers and peer_delta is None:
+            raise ValueError("signal_peers needs peer_delta")
+        self.peer_sync = int(peer_sync) if peer_sync is not None else None
+        self.flags = ((_cabi.OJX_GEMV_STATIC_WEIGHTS if static_weights else 0) |
+                      (_cabi.OJX_GEMV_WAIT_PEERS if wait_peers else 0) | (_cabi.OJX_GEMV_SIGNAL_PEERS if signal_peers else 0) |
+                      int(extra_flags))
         self._peers = None
         if peer_delta is not None:
             if not (1 <= len(peer_delta) <= 8):
@@ -283,10 +298,11 @@ class GroupedGemv:
             self._peers = (ctypes.c_int64 * len(peer_delta))(*[int(d) for d in peer_delta])
 
     def __call__(self) -> None:
+        _cabi.raise_pending()
         with torch.cuda.device(self.device):
             st = _cabi.lib().ojx_e8t_gemv_grouped_ex(
                 self.table.data_ptr(), self.count, self.total_tiles, self.M, _dtype_code(self.x_dtype),
                 _dtype_code(self.y_dtype), self.needs_reduce,
                 ctypes.addressof(self._peers) if self._peers is not None else None,
-                len(self._peers) if self._peers is not None else 1, self.flags, _stream_ptr(self.device))
+                len(self._peers) if self._peers is not None else 1, self.peer_sync, self.flags, _stream_ptr(self.device))
         _cabi.check(st, "ojx_e8t_gemv_grouped_ex")

@@ -127,9 +127,12 @@ class PeerWindow:
     themselves - the fused form of "compute a column shard, then all-gather"
     (see ``GroupedGemv(..., peer_delta=window.delta)``).
 
-    ``local`` is this rank's buffer, laid out ``[world, ...]`` by the caller (slot r belongs to rank r);
+    ``local`` is this rank's buffer, laid out by the caller (for example ``[world, ...]`` with slot r belonging
+    to rank r, or full ``[M, N]`` matrices of which every rank fills its column block);
     ``delta[r]`` is the byte distance from ``local`` to rank r's copy as mapped here (0 for this rank).
-    The ranks must meet (``fence()``) between the kernels that write a window and anyone reading it.
+    Between the kernels that write a window and anyone reading it the ranks must either meet (``fence()``), or
+    the launches order themselves on the device through the window's ``sync_ptr`` block
+    (``GroupedGemv(..., peer_sync=window.sync_ptr, wait_peers=..., signal_peers=...)``).
     Construction is collective; it raises if the device memory cannot be shared between the ranks.
     """
 
@@ -142,8 +145,14 @@ class PeerWindow:
             raise ValueError("at most 8 ranks")
         from . import _cabi
         my_index = device.index if device.index is not None else torch.cuda.current_device()
-        self.local = torch.zeros(numel, dtype=dtype, device=device)
-        handle = self.local.untyped_storage()._share_cuda_()
+        # the payload, then (256-byte aligned) the ojx_e8t_peer_sync block, in ONE allocation: one mapping serves both
+        itemsize = torch.empty(0, dtype=dtype).element_size()
+        payload = (numel * itemsize + 255) // 256 * 256
+        self._raw = torch.zeros(payload + 256, dtype=torch.uint8, device=device)
+        self.local = self._raw[: numel * itemsize].view(dtype)
+        self.sync_ptr = int(self._raw.data_ptr()) + payload
+        self._sync_words = self._raw[payload: payload + _cabi.PEER_SYNC_BYTES].view(torch.int32)
+        handle = self._raw.untyped_storage()._share_cuda_()
         handles = [None] * self.world
         dist.all_gather_object(handles, handle, group=group)
         self._peer_storages = []
@@ -166,6 +175,24 @@ class PeerWindow:
         rank frees its own buffer or exits."""
         self._peer_storages.clear()
         self.delta = [0] * len(self.delta)
+
+    def sync_status(self) -> int:
+        """Status word of the device-side ordering block: 0, or the (negative) code of a wait that gave up.
+        Synchronises the current stream."""
+        return int(self._sync_words[2].item())
+
+    def set_spin_limit(self, polls: int) -> None:
+        """Polls per awaited rank before a device-side wait gives up (0: the library default, about a second)."""
+        self._sync_words[3] = int(polls)
+
+    def wait_peers(self) -> None:
+        """Stream-ordered, device-side: what follows on the current stream runs once every rank has published the
+        launch this rank signalled last (for work of other libraries that reads the window)."""
+        from . import _cabi
+        with torch.cuda.device(self.local.device):
+            st = _cabi.lib().ojx_e8t_peer_wait(self.sync_ptr, self.world,
+                                               int(torch.cuda.current_stream(self.local.device).cuda_stream))
+        _cabi.check(st, "ojx_e8t_peer_wait")
 
     def fence(self) -> None:
         """All ranks' earlier kernels on their current streams have completed once this returns on the stream
