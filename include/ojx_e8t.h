@@ -264,6 +264,22 @@ int32_t ojx_e8t_gemm(const void* x, int32_t x_dtype, int64_t M,
 int32_t ojx_e8t_gemm_status(const void* workspace, void* stream);
 
 /*
+ * Backward of the packed linear with respect to its input: dX[M, K] = dY[M, N] . W[N, K], W given packed, on the
+ * same tcgen05 pipeline (the contraction runs over the weight rows; the decoded weights enter the MMAs as an
+ * MN-major operand, so no dense or transposed copy of W ever exists).  Replaces the decode-then-matmul of
+ * _FusedE8GEMMFunction.backward (ojasx2/math/lattice.py:642-717) and the reference's native
+ * fused_ternary_e8_gemm_backward_dx (ojasx2/math/csrc/ojasx_math_core.hpp:641-702, schema
+ * ojasx_math_bindings.cpp:594).  Requires K % 256 == 0, N % 8 == 0, group 32, bf16 or fp16 dY; fp32 accumulation;
+ * workspace as for ojx_e8t_gemm (size from ojx_e8t_gemm_dx_workspace_bytes; ojx_e8t_gemm_status reports on it).
+ */
+size_t  ojx_e8t_gemm_dx_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int32_t ojx_e8t_gemm_dx(const void* grad_y, int32_t gy_dtype, int64_t M,
+                        const uint8_t* packed, const uint16_t* scales,
+                        int64_t N, int64_t K, int32_t group,
+                        void* dx, int32_t dx_dtype,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Seeded synthetic data, generated on the device: element i of stream `seed` is a sum of twelve
  * 24-bit uniforms from splitmix64, scaled to ~N(0, sigma), then rounded to `dtype`.  Integer-exact,
  * so host and device produce identical bits.  Used by the benchmark to fill 70B-shaped weights

@@ -154,5 +154,9 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
                   const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
                   void* workspace, size_t workspace_bytes, cudaStream_t s);
 int32_t gemm_status_impl(const void* workspace, cudaStream_t s);
+size_t  gemm_dx_workspace_bytes_impl(int64_t M, int64_t N, int64_t K);
+int32_t gemm_dx_impl(const void* gy, int gy_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                     int64_t N, int64_t K, int group, void* dx, int dx_dtype,
+                     void* workspace, size_t workspace_bytes, cudaStream_t s);
 
 }  // namespace ojx

@@ -172,6 +172,19 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                                  // SWIZZLE_128B
     return d;
 }
+// MN-major operand tile with the 128-byte swizzle (used for the transposed product dX = dY . W): 64 consecutive
+// "M" elements (here: k) are contiguous (one 128-byte row), eight consecutive "K" indices (here: weight rows n)
+// form a 1024-byte swizzle atom; atoms follow each other along K every `kDxSbo` bytes and along M every `kDxLbo`.
+constexpr uint32_t kDxSbo = 1024, kDxLbo = 8192;
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);            // start address, 16-byte units
+    d |= (uint64_t)(kDxLbo >> 4) << 16;                      // leading byte offset: next block of 64 M elements
+    d |= (uint64_t)(kDxSbo >> 4) << 32;                      // stride byte offset: next group of eight K indices
+    d |= (uint64_t)1 << 46;                                  // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                                  // SWIZZLE_128B
+    return d;
+}
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -267,6 +280,12 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// kDX = false: y[M, N] = x . W^T, contraction over K (the weights' row direction), p.N = weight rows, p.K = columns.
+// kDX = true:  dX[M, K] = dY . W, contraction over the weight ROWS.  The roles are swapped in the parameters: p.N is
+//              the number of weight COLUMNS (the output's feature dimension, tiled like N above) and p.K the number
+//              of weight rows (the contraction length, any positive value: the last block is zero-filled).  The
+//              decoded weights enter the MMA as an MN-major operand, so a decoded rank is still one 16-byte store.
+template <bool kDX>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -325,7 +344,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     const int m_blocks = (p.M + p.bn - 1) / p.bn;
     const uint32_t x_bytes = (uint32_t)p.bn * kGemmBK * 2;
     const int tiles = min(n_blocks * m_blocks, p.tile_limit);
-    const int k_blocks = p.K / kGemmBK;
+    const int k_blocks = (p.K + kGemmBK - 1) / kGemmBK;
 
     if (warp == 12) {
         // ---------------- TMA producer ----------------
@@ -372,10 +391,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
 #pragma unroll
                     for (int k = 0; k < kGemmBK / 16; ++k) {
                         const uint64_t bd = umma_desc_sw128(x_addr + k * 32);
-                        tc_mma_f16(tmem_base, umma_desc_sw128(a_addr + k * 32), bd, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                        if (p.rows == kGemmBM)
-                            tc_mma_f16(tmem_base + kGemmBN, umma_desc_sw128(a_addr + kGemmHalf * 128 + k * 32), bd, p.idesc,
-                                       (kb > 0 || k > 0) ? 1u : 0u);
+                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                        if constexpr (kDX) {
+                            // sixteen weight rows = two swizzle atoms along the contraction; 128 outputs = two 64-wide blocks
+                            tc_mma_f16(tmem_base, umma_desc_mn_sw128(a_addr + k * 2 * kDxSbo), bd, p.idesc, acc);
+                            if (p.rows == kGemmBM)
+                                tc_mma_f16(tmem_base + kGemmBN, umma_desc_mn_sw128(a_addr + 2 * kDxLbo + k * 2 * kDxSbo), bd, p.idesc, acc);
+                        } else {
+                            tc_mma_f16(tmem_base, umma_desc_sw128(a_addr + k * 32), bd, p.idesc, acc);
+                            if (p.rows == kGemmBM)
+                                tc_mma_f16(tmem_base + kGemmBN, umma_desc_sw128(a_addr + kGemmHalf * 128 + k * 32), bd, p.idesc, acc);
+                        }
                     }
                     tc_commit(empty_bar(s));           // frees the stage once these MMAs have read it
                 }
@@ -384,6 +410,71 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         }
     } else if (warp >= 4 && (warp - 4) * 32 < p.rows) {
         // ---------------- decoders (warps beyond the tile's rows stay idle) ----------------
+        if constexpr (kDX) {
+            // Thread (j, kq) of a stage decodes weight row kb*64 + j, columns [64 kq, 64 kq + 64) of the tile's column range:
+            // eight ranks = 12 bytes of codes and two scales, each rank one 16-byte chunk of the MN-major tile.
+            const int r = (warp - 4) * 32 + lane;
+            const int j = r & 63, kq = r >> 6;
+            const uint8_t* digit_lane = reinterpret_cast<const uint8_t*>(lut) + (lane & (kGemmDigitCopies - 1)) * 8;
+            const int64_t row_bytes = (int64_t)p.N * 3 / 16, row_scales = p.N / 32;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int n_blk = tile % n_blocks;
+                const int col0 = n_blk * p.rows + kq * 64;                       // first weight column of this thread
+                const uint8_t* cbase = p.packed + (int64_t)col0 * 3 / 16;
+                const uint16_t* sbase = p.scales + col0 / 32;
+                auto fetch = [&](int kb, uint32_t (&cw)[3], uint32_t& sw) {
+                    const int row = kb * kGemmBK + j;
+                    if (row < p.K && col0 < p.N) {
+                        const uint32_t* cp = reinterpret_cast<const uint32_t*>(cbase + (int64_t)row * row_bytes);
+                        cw[0] = __ldg(cp); cw[1] = __ldg(cp + 1); cw[2] = __ldg(cp + 2);
+                        sw = __ldg(reinterpret_cast<const uint32_t*>(sbase + (int64_t)row * row_scales));
+                    } else {                                                     // beyond the matrix: rank of the zero vector, scale 0
+                        cw[0] = 0x68668668u; cw[1] = 0x86686686u; cw[2] = 0x66866866u; sw = 0u;   // rank 1640 eight times
+                    }
+                };
+                uint32_t nw[3], ns;
+                fetch(0, nw, ns);
+                for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+                    uint32_t cw[4] = {nw[0], nw[1], nw[2], 0u};
+                    const uint32_t sw = ns;
+                    if (kb + 1 < k_blocks) fetch(kb + 1, nw, ns);                // the next stage's words travel during this one's decode
+                    const int s = it % kGemmStages;
+                    const uint32_t ph = (it / kGemmStages) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 4)) { ok = false; break; }
+                    uint8_t* arow = smem + kGemmStages * kXStageBytes + s * kAStageBytes + kq * kDxLbo + (j >> 3) * kDxSbo + (j & 7) * 128;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint2 lo8[4], hi8[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int c = half * 4 + q;
+                            const int bit = 12 * c, w = bit >> 5, sh = bit & 31;
+                            uint32_t R;                              // 2 * rank
+                            if (sh + 12 <= 32) R = sh >= 1 ? (cw[w] >> (sh - 1)) : (cw[w] << 1);
+                            else R = __funnelshift_r(cw[w], cw[w + 1], sh - 1);
+                            R &= 0x1FFEu;
+                            const uint32_t v = (R * 6473u) >> 19;    // R div 81 (exact for R < 6562)
+                            const uint32_t u = R - 81u * v;
+                            lo8[q] = *reinterpret_cast<const uint2*>(digit_lane + u * (kGemmDigitCopies * 8));
+                            hi8[q] = *reinterpret_cast<const uint2*>(digit_lane + v * (kGemmDigitCopies * 8));
+                        }
+                        const uint32_t sc2 = prmt(sw, 0u, half == 0 ? 0x1010u : 0x3232u);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int c = half * 4 + q;
+                            const uint4 v = make_uint4(hmul2_u32(lo8[q].x, sc2), hmul2_u32(lo8[q].y, sc2),
+                                                       hmul2_u32(hi8[q].x, sc2), hmul2_u32(hi8[q].y, sc2));
+                            *reinterpret_cast<uint4*>(arow + ((c ^ (j & 7)) << 4)) = v;
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_bar(s));
+                }
+            }
+        } else {
         const int r = (warp - 4) * 32 + lane;           // row of the 256-row tile
         const uint8_t* digit_lane = reinterpret_cast<const uint8_t*>(lut) + (lane & (kGemmDigitCopies - 1)) * 8;
         uint32_t it = 0;
@@ -443,6 +534,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
                     if (lane == 0) mbar_arrive(full_bar(s));
                 }
             }
+        }
         }
     } else if (warp < 4) {
         // ---------------- epilogue (warps 0-3 own TMEM lanes 32*warp ..) ----------------
@@ -538,12 +630,8 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
             }
     }
 
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes) != cudaSuccess)
-            return OJX_ERR_LAUNCH;
-        configured = true;
-    }
+    static std::atomic<uint64_t> configured{0};                  // one bit per device: the opt-in is per context
+    OJX_RETURN_IF(ensure_dynamic_smem(gemm_tcgen05_kernel<false>, kGemmSmemBytes, configured) != OJX_OK, OJX_ERR_LAUNCH);
     if (convert) {
         if (K <= 4096)
             normalize_rows_bf16_to_f16_kernel<32, 16><<<(unsigned)((M + 7) / 8), 256, 0, s>>>(
@@ -587,7 +675,7 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         const int64_t all = ((Ns + rows - 1) / rows) * ((Ms + bn - 1) / bn);
         prm.tile_limit = (int)(all < tile_limit ? all : tile_limit);
         const int grid = prm.tile_limit < num_sms() ? prm.tile_limit : num_sms();
-        gemm_tcgen05_kernel<<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+        gemm_tcgen05_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
         return launch_status();
     };
 
@@ -603,6 +691,96 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         return launch_region((n_blocks - leftover) * rows, (m_blocks - 1) * bn, kGemmHalf, 128, 1 << 30);
     }
     return launch_region(0, 0, rows, bn, 1 << 30);
+}
+
+// dX[M, K] = dY[M, N] . W[N, K] without ever materialising W (the backward of the linear with respect to its
+// input: ojasx2/math/lattice.py:642-717, native form ojasx2/math/csrc/ojasx_math_core.hpp:641-702).
+// Same pipeline as the forward kernel; the contraction runs over the weight rows.
+inline bool gemm_dx_ok(int64_t M, int64_t N, int64_t K, int group, int gy_dtype) {
+    return M >= 1 && N >= 8 && N % 8 == 0 && K >= 256 && K % 256 == 0 && group == 32 &&
+           (gy_dtype == OJX_BF16 || gy_dtype == OJX_F16) && M < (1 << 30) && N < (1 << 30) && K < (1 << 30);
+}
+size_t gemm_dx_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
+    (void)K;
+    if (M <= 0 || N <= 0) return 256;
+    return 256 + gemm_up_bytes(M) + (size_t)M * (size_t)N * 2;
+}
+
+int32_t gemm_dx_impl(const void* gy, int gy_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                     int64_t N, int64_t K, int group, void* dx, int dx_dtype,
+                     void* workspace, size_t workspace_bytes, cudaStream_t s) {
+    OJX_RETURN_IF(!gy || !packed || !scales || !dx, OJX_ERR_NULL);
+    OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0, OJX_ERR_SHAPE);
+    OJX_RETURN_IF(dtype_size(gy_dtype) == 0 || dtype_size(dx_dtype) == 0, OJX_ERR_DTYPE);
+    OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
+    group = effective_group(group);
+    OJX_RETURN_IF(!gemm_dx_ok(M, N, K, group, gy_dtype), OJX_ERR_UNSUPPORTED);
+    OJX_RETURN_IF(((reinterpret_cast<uintptr_t>(gy) | reinterpret_cast<uintptr_t>(packed) |
+                    reinterpret_cast<uintptr_t>(scales)) & 15) != 0, OJX_ERR_ALIGN);
+    const bool convert = gy_dtype == OJX_BF16;
+    const size_t need = convert ? gemm_dx_workspace_bytes_impl(M, N, K) : 256;
+    OJX_RETURN_IF(!workspace || workspace_bytes < need, OJX_ERR_WORKSPACE);
+    OJX_RETURN_IF((reinterpret_cast<uintptr_t>(workspace) & 255) != 0, OJX_ERR_ALIGN);
+    PFN_encodeTiled encode = get_encode_tiled();
+    OJX_RETURN_IF(encode == nullptr, OJX_ERR_LAUNCH);
+
+    float* up = convert ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256) : nullptr;
+    void* gy_f16 = convert ? static_cast<void*>(static_cast<uint8_t*>(workspace) + 256 + gemm_up_bytes(M)) : const_cast<void*>(gy);
+
+    // tile shape over (K outputs) x (M tokens): same cost model as the forward launch
+    int rows = kGemmBM, bn = kGemmBN;
+    {
+        double best = 1e30;
+        const int cand_rows[2] = {256, 128}, cand_bn[2] = {256, 128};
+        for (int ri = 0; ri < 2; ++ri)
+            for (int bi = 0; bi < 2; ++bi) {
+                const int64_t t = ((K + cand_rows[ri] - 1) / cand_rows[ri]) * ((M + cand_bn[bi] - 1) / cand_bn[bi]);
+                const int64_t waves = (t + num_sms() - 1) / num_sms();
+                const double penalty = (cand_rows[ri] == 128 ? 1.25 : 1.0) * (cand_bn[bi] == 128 ? 1.5 : 1.0);
+                const double cost = (double)waves * cand_rows[ri] * cand_bn[bi] * penalty;
+                if (cost < best) { best = cost; rows = cand_rows[ri]; bn = cand_bn[bi]; }
+            }
+    }
+    static std::atomic<uint64_t> configured{0};
+    OJX_RETURN_IF(ensure_dynamic_smem(gemm_tcgen05_kernel<true>, kGemmSmemBytes, configured) != OJX_OK, OJX_ERR_LAUNCH);
+    if (convert) {
+        // per-token power-of-two factors exactly as in the forward launch; rows here are N long (any multiple of 8)
+        if (N <= 4096)
+            normalize_rows_bf16_to_f16_kernel<32, 16><<<(unsigned)((M + 7) / 8), 256, 0, s>>>(
+                static_cast<const __nv_bfloat16*>(gy), static_cast<__half*>(gy_f16), up, M, N, static_cast<int32_t*>(workspace));
+        else
+            normalize_rows_bf16_to_f16_kernel<256, 8><<<(unsigned)M, 256, 0, s>>>(
+                static_cast<const __nv_bfloat16*>(gy), static_cast<__half*>(gy_f16), up, M, N, static_cast<int32_t*>(workspace));
+        if (cudaGetLastError() != cudaSuccess) return OJX_ERR_LAUNCH;
+    } else if (cudaMemsetAsync(workspace, 0, 4, s) != cudaSuccess) {
+        return OJX_ERR_LAUNCH;
+    }
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)bn};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, gy_f16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return OJX_ERR_LAUNCH;
+    GemmParams prm;
+    prm.packed = packed; prm.scales = scales; prm.bias = nullptr;
+    prm.y = dx;
+    prm.status = static_cast<int32_t*>(workspace);
+    prm.M = (int)M;
+    prm.N = (int)K;                    // roles swapped: the output's feature dimension is the weight columns ...
+    prm.K = (int)N;                    // ... and the contraction runs over the weight rows
+    prm.y_stride = (int)K;
+    prm.y_dtype = dx_dtype; prm.bias_dtype = gy_dtype;
+    prm.up = up;
+    prm.rows = rows; prm.bn = bn;
+    // as the forward descriptor, plus bit 15: the A operand is MN-major
+    prm.idesc = (1u << 4) | (1u << 15) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kGemmHalf >> 4) << 24);
+    const int64_t all = ((K + rows - 1) / rows) * ((M + bn - 1) / bn);
+    prm.tile_limit = (int)(all < (1 << 30) ? all : (1 << 30));
+    const int grid = prm.tile_limit < num_sms() ? prm.tile_limit : num_sms();
+    gemm_tcgen05_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+    return launch_status();
 }
 
 int32_t gemm_status_impl(const void* workspace, cudaStream_t s) {

@@ -52,17 +52,15 @@ def fused_ternary_e8_gemm_bwd_dx(grad_y: torch.Tensor, packed_weight: torch.Tens
                                  in_features: int, group_size: int = 32) -> torch.Tensor:
     """Same schema as the reference's ``fused_ternary_e8_gemm_bwd_dx(Tensor grad_y, Tensor packed_weight,
     Tensor block_scales, int in_features, int group_size=32) -> Tensor``
-    (``ojasx_math_bindings.cpp:479-533,594``): ``dX [M, K] = dY [M, N] . W [N, K]``.  Not on the accelerated
-    path: the weights are decoded once by the decode kernel and multiplied with ``torch.matmul``."""
+    (``ojasx_math_bindings.cpp:479-533,594``): ``dX [M, K] = dY [M, N] . W [N, K]``, computed by the transposed
+    tensor-core kernel straight from the packed codes for 16-bit gradients (``ops.linear_dx``)."""
     if grad_y.dim() != 2 or packed_weight.dim() != 2 or block_scales.dim() != 2:
         raise RuntimeError("fused_ternary_e8_gemm_bwd_dx expects 2-D grad_y, packed_weight and block_scales")
     n = int(packed_weight.shape[0])
     if int(grad_y.shape[1]) != n or int(packed_weight.shape[1]) * 16 != int(in_features) * 3:
         raise RuntimeError("fused_ternary_e8_gemm_bwd_dx: shapes do not match")
-    del group_size
     scales = block_scales if block_scales.dtype == torch.float16 else block_scales.to(torch.float16)
-    w = ops.decode(packed_weight.contiguous().view(-1), scales.contiguous().view(-1), (n, int(in_features)), grad_y.dtype)
-    return grad_y.matmul(w)
+    return ops.linear_dx(grad_y, packed_weight.contiguous().view(-1), scales.contiguous().view(-1), n, int(in_features), group_size)
 
 
 def install_into_reference() -> bool:

@@ -107,8 +107,9 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
     """``y = x . dequant(W)^T + bias`` straight from the packed codes.
 
     Nine inputs and nine gradients, as in the reference (``lattice.py:551-563,717``).  Forward runs the
-    fused kernels; x is not saved for backward (only the packed buffers are).  Backward (outside the
-    accelerated path) decodes W once with the decode kernel and multiplies with ``torch.matmul``.
+    fused kernels; x is not saved for backward (only the packed buffers are).  Backward computes
+    ``dX = dY . W`` with the transposed tensor-core kernel straight from the packed codes for 16-bit
+    gradients (``ops.linear_dx``); fp32 gradients decode W with the decode kernel and multiply.
     """
 
     @staticmethod
@@ -123,6 +124,7 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
         ctx.out_features = out_features
         ctx.has_bias = bias is not None
         ctx.use_hadamard = use_hadamard
+        ctx.group_size = group_size
         x_2d = x_rot.reshape(-1, in_features)
         y_2d = ops.linear(x_2d, packed_weight, block_scales, bias, out_features, in_features, group_size)
         return y_2d.reshape(*x_rot.shape[:-1], out_features)
@@ -131,8 +133,8 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
     def backward(ctx, grad_y):
         packed_weight, block_scales = ctx.saved_tensors
         gy_2d = grad_y.reshape(-1, ctx.out_features).contiguous()
-        w = ops.decode(packed_weight, block_scales, (ctx.out_features, ctx.in_features), ctx.x_dtype)
-        grad_x = gy_2d.to(ctx.x_dtype).matmul(w).reshape(ctx.x_shape)
+        grad_x = ops.linear_dx(gy_2d.to(ctx.x_dtype), packed_weight, block_scales, ctx.out_features, ctx.in_features,
+                               ctx.group_size).reshape(ctx.x_shape)
         if ctx.use_hadamard and ctx.in_features % 32 == 0:
             grad_x = fwht_block32(grad_x)
         grad_bias = gy_2d.sum(dim=0) if ctx.has_bias else None

@@ -197,6 +197,40 @@ def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: 
     return y
 
 
+def linear_dx(grad_y2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, out_features: int, in_features: int,
+              group_size: int = 32, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """dX[M, K] = dY[M, N] . dequant(W)[N, K] straight from the packed codes (``ojx_e8t_gemm_dx``): the backward of
+    :func:`linear` with respect to its input, without a decoded copy of W.  Shapes the tensor-core kernel does not
+    take (fp32 gradients, K % 256 != 0, N % 8 != 0, another group size) decode W with the decode kernel and multiply."""
+    n, k = int(out_features), int(in_features)
+    dev = _require_cuda(grad_y2d, packed, scales)
+    if grad_y2d.dim() != 2 or grad_y2d.shape[1] != n:
+        raise ValueError(f"grad_y must be [M, {n}], got {tuple(grad_y2d.shape)}")
+    if packed.dtype != torch.uint8 or scales.dtype != torch.float16:
+        raise TypeError("packed must be uint8 and scales float16")
+    gy = grad_y2d.contiguous()
+    m = int(gy.shape[0])
+    ydt = out_dtype or gy.dtype
+    g = effective_group(group_size)
+    if m == 0:
+        return torch.empty((0, k), dtype=ydt, device=dev)
+    fast = (gy.dtype in (torch.bfloat16, torch.float16) and k % 256 == 0 and n % 8 == 0 and g == 32
+            and (k * 3 // 16) * n == packed.numel())
+    if not fast:
+        w = decode(packed, scales, (n, k), gy.dtype if gy.dtype.is_floating_point else torch.float32)
+        return gy.matmul(w).to(ydt)
+    _cabi.raise_pending()
+    pk, sc = packed.contiguous(), scales.contiguous()
+    dx = torch.empty((m, k), dtype=ydt, device=dev)
+    lib = _cabi.lib()
+    with torch.cuda.device(dev):
+        ws = _gemm_scratch(dev, lib.ojx_e8t_gemm_dx_workspace_bytes(m, n, k))
+        st = lib.ojx_e8t_gemm_dx(gy.data_ptr(), _dtype_code(gy.dtype), m, pk.data_ptr(), sc.data_ptr(), n, k, g,
+                                 dx.data_ptr(), _dtype_code(ydt), ws.data_ptr(), ws.numel(), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_gemm_dx")
+    return dx
+
+
 def _gemm_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     """256-byte aligned scratch for the prefill kernel (status block + fp16 copy of bf16 activations)."""
     buf = scratch(device, nbytes + 256, "gemm")

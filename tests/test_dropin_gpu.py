@@ -160,6 +160,46 @@ def test_prefill_2048_tokens_full_size_shapes(P, k, n):
     _check_against_dense(P, k, n, 2048, "gemm")
 
 
+@pytest.mark.parametrize("k,n,m,dt", [(256, 64, 16, torch.float16), (512, 200, 300, torch.bfloat16), (4096, 1024, 2048, torch.bfloat16),
+                                       (1024, 4096, 513, torch.bfloat16), (14336, 4096, 256, torch.float16)])
+def test_backward_dx_kernel_matches_dense_product(P, k, n, m, dt):
+    """dX = dY . W from the packed codes (contraction over the weight rows on the tensor cores) against a dense fp32
+    product with the bit-exact decoded weights: ragged token blocks, a contraction length that is not a multiple
+    of the 64-row block, long and short contractions."""
+    dev = torch.device(DEV)
+    w = P.ops.generate(n * k, 700 + n, 0.02, torch.float16, dev).view(n, k)
+    pk, sc = P.ops.encode(w, 32)
+    del w
+    wd = P.ops.decode(pk, sc, (n, k), torch.float32)
+    gy = P.ops.generate(m * n, 701 + m, 1.0, dt, dev).view(m, n)
+    gy[1] *= 1.0e3
+    gy[m - 1] *= 1.0e-3
+    dx = P.ops.linear_dx(gy, pk, sc, n, k, 32)
+    P.ops.gemm_status(dev)
+    assert dx.dtype == dt and tuple(dx.shape) == (m, k)
+    ref = gy.float() @ wd
+    for rows in (slice(0, 1), slice(1, 2), slice(m - 1, m), slice(0, m)):
+        d = dx[rows].float() - ref[rows]
+        assert float(d.norm() / ref[rows].norm()) <= 2e-3, (k, n, m, rows)
+    dx32 = P.ops.linear_dx(gy, pk, sc, n, k, 32, out_dtype=torch.float32)
+    assert float((dx32 - ref).norm() / ref.norm()) <= 2e-5            # fp32 accumulation of exact products
+
+
+def test_autograd_backward_uses_the_packed_weights(P):
+    dev = torch.device(DEV)
+    lin = torch.nn.Linear(512, 96, bias=True).to(dev)
+    layer = P.E8LatticeLinear.from_linear(lin, bitrate=1.5, group_size=32)
+    x = torch.randn(6, 7, 512, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    y = layer(x)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    w = layer.unpack_weights(torch.float32)
+    ref = gy.float().reshape(-1, 96) @ w
+    assert x.grad.dtype == torch.bfloat16
+    assert float((x.grad.float().reshape(-1, 512) - ref).norm() / ref.norm()) <= 4e-3        # bf16 output rounding
+    assert layer.bias.grad is not None and float((layer.bias.grad.float() - gy.float().sum((0, 1))).abs().max()) < 0.1
+
+
 def test_activation_outliers_nan_and_inf(P, oracle):
     """One huge activation per 256-wide slice must not wipe out its neighbours, and non-finite activations
     must show up in the outputs the way a dense product shows them (rows of the batch they belong to)."""
