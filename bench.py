@@ -40,12 +40,11 @@ WORKLOAD = ("decode GEMV sweep, Llama-3-8B linear shapes (K->N 4096->4096, 4096-
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch from the ncu captures summarised under profiles/
 # (K=4096, N=14336, 16 matrices per launch: 234.9 MB of codes + scales, plus x and y, are the algorithmic bytes).
 NCU_TRAFFIC = {
-    "gemv_a16_kernel<1> (1-8 rows, captured at 4)": {"dram_bytes": 238.8e6, "algorithmic_bytes": 237.2e6,
-                                                      "profile": "profiles/gemv_a16_kernel_K4096_N14336_R16_M4.md"},
-    "gemv_a16_kernel<2> (9-16 rows, captured at 16)": {"dram_bytes": 243.1e6, "algorithmic_bytes": 244.3e6,
-                                                        "profile": "profiles/gemv_a16_kernel_K4096_N14336_R16_M16.md"},
+    "gemv_a16_kernel<1>": {"dram_bytes": 239.95e6, "algorithmic_bytes": 237.2e6, "captured_at_rows": 4,
+                           "profile": "profiles/gemv_a16_kernel_K4096_N14336_R16_M4.md"},
+    "gemv_a16_kernel<2>": {"dram_bytes": 245.26e6, "algorithmic_bytes": 244.3e6, "captured_at_rows": 16,
+                           "profile": "profiles/gemv_a16_kernel_K4096_N14336_R16_M16.md"},
 }
-TRAFFIC_PER_LAUNCH = NCU_TRAFFIC["gemv_a16_kernel<2> (9-16 rows, captured at 16)"]["dram_bytes"]
 # Llama-3-70B linear shapes (N, K) of one layer: q, k, v, o, gate, up, down
 L70 = [(8192, 8192), (1024, 8192), (1024, 8192), (8192, 8192), (28672, 8192), (28672, 8192), (8192, 28672)]
 L8 = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096), (4096, 14336)]
@@ -339,7 +338,7 @@ def main():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
                     help="N > 1: kernels store their column shard into every rank's output window (fused), NCCL all-gather "
                          "per launch, or no exchange at all (sharded compute only, for attribution)")
-    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "encode", "decode"],
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "gemm_dx", "encode", "decode"],
                     help="run a few launches of ONE kernel on a small case and exit (used for ncu captures)")
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--N", type=int, default=4096)
@@ -504,6 +503,35 @@ def main():
 
     ms_per_step = timed_steps(step, args.steps)
     value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # Per-kernel launch durations for the roofline: the same passes once more with a pair of CUDA events around every
+    # launch (recorded on the launching stream, read after the loop: no synchronisation inside the pass).  Kept apart
+    # from the headline timing because an event between two launches removes their programmatic overlap.
+    def instrumented(reps):
+        pairs = {key: [] for key in groups}
+        for _ in range(reps):
+            for b in BATCHES:
+                for si in range(len(SHAPES)):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(); groups[(si, b)](); e1.record()
+                    pairs[(si, b)].append((e0, e1))
+            if fused:
+                arena.fence()
+        torch.cuda.synchronize()
+        return {key: statistics.mean(a.elapsed_time(c) for a, c in v) for key, v in pairs.items()}
+    launch_ms = instrumented(max(3, args.steps // 2))
+    per_kernel = {}
+    for name, rows in (("gemv_a16_kernel<1>", (1, 4)), ("gemv_a16_kernel<2>", (16,))):
+        keys_k = [(si, b) for (si, b) in launch_ms if b in rows]
+        t = sum(launch_ms[k_] for k_ in keys_k)
+        algo = sum(R * (SHAPES[si][0] * SHAPES[si][1] // 4 + b * SHAPES[si][0] * 2 + b * SHAPES[si][1] * 2) // world for si, b in keys_k)
+        per_kernel[name] = {"launches_per_pass": len(keys_k), "avg_launch_ms": t / len(keys_k), "share_of_pass": None,
+                            "algorithmic_bytes_per_avg_launch": algo / len(keys_k),
+                            "achieved_GBps": algo / (t * 1e-3) / 1e9, "frac": algo / (t * 1e-3) / 1e9 / hbm_peak}
+    tot = sum(v["avg_launch_ms"] * v["launches_per_pass"] for v in per_kernel.values())
+    for v in per_kernel.values():
+        v["share_of_pass"] = v["avg_launch_ms"] * v["launches_per_pass"] / tot
+    dominant = max(per_kernel, key=lambda k_: per_kernel[k_]["share_of_pass"])
     no_exchange = None
     if world > 1:
         for _ in range(2):
@@ -588,12 +616,17 @@ def main():
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": sweep_config(R, launches_per_step, parallelism, bytes_per_step / 3 / 1e9),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s", "frac": achieved / (hbm_peak * world),
-                         "traffic": TRAFFIC_PER_LAUNCH, "traffic_per_kernel": NCU_TRAFFIC,
-                         "kernel": "gemv_a16_kernel (one grouped launch per shape and batch)",
+            "roofline": {"bound": "hbm", "kernel": dominant + " (the instance with the largest share of a pass: %.0f %%)" % (100 * per_kernel[dominant]["share_of_pass"]),
+                         "achieved": per_kernel[dominant]["achieved_GBps"], "peak": hbm_peak, "unit": "GB/s",
+                         "frac": per_kernel[dominant]["frac"],
+                         "traffic": NCU_TRAFFIC[dominant]["dram_bytes"], "traffic_per_kernel": NCU_TRAFFIC,
+                         "per_kernel": per_kernel,
+                         "whole_pass": {"achieved": achieved, "peak": hbm_peak * world, "frac": achieved / (hbm_peak * world),
+                                        "note": "(packed + activation + output bytes of a pass) / time of a pass, all GPUs together, launch gaps included"},
                          "peak_source": peak_src + " (MEASURED_PEAKS.json hbm_gbs)" if peak_src == "measured" else peak_src,
-                         "note": "achieved = (packed + activation + output bytes of a pass) / time of a pass, all GPUs together; launch gaps included; "
-                                 "peak = measured per-GPU HBM bandwidth x n_gpus; per-launch figures under decode_detail"},
+                         "note": "achieved = this rank's algorithmic bytes (codes + scales + x + y) of the kernel's launches / their CUDA-event "
+                                 "durations, measured in an instrumented pass; peak = measured per-GPU HBM copy bandwidth; traffic = dram bytes "
+                                 "read + written by ONE profiled launch (16 matrices of 14336 x 4096, see profiles/), algorithmic bytes of that launch beside it"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d_per_step * world,
                     "d2h_bytes_per_step": d2h_per_step, "ms_per_step": e2e_ms,
                     "note": "every rank uploads its activations; rank 0 reads the whole result (all ranks' shards) back"},
@@ -646,6 +679,11 @@ def run_case(args):
         pk, sc = ops.encode(w, 32)
         x = ops.generate(m * k, 7, 1.0, torch.bfloat16, dev).view(m, k)
         fn = lambda: ops.linear(x, pk, sc, None, n, k, 32, force="gemm")
+        info["flops_per_launch"] = 2.0 * m * n * k
+    elif args.case == "gemm_dx":
+        pk, sc = ops.encode(w, 32)
+        gy = ops.generate(m * n, 7, 1.0, torch.bfloat16, dev).view(m, n)
+        fn = lambda: ops.linear_dx(gy, pk, sc, n, k, 32)
         info["flops_per_launch"] = 2.0 * m * n * k
     elif args.case == "encode":
         pk = torch.empty(n * k * 3 // 16, dtype=torch.uint8, device=dev)
@@ -723,6 +761,22 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
             out["prefill"].append({"K": k, "N": n, "M": m, "ms": ms, "TFLOPs": tf, "frac_bf16_peak": tf / tf_peak,
                                    "calls_per_timing": len(mats),
                                    "single_cold_call_ms": ms_single, "single_cold_call_TFLOPs": 2.0 * m * n * k / (ms_single * 1e-3) / 1e12})
+
+        # Backward with respect to the input, dX = dY . W straight from the packed codes, same shapes and token count
+        out["backward_dx"] = []
+        for si, (k, n) in enumerate(SHAPES):
+            gy = ops.generate(m * n, 199 + si, 1.0, torch.bfloat16, dev).view(m, n)
+            mats = packed_store[si][:8]
+
+            def stream_of_dx():
+                for pk, sc in mats:
+                    ops.linear_dx(gy, pk, sc, n, k, 32)
+
+            ms = timed(stream_of_dx, 5) / len(mats)
+            ops.gemm_status(dev)
+            tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+            out["backward_dx"].append({"K": k, "N": n, "M": m, "ms": ms, "TFLOPs": tf, "frac_bf16_peak": tf / tf_peak,
+                                       "calls_per_timing": len(mats)})
 
         k, n = 8192, 28672
         w = ops.generate(n * k, 5, 0.02, torch.float16, dev).view(n, k)

@@ -13,6 +13,9 @@ from .streaming_e8 import (_copy_row_block_into_layer, _pack_row_block, _validat
 from .hardware import (dispatch_tilelang_e8_gemm, fused_ternary_e8_gemm_bwd_dx, fused_ternary_e8_gemm_fwd,     # noqa: F401
                        install_into_reference)
 from .sharding import ColumnShardedLinear, shard_rows                        # noqa: F401
+from . import torch_ops                                                      # noqa: F401
+
+torch_ops.register()       # torch.ops.ojasx_math_native.fused_ternary_e8_gemm_fwd / _bwd_dx (CUDA, fake, autograd)
 
 __all__ = [
     "E8LatticeLinear", "TernaryE8LatticePacker", "_FusedE8GEMMFunction", "pack_model_e8", "fwht_block32",

@@ -64,8 +64,11 @@ def fused_ternary_e8_gemm_bwd_dx(grad_y: torch.Tensor, packed_weight: torch.Tens
 
 
 def install_into_reference() -> bool:
-    """Rebinds the reference's seam to this backend when the reference package is importable.
-    Returns True when the patch was applied."""
+    """Rebinds the reference's kernel seam (the module-level ``dispatch_tilelang_e8_gemm`` that
+    ``_FusedE8GEMMFunction.forward`` calls first, ``ojasx2/math/lattice.py:51-55,583-589``) to this backend when the
+    reference package is importable.  Returns True when the patch was applied.  The reference's second seam, the
+    native module's ``fused_ternary_e8_gemm_fwd`` / ``_bwd_dx`` operators, is served by ``torch_ops.register()``:
+    ``torch.ops.ojasx_math_native.*`` with the reference's schemas and a CUDA implementation."""
     try:
         import ojasx2.math.lattice as ref_lattice   # type: ignore
     except Exception:

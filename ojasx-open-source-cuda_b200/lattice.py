@@ -126,15 +126,28 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
         ctx.use_hadamard = use_hadamard
         ctx.group_size = group_size
         x_2d = x_rot.reshape(-1, in_features)
-        y_2d = ops.linear(x_2d, packed_weight, block_scales, bias, out_features, in_features, group_size)
+        eff = ops.effective_group(group_size)
+        if torch.compiler.is_compiling() and in_features % eff == 0:
+            # under torch.compile the kernels are reached through the registered operator, which the compiler
+            # keeps as one opaque node (row-major 2-D operands, as the reference's native module takes them)
+            y_2d = torch.ops.ojasx_math_native.fused_ternary_e8_gemm_fwd(
+                x_2d, packed_weight.view(out_features, -1), block_scales.view(out_features, -1), bias, eff)
+        else:
+            y_2d = ops.linear(x_2d, packed_weight, block_scales, bias, out_features, in_features, group_size)
         return y_2d.reshape(*x_rot.shape[:-1], out_features)
 
     @staticmethod
     def backward(ctx, grad_y):
         packed_weight, block_scales = ctx.saved_tensors
         gy_2d = grad_y.reshape(-1, ctx.out_features).contiguous()
-        grad_x = ops.linear_dx(gy_2d.to(ctx.x_dtype), packed_weight, block_scales, ctx.out_features, ctx.in_features,
-                               ctx.group_size).reshape(ctx.x_shape)
+        eff = ops.effective_group(ctx.group_size)
+        if torch.compiler.is_compiling() and ctx.in_features % eff == 0:
+            grad_x = torch.ops.ojasx_math_native.fused_ternary_e8_gemm_bwd_dx(
+                gy_2d.to(ctx.x_dtype), packed_weight.view(ctx.out_features, -1), block_scales.view(ctx.out_features, -1),
+                ctx.in_features, eff).reshape(ctx.x_shape)
+        else:
+            grad_x = ops.linear_dx(gy_2d.to(ctx.x_dtype), packed_weight, block_scales, ctx.out_features, ctx.in_features,
+                                   ctx.group_size).reshape(ctx.x_shape)
         if ctx.use_hadamard and ctx.in_features % 32 == 0:
             grad_x = fwht_block32(grad_x)
         grad_bias = gy_2d.sum(dim=0) if ctx.has_bias else None

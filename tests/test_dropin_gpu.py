@@ -200,6 +200,47 @@ def test_autograd_backward_uses_the_packed_weights(P):
     assert layer.bias.grad is not None and float((layer.bias.grad.float() - gy.float().sum((0, 1))).abs().max()) < 0.1
 
 
+def test_registered_operators_and_compile_without_graph_breaks(P):
+    """torch.ops.ojasx_math_native.fused_ternary_e8_gemm_fwd / _bwd_dx with the reference's schema strings
+    (ojasx_math_bindings.cpp:592-595): callable on CUDA tensors, shape-inferable on meta tensors, and a packed layer
+    with LoRA compiles as ONE graph (fullgraph=True) and gives the eager result, forward and backward."""
+    dev = torch.device(DEV)
+    ns = torch.ops.ojasx_math_native
+    fwd = ns.fused_ternary_e8_gemm_fwd.default
+    assert str(fwd._schema) == ("ojasx_math_native::fused_ternary_e8_gemm_fwd(Tensor x, Tensor packed_weight, Tensor block_scales, "
+                                "Tensor? bias=None, int group_size=32) -> Tensor")
+    assert str(ns.fused_ternary_e8_gemm_bwd_dx.default._schema) == (
+        "ojasx_math_native::fused_ternary_e8_gemm_bwd_dx(Tensor grad_y, Tensor packed_weight, Tensor block_scales, "
+        "int in_features, int group_size=32) -> Tensor")
+    n, k, m = 192, 512, 6
+    lin = torch.nn.Linear(k, n, bias=True).to(dev)
+    layer = P.E8LatticeLinear.from_linear(lin, rank=4, bitrate=1.5, group_size=32)
+    with torch.no_grad():
+        layer.lora_B.normal_(0, 0.02)
+    pk2, sc2 = layer.packed_weight.view(n, -1), layer.block_scales.view(n, -1)
+    x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+    y_op = ns.fused_ternary_e8_gemm_fwd(x, pk2, sc2, layer.bias.detach().bfloat16(), 32)
+    assert torch.equal(y_op, P.ops.linear(x, layer.packed_weight, layer.block_scales, layer.bias.detach(), n, k, 32))
+    meta = ns.fused_ternary_e8_gemm_fwd(x.to("meta"), pk2.to("meta"), sc2.to("meta"), None, 32)
+    assert meta.device.type == "meta" and tuple(meta.shape) == (m, n) and meta.dtype == torch.bfloat16
+    gmeta = ns.fused_ternary_e8_gemm_bwd_dx(y_op.to("meta"), pk2.to("meta"), sc2.to("meta"), k, 32)
+    assert tuple(gmeta.shape) == (m, k)
+
+    compiled = torch.compile(layer, fullgraph=True, backend="aot_eager")
+    xe = x.clone().requires_grad_(True)
+    xc = x.clone().requires_grad_(True)
+    ye = layer(xe)
+    yc = compiled(xc)
+    assert torch.equal(ye, yc)
+    g = torch.randn_like(ye)
+    ye.backward(g)
+    ge_b = layer.lora_B.grad.clone()
+    layer.zero_grad()
+    yc.backward(g)
+    assert torch.allclose(xe.grad.float(), xc.grad.float(), rtol=2e-2, atol=2e-2)
+    assert torch.allclose(ge_b.float(), layer.lora_B.grad.float(), rtol=2e-2, atol=2e-2)
+
+
 def test_activation_outliers_nan_and_inf(P, oracle):
     """One huge activation per 256-wide slice must not wipe out its neighbours, and non-finite activations
     must show up in the outputs the way a dense product shows them (rows of the batch they belong to)."""

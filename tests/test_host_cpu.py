@@ -135,6 +135,24 @@ def test_fwht_equals_reference_output_bit_for_bit(P, golden):
         assert np.array_equal(y.float().numpy().view(np.uint32), arrays[f"fwht/{tag}/output"].view(np.uint32)), tag
 
 
+def test_native_operator_schemas_and_shape_inference(P):
+    """The two operators of the reference's native module (ojasx_math_bindings.cpp:592-595) exist under the same
+    namespace with the same schema strings, and infer shapes without touching data."""
+    ns = torch.ops.ojasx_math_native
+    assert "Tensor? bias=None, int group_size=32" in str(ns.fused_ternary_e8_gemm_fwd.default._schema)
+    assert "int in_features, int group_size=32" in str(ns.fused_ternary_e8_gemm_bwd_dx.default._schema)
+    x = torch.empty(5, 256, device="meta", dtype=torch.float16)
+    pk = torch.empty(24, 48, device="meta", dtype=torch.uint8)
+    sc = torch.empty(24, 8, device="meta", dtype=torch.float16)
+    y = ns.fused_ternary_e8_gemm_fwd(x, pk, sc, None, 32)
+    assert tuple(y.shape) == (5, 24) and y.dtype == torch.float16
+    dx = ns.fused_ternary_e8_gemm_bwd_dx(y, pk, sc, 256, 32)
+    assert tuple(dx.shape) == (5, 256)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        ns.fused_ternary_e8_gemm_fwd(torch.zeros(5, 256), torch.zeros(24, 48, dtype=torch.uint8),
+                                     torch.ones(24, 8, dtype=torch.float16), None, 32)     # no CPU implementation
+
+
 def test_shard_rows_cover_everything(P):
     from importlib import import_module
     sh = import_module(P.__name__ + ".sharding")
