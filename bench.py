@@ -50,6 +50,10 @@ L70 = [(8192, 8192), (1024, 8192), (1024, 8192), (8192, 8192), (28672, 8192), (2
 L8 = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096), (4096, 14336)]
 
 
+FUSED_TEXT = ("output-column shards; the kernels store their shard into every rank's output window over NVLink; "
+              "one 4-byte all-reduce per pass as the fence (the windows are compared with an all-gather once, outside the timed region)")
+
+
 def sweep_config(rotation, launches_per_step, parallelism, packed_gb):
     return {"workload": WORKLOAD, "rotation": rotation,
             "l2": "inputs larger than L2: %.2f GB of packed weights per pass, a matrix is revisited only after the whole sweep" % packed_gb,
@@ -305,7 +309,7 @@ def run_reference_arm(args):
     line = {"metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * sum(secs) / len(secs), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "impl": "reference",
-            "config": sweep_config(args.rotation, 12, "host CPU", packed_gb),
+            "config": sweep_config(args.rotation, 15, "single GPU" if args.gpus == 1 else FUSED_TEXT, packed_gb),
             "note": "a step of this arm is the bounded sample named in cpu_baseline.sample, not the whole pass; GB/s on packed bytes is size-independent",
             "cpu_baseline": cb,
             "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -605,8 +609,7 @@ def main():
         if world == 1:
             parallelism = "single GPU"
         elif fused:
-            parallelism = ("output-column shards; the kernels store their shard into every rank's output window over NVLink; "
-                           "one 4-byte all-reduce per pass as the fence (the windows are compared with an all-gather once, outside the timed region)")
+            parallelism = FUSED_TEXT
         elif use_nccl:
             parallelism = "output-column shards + one NCCL all-gather per launch (12 per pass), overlapped with the next launch"
         else:
