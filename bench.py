@@ -963,13 +963,32 @@ def run_encoder70b(torch, ops, sharding, dist, dev, world, rank, hbm_peak, barri
                 ops.generate(cnt, 70000 + 10 * layer + j, 0.02, torch.float16, dev, start=n0 * k, out=w[off: off + cnt])
                 views.append((w[off: off + cnt].view(n1 - n0, k), pk[off * 3 // 16: (off + cnt) * 3 // 16], sc[off // 32: (off + cnt) // 32]))
                 off += cnt
+        # the chunk's 7 x chunk launches replayed from a CUDA graph (no per-launch host work), eager if capture fails
+        def encode_all():
+            for wv, pv, sv in views:
+                ops.encode(wv, 32, out=(pv, sv))
+        run, graph = encode_all, None
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                encode_all()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                encode_all()
+            run = graph.replay
+        except Exception as exc:                                  # noqa: BLE001
+            print(f"[bench] encoder graph capture unavailable: {exc}", file=sys.stderr)
+            torch.cuda.synchronize()
         barrier()
         e0.record()
-        for wv, pv, sv in views:
-            ops.encode(wv, 32, out=(pv, sv))
+        run()
         e1.record()
         barrier()
         total_ms += e0.elapsed_time(e1)
+        del graph
         if c0 == 0 and rank == 0:
             check = _encoder_hash_check(torch, views[:7])
     if world > 1:

@@ -165,7 +165,9 @@ __device__ __forceinline__ float load_any(const void* p, int dt, int64_t i) {
     return static_cast<const float*>(p)[i];
 }
 
-// Sums the K-chunk partials of every problem that has them (fixed order), adds bias, casts.
+// Sums the K-chunk partials of every problem that has them (fixed order), adds bias, casts, stores - to this rank's
+// buffer and to every peer's window.  16-bit outputs whose rows come in multiples of eight are handled eight rows
+// (one 16-byte vector) per thread.
 template <bool kBf16>
 __global__ void __launch_bounds__(256, 3) gemv_reduce_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev,
                                                            const __grid_constant__ ojx_e8t_gemv_problem single,
@@ -176,13 +178,49 @@ __global__ void __launch_bounds__(256, 3) gemv_reduce_kernel(const ojx_e8t_gemv_
         if (P.partial == nullptr) continue;
         const int kc = gemv_kchunks(P.K);
         const int64_t total = (int64_t)M * P.N;
+        const int64_t ld = P.ldy > 0 ? P.ldy : P.N;
+        const bool vec = y_dtype != OJX_F32 && (P.N & 7) == 0 && (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(P.y) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(P.partial) & 31) == 0;
+        if (vec) {
+            const int64_t per_col = P.N / 8;
+            for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < (int64_t)M * per_col;
+                 v += (int64_t)gridDim.x * blockDim.x) {
+                const int64_t col = v / per_col, row = (v - col * per_col) * 8;
+                float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int c = 0; c < kc; ++c) {
+                    const float4* src = reinterpret_cast<const float4*>(P.partial + (int64_t)c * total + col * P.N + row);
+                    const float4 a = __ldcg(src), b = __ldcg(src + 1);
+                    s8[0] += a.x; s8[1] += a.y; s8[2] += a.z; s8[3] += a.w;
+                    s8[4] += b.x; s8[5] += b.y; s8[6] += b.z; s8[7] += b.w;
+                }
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float lo = s8[2 * i], hi = s8[2 * i + 1];
+                    if (P.bias != nullptr) { lo += load_act<kBf16>(P.bias, row + 2 * i); hi += load_act<kBf16>(P.bias, row + 2 * i + 1); }
+                    if (y_dtype == OJX_BF16) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+                    } else {
+                        const __half2 h = __floats2half2_rn(lo, hi);
+                        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                }
+                const uint4 val = make_uint4(w[0], w[1], w[2], w[3]);
+                uint8_t* dst = static_cast<uint8_t*>(P.y) + (col * ld + row) * 2;
+#pragma unroll 1
+                for (int r = 0; r < peers.world; ++r)              // delta is 0 for this rank itself
+                    *reinterpret_cast<uint4*>(dst + peers.delta[r]) = val;
+            }
+            continue;
+        }
         for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
              i += (int64_t)gridDim.x * blockDim.x) {
             float s = 0.f;
             for (int c = 0; c < kc; ++c) s += P.partial[(int64_t)c * total + i];
             const int64_t col = i / P.N, row = i - col * P.N;
             if (P.bias != nullptr) s += load_act<kBf16>(P.bias, row);
-            const int64_t at = col * (P.ldy > 0 ? P.ldy : P.N) + row;
+            const int64_t at = col * ld + row;
             store_any(P.y, y_dtype, at, s);
 #pragma unroll 1
             for (int r = 0; r < peers.world; ++r)                  // the other ranks' windows (nothing when world == 1)

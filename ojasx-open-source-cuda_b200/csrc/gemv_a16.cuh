@@ -53,7 +53,8 @@ template <int NB> struct A16Cfg {
     static constexpr int kRed = 2;                                        // reduction buffers (written at item n, n + 2, ...)
     static constexpr int kLutBytes = ((kNumPoints * 16 + 1023) / 1024) * 1024;   // two interleaved copies of 8-byte entries
     static constexpr int kRedFloats = kGemvWarps * 256 * NB;              // per buffer: 16 warps x 32 rows x 8 NB columns
-    static constexpr size_t kSmem = (size_t)kLutBytes + (size_t)kStages * kA16StageBytes + (size_t)kRed * kRedFloats * sizeof(float) + 256;
+    static constexpr int kOutStageBytes = 16 * kA16Rows * 2;              // an item's outputs as 16-bit values, [column][row]
+    static constexpr size_t kSmem = (size_t)kLutBytes + (size_t)kStages * kA16StageBytes + (size_t)kRed * kRedFloats * sizeof(float) + 256 + kOutStageBytes;
 };
 
 __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
@@ -118,6 +119,7 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     uint8_t* tail = smem + Cfg::kLutBytes + S * kA16StageBytes + Cfg::kRed * Cfg::kRedFloats * sizeof(float);
     const uint32_t bar_full = smem_u32(tail), bar_lut = bar_full + 8 * S;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 64);
+    uint16_t* ost = reinterpret_cast<uint16_t*>(tail + 256);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -348,26 +350,52 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
         }
         __syncthreads();           // the stage is free again and every warp's partial sums are visible
 
-        // ---- sum over the warps in warp order; thread tid owns element tid of the 256 NB fragment values ----
-        if (tid < 256 * NB && !dead) {
-            const float* rb = red + (size_t)(n & 1) * Cfg::kRedFloats + tid;
+        // ---- sum over the warps in warp order; thread tid owns element tid of the 256 NB fragment values.
+        // 16-bit outputs of a full 32-row tile are first collected in shared memory ([column][row]) and then written as
+        // 16-byte vectors - to this rank's buffer and, in a column-sharded launch, to every peer's window - instead of one
+        // 2-byte store per value and target. ----
+        if (tid < 256 * NB) {
             const int comp = tid & 3, lp = (tid >> 2) & 31, nb = (tid >> 7) % NB, tl = tid / (128 * NB);
-            const int row = tile * kA16Rows + tl * 16 + (lp >> 2) + ((comp >> 1) << 3);
+            const int rin = tl * 16 + (lp >> 2) + ((comp >> 1) << 3);        // row inside the item
+            const int row = tile * kA16Rows + rin;
             const int col = nb * 8 + ((lp & 3) << 1) + (comp & 1);
-            const ojx_e8t_gemv_problem& P = probs[prob];
-            const int rN = P.N;
-            if (row < rN && col < M) {                               // activation rows beyond M hold zeros: nothing to add up
-                float sum = 0.f;
+            bool vec = false;
+            int64_t ld = 0;
+            void* ybase = nullptr;
+            if (!dead) {
+                const ojx_e8t_gemv_problem& P = probs[prob];
+                const int rN = P.N;
+                ld = P.ldy > 0 ? P.ldy : rN;
+                ybase = P.y;
+                vec = P.partial == nullptr && y_dtype != OJX_F32 && tile * kA16Rows + kA16Rows <= rN && (ld & 7) == 0 &&
+                      (reinterpret_cast<uintptr_t>(P.y) & 15) == 0;
+                if (row < rN && col < M) {                           // activation rows beyond M hold zeros: nothing to add up
+                    const float* rb = red + (size_t)(n & 1) * Cfg::kRedFloats + tid;
+                    float sum = 0.f;
 #pragma unroll
-                for (int w = 0; w < kGemvWarps; ++w)
-                    if (w < act) sum += rb[w * 256 * NB];
-                if (P.partial != nullptr) P.partial[((int64_t)chunk * M + col) * rN + row] = sum;
-                else {
-                    if (P.bias != nullptr) sum += load_any(P.bias, kXF16 ? OJX_F16 : OJX_BF16, row);
-                    const int64_t at = (int64_t)col * (P.ldy > 0 ? P.ldy : rN) + row;
-                    store_any(P.y, y_dtype, at, sum);
-                    if (peers.world > 1) store_peers(peers, P.y, y_dtype, at, sum);
+                    for (int w = 0; w < kGemvWarps; ++w)
+                        if (w < act) sum += rb[w * 256 * NB];
+                    if (P.partial != nullptr) P.partial[((int64_t)chunk * M + col) * rN + row] = sum;
+                    else {
+                        if (P.bias != nullptr) sum += load_any(P.bias, kXF16 ? OJX_F16 : OJX_BF16, row);
+                        if (vec) {
+                            ost[col * kA16Rows + rin] = y_dtype == OJX_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum))
+                                                                            : __half_as_ushort(__float2half_rn(sum));
+                        } else {
+                            const int64_t at = (int64_t)col * ld + row;
+                            store_any(P.y, y_dtype, at, sum);
+                            if (peers.world > 1) store_peers(peers, P.y, y_dtype, at, sum);
+                        }
+                    }
                 }
+            }
+            // every summing thread, whatever it did above, so that the count of the named barrier is always met
+            asm volatile("bar.sync 1, %0;" ::"r"(256 * NB) : "memory");
+            if (vec && tid < M * 4 * peers.world) {
+                const int target = tid / (M * 4), v = tid - target * (M * 4), vcol = v >> 2, q = v & 3;
+                const uint4 val = *reinterpret_cast<const uint4*>(ost + vcol * kA16Rows + q * 8);
+                uint8_t* dst = static_cast<uint8_t*>(ybase) + peers.delta[target] + ((int64_t)vcol * ld + tile * kA16Rows + q * 8) * 2;
+                *reinterpret_cast<uint4*>(dst) = val;
             }
         }
     }
