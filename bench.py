@@ -786,6 +786,18 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
         pk = torch.empty(n * k * 3 // 16, dtype=torch.uint8, device=dev)
         sc = torch.empty(n * k // 32, dtype=torch.float16, device=dev)
         ops.encode(w, 32, out=(pk, sc))
+        # encoder on one matrix, plain and with the 32-point rotation fused into its registers; for comparison the
+        # rotation as a kernel of its own followed by the plain encoder (what two separate operators cost)
+        enc = {"rows": n, "cols": k, "dtype": "f16", "bytes_per_weight": 2.25}
+        for name, fn in (("plain", lambda: ops.encode(w, 32, out=(pk, sc))),
+                         ("rotation_fused", lambda: ops.encode(w, 32, out=(pk, sc), hadamard=True)),
+                         ("rotation_then_encode", lambda: ops.encode(ops.fwht32(w), 32, out=(pk, sc)))):
+            ms = timed(fn, 3)
+            gbs = n * k * 2.25 / (ms * 1e-3) / 1e9
+            enc[name] = {"ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak}
+        out["encoder_one_matrix"] = enc
+        out["ingest"] = run_ingest(torch, dev)
+        ops.encode(w, 32, out=(pk, sc))
         # decoder (unpack): packed codes + scales -> dense fp16 weights, 0.25 B read + 2 B written per weight
         ms = timed(lambda: ops.decode(pk, sc, (n, k), torch.float16, out=w), 3)
         gbs = n * k * 2.25 / (ms * 1e-3) / 1e9
@@ -797,6 +809,36 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
     torch.cuda.empty_cache()
     out["encoder70b"] = run_encoder70b(torch, ops, sharding, dist, dev, world, rank, hbm_peak, barrier)
     return out
+
+
+def run_ingest(torch, dev, rows=14336, cols=4096, row_block=1024):
+    """Checkpoint ingestion of one bf16 matrix: safetensors file -> row blocks -> pinned slots -> encoder -> a layer's
+    packed buffers (the library's _stream_safetensor_weight), host wall clock, file already in the page cache."""
+    try:
+        import tempfile
+        from safetensors import safe_open
+        from safetensors.torch import save_file
+    except ImportError as exc:
+        return {"unavailable": str(exc)}
+    pkg = importlib.import_module("ojasx-open-source-cuda_b200")
+    w = (torch.randn(rows, cols, generator=torch.Generator().manual_seed(3)) * 0.02).to(torch.bfloat16)
+    layer = pkg.E8LatticeLinear(cols, rows, bias=False, group_size=32, bitrate=1.5, device=dev)
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "w.safetensors")
+        save_file({"w": w}, path)
+        best = None
+        with safe_open(path, framework="pt", device="cpu") as handle:
+            for _ in range(3):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                pkg._stream_safetensor_weight(handle, "w", layer, row_block, False)
+                torch.cuda.synchronize()
+                dt = time.perf_counter() - t0
+                best = dt if best is None else min(best, dt)
+    src = rows * cols * 2
+    return {"rows": rows, "cols": cols, "dtype": "bf16", "row_block": row_block, "ms": best * 1e3,
+            "source_GBps": src / best / 1e9,
+            "what": "host wall clock of the best of 3 passes; bounded by reading the file and the host->device link, not by the encoder"}
 
 
 def run_stack(torch, ops, sharding, dist, dev, world, rank, timed, hbm_peak, layers=32):

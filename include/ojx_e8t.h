@@ -20,6 +20,7 @@
  *                         (and its row-block caller)             ojasx2/streaming_e8.py:112-159
  *   ojx_e8t_decode        TernaryE8LatticePacker.unpack          ojasx2/math/lattice.py:386-419
  *                         workspace reconstruction               ojasx2/math/lattice.py:62-84,412-416
+ *   ojx_e8t_fwht32        fwht_block32                           ojasx2/math/lattice.py:91-102
  *   ojx_e8t_gemv/_gemm    _FusedE8GEMMFunction.forward           ojasx2/math/lattice.py:551-640
  *                         dispatch_tilelang_e8_gemm              ojasx2/tilelang_kernels.py:370-419
  *                         _build_tl_ternary_e8_1_5bit_gemm       ojasx2/tilelang_kernels.py:277-363
@@ -86,6 +87,26 @@ void    ojx_e8t_set_wait_limit(uint32_t polls);
  */
 int32_t ojx_e8t_encode(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
                        uint8_t* packed_out, uint16_t* scales_out, void* stream);
+
+/*
+ * Encoder with options.  flags = 0 is ojx_e8t_encode.  OJX_ENCODE_HADAMARD rotates every block of 32
+ * consecutive weights of a row by the normalised Walsh-Hadamard transform in registers before encoding it, in
+ * w's own arithmetic - the bytes equal pack(fwht_block32(w)), which is what the reference's _pack_row_block
+ * (ojasx2/streaming_e8.py:112-125) and E8LatticeLinear.from_linear (ojasx2/math/lattice.py:783-812) compute with
+ * use_hadamard=True, without the rotated copy of w in memory.  Needs group == 32 and cols % 32 == 0
+ * (OJX_ERR_SHAPE otherwise); unknown flag bits return OJX_ERR_UNSUPPORTED.
+ */
+#define OJX_ENCODE_HADAMARD 1u
+int32_t ojx_e8t_encode_ex(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group, uint32_t flags,
+                          uint8_t* packed_out, uint16_t* scales_out, void* stream);
+
+/*
+ * 32-point normalised Walsh-Hadamard transform of every block of 32 consecutive elements.  Replaces
+ * fwht_block32 (ojasx2/math/lattice.py:91-102) bit for bit: butterflies and the final scaling are rounded to the
+ * element type exactly where the reference's tensor operations round.  count % 32 == 0; x and out 16-byte
+ * aligned; out may be x.
+ */
+int32_t ojx_e8t_fwht32(const void* x, int32_t dtype, int64_t count, void* out, void* stream);
 
 /*
  * Decoder.  Replaces TernaryE8LatticePacker.unpack (ojasx2/math/lattice.py:386-419).

@@ -6,6 +6,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "fwht.cuh"
 
 namespace ojx {
 
@@ -79,7 +80,9 @@ __device__ __forceinline__ uint32_t encode_block8_rcp(const float* x, float scal
     return block8_rank(b);
 }
 
-template <typename T, int GROUP>
+// kHad: the group is first rotated by the 32-point Walsh-Hadamard transform in T's arithmetic (what
+// _pack_row_block / E8LatticeLinear.from_linear do with use_hadamard, ojasx2/streaming_e8.py:112-125), in registers.
+template <typename T, int GROUP, bool kHad = false>
 __global__ void __launch_bounds__(128) encode_kernel(const T* __restrict__ w, int64_t total, int group_rt,
                                                       float sqrt_group, uint8_t* __restrict__ packed,
                                                       uint16_t* __restrict__ scales, int64_t ngroups) {
@@ -110,6 +113,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const T* __restrict__ w, in
 #pragma unroll
                 for (int i = 0; i < GROUP; ++i) xr[i] = (base + i < total) ? to_f32<T>(w[base + i]) : 0.f;
             }
+            if constexpr (kHad && GROUP == 32) fwht32_values<T>(xr);
 #pragma unroll
             for (int d = 0; d < GROUP; d += 8)
 #pragma unroll
@@ -178,8 +182,8 @@ __global__ void __launch_bounds__(128) encode_kernel(const T* __restrict__ w, in
 }
 
 template <typename T>
-static int32_t encode_typed(const void* w, int64_t total, int group, uint8_t* packed, uint16_t* scales,
-                            cudaStream_t s) {
+static int32_t encode_typed(const void* w, int64_t total, int group, bool hadamard, uint8_t* packed,
+                            uint16_t* scales, cudaStream_t s) {
     const int64_t ngroups = (total + group - 1) / group;
     const float sg = (float)sqrt((double)group);
     const int threads = 128;
@@ -187,24 +191,29 @@ static int32_t encode_typed(const void* w, int64_t total, int group, uint8_t* pa
     if (blocks > 148 * 64) blocks = 148 * 64;
     if (blocks < 1) blocks = 1;
     const T* wp = static_cast<const T*>(w);
-    if (group == 32)
+    if (hadamard)
+        encode_kernel<T, 32, true><<<(unsigned)blocks, threads, 0, s>>>(wp, total, group, sg, packed, scales, ngroups);
+    else if (group == 32)
         encode_kernel<T, 32><<<(unsigned)blocks, threads, 0, s>>>(wp, total, group, sg, packed, scales, ngroups);
     else
         encode_kernel<T, 0><<<(unsigned)blocks, threads, 0, s>>>(wp, total, group, sg, packed, scales, ngroups);
     return launch_status();
 }
 
-int32_t encode_impl(const void* w, int w_dtype, int64_t rows, int64_t cols, int group,
+int32_t encode_impl(const void* w, int w_dtype, int64_t rows, int64_t cols, int group, uint32_t flags,
                     uint8_t* packed, uint16_t* scales, cudaStream_t s) {
     OJX_RETURN_IF(!w || !packed || !scales, OJX_ERR_NULL);
     OJX_RETURN_IF(rows <= 0 || cols <= 0, OJX_ERR_SHAPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
     group = effective_group(group);
+    OJX_RETURN_IF((flags & ~(uint32_t)OJX_ENCODE_HADAMARD) != 0, OJX_ERR_UNSUPPORTED);
+    const bool had = (flags & OJX_ENCODE_HADAMARD) != 0;
+    OJX_RETURN_IF(had && (group != 32 || cols % 32 != 0), OJX_ERR_SHAPE);
     const int64_t total = rows * cols;
     switch (w_dtype) {
-        case OJX_F32: return encode_typed<float>(w, total, group, packed, scales, s);
-        case OJX_F16: return encode_typed<__half>(w, total, group, packed, scales, s);
-        case OJX_BF16: return encode_typed<__nv_bfloat16>(w, total, group, packed, scales, s);
+        case OJX_F32: return encode_typed<float>(w, total, group, had, packed, scales, s);
+        case OJX_F16: return encode_typed<__half>(w, total, group, had, packed, scales, s);
+        case OJX_BF16: return encode_typed<__nv_bfloat16>(w, total, group, had, packed, scales, s);
         default: return OJX_ERR_DTYPE;
     }
 }

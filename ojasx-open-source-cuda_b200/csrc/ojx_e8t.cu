@@ -100,7 +100,16 @@ void ojx_e8t_set_wait_limit(uint32_t polls) { ojx::wait_limit_override() = polls
 
 int32_t ojx_e8t_encode(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
                        uint8_t* packed_out, uint16_t* scales_out, void* stream) {
-    return ojx::encode_impl(w, w_dtype, rows, cols, group, packed_out, scales_out, (cudaStream_t)stream);
+    return ojx::encode_impl(w, w_dtype, rows, cols, group, 0u, packed_out, scales_out, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_encode_ex(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group, uint32_t flags,
+                          uint8_t* packed_out, uint16_t* scales_out, void* stream) {
+    return ojx::encode_impl(w, w_dtype, rows, cols, group, flags, packed_out, scales_out, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_fwht32(const void* x, int32_t dtype, int64_t count, void* out, void* stream) {
+    return ojx::fwht32_impl(x, dtype, count, out, (cudaStream_t)stream);
 }
 
 int32_t ojx_e8t_decode(const uint8_t* packed, const uint16_t* scales, int64_t rows, int64_t cols,

@@ -36,14 +36,30 @@ def _check_bitrate(bitrate: float) -> None:
             f"bitrate={bitrate!r}: the B200 backend implements the 1.5-bit ternary-E8 path only")
 
 
+class _Fwht32(torch.autograd.Function):
+    """The transform is symmetric and orthogonal, so its adjoint is itself."""
+
+    @staticmethod
+    def forward(ctx, x):
+        return ops.fwht32(x)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return ops.fwht32(grad)
+
+
 def fwht_block32(x: torch.Tensor) -> torch.Tensor:
     """Normalised 32-point Walsh-Hadamard transform over consecutive blocks of the last dimension.
 
-    Same butterfly order and final scaling as the reference (``lattice.py:91-102``), so results are
-    bit-identical; tensors whose last dimension is not a multiple of 32 are returned unchanged.
+    Same butterfly order, roundings and final scaling as the reference (``lattice.py:91-102``), so results are
+    bit-identical; tensors whose last dimension is not a multiple of 32 are returned unchanged.  CUDA tensors
+    of the three float types take one kernel (``ops.fwht32``); anything else runs the tensor expression below.
     """
     if x.shape[-1] == 0 or x.shape[-1] % 32 != 0:
         return x
+    if x.is_cuda and x.dtype in (torch.float32, torch.float16, torch.bfloat16) and x.numel() > 0 \
+            and not torch.compiler.is_compiling():
+        return _Fwht32.apply(x) if (x.requires_grad and torch.is_grad_enabled()) else ops.fwht32(x)
     h = x.reshape(-1, 32)
     span = 1
     while span < 32:
@@ -198,8 +214,7 @@ class E8LatticeLinear(nn.Module):
                 lora_alpha=lora_alpha, group_size=eff_gs, bitrate=bitrate, use_hadamard=use_hadamard,
                 device=linear.weight.device, dtype=linear.weight.dtype)
         with torch.no_grad():
-            w_to_pack = fwht_block32(linear.weight) if m.use_hadamard else linear.weight
-            ops.encode(w_to_pack, m.group_size, out=(m.packed_weight, m.block_scales))
+            ops.encode(linear.weight, m.group_size, out=(m.packed_weight, m.block_scales), hadamard=m.use_hadamard)
             if linear.bias is not None:
                 m.bias.copy_(linear.bias)
         return m

@@ -73,10 +73,29 @@ def packed_sizes(rows: int, cols: int, group_size: int) -> Tuple[int, int]:
     return padded * 3 // 16, padded // g
 
 
-def encode(w: torch.Tensor, group_size: int = 32, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
-           ) -> Tuple[torch.Tensor, torch.Tensor]:
+def fwht32(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Normalised 32-point Walsh-Hadamard transform of consecutive blocks of the last dimension, one kernel,
+    bit-identical to the reference's ``fwht_block32`` (``ojasx2/math/lattice.py:91-102``)."""
+    dev = _require_cuda(x)
+    if x.shape[-1] % 32 != 0 or x.numel() == 0:
+        raise ValueError("the last dimension must be a positive multiple of 32")
+    xc = x.detach().contiguous()
+    if xc.data_ptr() % 16:
+        xc = xc.clone()
+    res = torch.empty_like(xc) if out is None else out
+    if res.shape != xc.shape or res.dtype != xc.dtype or not res.is_contiguous() or res.data_ptr() % 16:
+        raise ValueError("output buffer has the wrong shape, dtype, layout or alignment")
+    with torch.cuda.device(dev):
+        st = _cabi.lib().ojx_e8t_fwht32(xc.data_ptr(), _dtype_code(xc.dtype), xc.numel(), res.data_ptr(), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_fwht32")
+    return res
+
+
+def encode(w: torch.Tensor, group_size: int = 32, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+           hadamard: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """``w`` [rows, cols] -> (packed uint8[P*3/16], scales fp16[P/g]); bit-exact with the
-    reference's ``TernaryE8LatticePacker.pack``."""
+    reference's ``TernaryE8LatticePacker.pack``.  ``hadamard=True`` encodes ``fwht_block32(w)`` without
+    materialising it (rotation fused into the encoder when the group is 32, one extra kernel otherwise)."""
     if w.dim() != 2:
         raise ValueError(f"expected a 2-D weight, got shape {tuple(w.shape)}")
     dev = _require_cuda(w)
@@ -84,6 +103,12 @@ def encode(w: torch.Tensor, group_size: int = 32, out: Optional[Tuple[torch.Tens
     if rows == 0 or cols == 0:
         raise ValueError("empty weight")
     wc = w.detach().contiguous()
+    flags = 0
+    if hadamard and cols % 32 == 0:
+        if effective_group(group_size) == 32:
+            flags = _cabi.OJX_ENCODE_HADAMARD
+        else:
+            wc = fwht32(wc)
     nbytes, nscales = packed_sizes(rows, cols, group_size)
     if out is None:
         packed = torch.empty(nbytes, dtype=torch.uint8, device=dev)
@@ -94,9 +119,9 @@ def encode(w: torch.Tensor, group_size: int = 32, out: Optional[Tuple[torch.Tens
                 or scales.dtype != torch.float16 or not packed.is_contiguous() or not scales.is_contiguous():
             raise ValueError("output buffers have the wrong size, dtype or layout")
     with torch.cuda.device(dev):
-        st = _cabi.lib().ojx_e8t_encode(wc.data_ptr(), _dtype_code(wc.dtype), rows, cols, int(group_size),
-                                        packed.data_ptr(), scales.data_ptr(), _stream_ptr(dev))
-    _cabi.check(st, "ojx_e8t_encode")
+        st = _cabi.lib().ojx_e8t_encode_ex(wc.data_ptr(), _dtype_code(wc.dtype), rows, cols, int(group_size), flags,
+                                           packed.data_ptr(), scales.data_ptr(), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_encode_ex")
     return packed, scales
 
 
