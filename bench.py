@@ -342,7 +342,7 @@ def main():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
                     help="N > 1: kernels store their column shard into every rank's output window (fused), NCCL all-gather "
                          "per launch, or no exchange at all (sharded compute only, for attribution)")
-    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "gemm_dx", "encode", "decode"],
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "gemm_dx", "encode", "decode", "project"],
                     help="run a few launches of ONE kernel on a small case and exit (used for ncu captures)")
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--N", type=int, default=4096)
@@ -693,6 +693,10 @@ def run_case(args):
         sc = torch.empty(n * k // 32, dtype=torch.float16, device=dev)
         fn = lambda: ops.encode(w, 32, out=(pk, sc))
         info["bytes_per_launch"] = n * k * 2.25
+    elif args.case == "project":                                # nearest E8 point of N*K/8 fp32 8-vectors: 4 B in + 4 B out per value
+        v = ops.generate(n * k, 60, 1.0, torch.float32, dev).view(-1, 8)
+        fn = lambda: ops.e8_project(v)
+        info["bytes_per_launch"] = n * k * 8.0
     else:
         pk, sc = ops.encode(w, 32)
         out = torch.empty((n, k), dtype=torch.float16, device=dev)
@@ -797,6 +801,14 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
             enc[name] = {"ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak}
         out["encoder_one_matrix"] = enc
         out["ingest"] = run_ingest(torch, dev)
+        # nearest-E8-point projection and the straight-through quantizer's forward: fp32, 4 B read + 4 B written per value
+        v = ops.generate(n * k // 2, 6, 1.0, torch.float32, dev).view(-1, 8)
+        out["e8_projection"] = {"values": int(v.numel()), "dtype": "f32"}
+        for name, fn in (("project", lambda: ops.e8_project(v)), ("ste_quantize", lambda: ops.e8_ste_quantize(v))):
+            ms = timed(fn, 3)
+            gbs = v.numel() * 8.0 / (ms * 1e-3) / 1e9
+            out["e8_projection"][name] = {"ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak}
+        del v
         ops.encode(w, 32, out=(pk, sc))
         # decoder (unpack): packed codes + scales -> dense fp16 weights, 0.25 B read + 2 B written per weight
         ms = timed(lambda: ops.decode(pk, sc, (n, k), torch.float16, out=w), 3)

@@ -21,6 +21,8 @@
  *   ojx_e8t_decode        TernaryE8LatticePacker.unpack          ojasx2/math/lattice.py:386-419
  *                         workspace reconstruction               ojasx2/math/lattice.py:62-84,412-416
  *   ojx_e8t_fwht32        fwht_block32                           ojasx2/math/lattice.py:91-102
+ *   ojx_e8t_project       conway_sloane_e8_project               ojasx2/math/lattice.py:162-203
+ *   ojx_e8t_ste_quantize  _E8STEFunction.forward                 ojasx2/math/lattice.py:853-867
  *   ojx_e8t_gemv/_gemm    _FusedE8GEMMFunction.forward           ojasx2/math/lattice.py:551-640
  *                         dispatch_tilelang_e8_gemm              ojasx2/tilelang_kernels.py:370-419
  *                         _build_tl_ternary_e8_1_5bit_gemm       ojasx2/tilelang_kernels.py:277-363
@@ -109,6 +111,45 @@ int32_t ojx_e8t_encode_ex(const void* w, int32_t w_dtype, int64_t rows, int64_t 
 int32_t ojx_e8t_fwht32(const void* x, int32_t dtype, int64_t count, void* out, void* stream);
 
 /*
+ * The 2.0-bit sibling format (four 2-bit codes per byte, weight = (code - 1.5) * scale, one fp16 rms scale per
+ * group of `group` consecutive weights of the flattened matrix; group a positive multiple of 8, anything else
+ * returns OJX_ERR_SHAPE where the reference raises ValueError).
+ *   ojx_e8t_encode_2bit   replaces E8LatticePacker.pack   (ojasx2/math/lattice.py:210-248), bit-exact:
+ *                         packed_out uint8[P/4], scales_out fp16[P/group], P = rows*cols padded up to group
+ *   ojx_e8t_decode_2bit   replaces E8LatticePacker.unpack (ojasx2/math/lattice.py:250-279): fp32 and fp16 exact,
+ *                         bf16 multiplies by the bf16-rounded scale as the reference does
+ *   ojx_e8t_linear_2bit   y[M, N] = x[M, K] . W^T (+ bias) from the packed codes in one fp32 kernel (any shape,
+ *                         any of the three dtypes for x, bias (x's dtype) and y); replaces the 2.0-bit branch of
+ *                         _FusedE8GEMMFunction.forward (ojasx2/math/lattice.py:596-624) and the native
+ *                         fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444).  This is a correctness path:
+ *                         the tensor-core kernels of this library serve the 1.5-bit format only.
+ */
+int32_t ojx_e8t_encode_2bit(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
+                            uint8_t* packed_out, uint16_t* scales_out, void* stream);
+int32_t ojx_e8t_decode_2bit(const uint8_t* packed, const uint16_t* scales, int64_t rows, int64_t cols, int32_t group,
+                            int32_t out_dtype, void* out, void* stream);
+int32_t ojx_e8t_linear_2bit(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                            const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype, void* stream);
+
+/*
+ * Nearest point of the E8 lattice (integer vectors with an even sum, or all of them shifted by 1/2) for
+ * each of `vectors` consecutive 8-vectors.  Replaces conway_sloane_e8_project (ojasx2/math/lattice.py:162-203;
+ * native form ojasx_math_core.hpp:385-425) bit for bit on fp32 input: round-half-even, first index wins the
+ * "largest rounding error" tie, an exact integer moves up when the parity has to be fixed, the integer candidate
+ * wins a distance tie, squared distances summed left to right without fused multiply-adds.  x and out fp32,
+ * 16-byte aligned; out may be x.  NaN input gives unspecified output for that vector.
+ */
+int32_t ojx_e8t_project(const float* x, int64_t vectors, float* out, void* stream);
+
+/*
+ * Forward of the straight-through E8 quantizer.  Replaces _E8STEFunction.forward
+ * (ojasx2/math/lattice.py:853-867) bit for bit on fp32 input: every group of eight consecutive elements of the
+ * flattened tensor (the last one zero-padded) is divided by its rms + 1e-8, projected to E8 and multiplied
+ * back, in one pass.  w and out fp32, 16-byte aligned, `count` elements; out may be w.
+ */
+int32_t ojx_e8t_ste_quantize(const float* w, int64_t count, float* out, void* stream);
+
+/*
  * Decoder.  Replaces TernaryE8LatticePacker.unpack (ojasx2/math/lattice.py:386-419).
  * out[rows, cols] = coord * cast(scale): fp32 and fp16 outputs are exact; bf16 output multiplies
  * by the bf16-rounded scale, as the reference does when asked for bf16.
@@ -125,8 +166,16 @@ int32_t ojx_e8t_decode(const uint8_t* packed, const uint16_t* scales, int64_t ro
  * multiplied by a power of two per (row, 256-wide slice of K) so that the slice maximum lies in [2^14, 2^15)
  * and converted to fp16 - exact for every element within 2^-29 of its slice maximum, so an activation
  * outlier does not degrade its neighbours; products are exact and accumulate in fp32.  Inf and NaN in x reach
- * every output of that activation row (0 * Inf = NaN, as in a dense product).  Other shapes and fp32
- * activations run a plain fp32 kernel.
+ * every output of that activation row (0 * Inf = NaN, as in a dense product).
+ * One bf16 activation row (M == 1, the decode case) runs on int8 tensor cores instead: the 32 activations of a
+ * scale group share the exponent of their largest finite magnitude and become 28-bit integers (four signed
+ * base-128 digits, one int8 MMA operand each), the ternary coordinates are int8, the integer dot product of a
+ * group is exact and is scaled once by weight scale * 2^exponent in fp32.  Every activation within 2^-19 of
+ * its group's maximum is represented exactly, smaller ones are rounded at 2^-27 of that maximum (below the
+ * rounding of the fp32 accumulation itself); scaling x by a power of two scales y by exactly that power.
+ * Inf / NaN activations are left out of the integer product and their products with the weights are added in
+ * fp32, which yields the same NaN / +-Inf pattern as a dense fp32 product.
+ * Other shapes and fp32 activations run a plain fp32 kernel.
  *   x, y       row-major, dtypes x_dtype / y_dtype (bf16, fp16 or fp32)
  *   bias       [N] in x_dtype, or null
  *   group      must be 32 and K % 32 == 0 (every row owns whole groups)

@@ -237,6 +237,8 @@ __global__ void __launch_bounds__(256, 3) gemv_reduce_kernel(const ojx_e8t_gemv_
 // Generic path: any N, K (flat packing where groups may cross rows included), any dtypes.
 // One warp per output feature; correctness path for shapes the fast kernels do not cover.
 // ---------------------------------------------------------------------------------------------
+// kTwoBit: the weights are 2-bit codes, (code - 1.5) * scale (E8LatticePacker, ojasx2/math/lattice.py:210-279).
+template <bool kTwoBit>
 __global__ void __launch_bounds__(256) generic_linear_kernel(const void* __restrict__ x, int x_dtype, int64_t M,
                                                               const uint8_t* __restrict__ packed,
                                                               const uint16_t* __restrict__ scales,
@@ -252,14 +254,20 @@ __global__ void __launch_bounds__(256) generic_linear_kernel(const void* __restr
             for (int j = 0; j < 8; ++j) acc[j] = 0.f;
             for (int64_t k = lane; k < K; k += 32) {
                 const int64_t flat = n * K + k;
-                const int64_t code_idx = flat >> 3;
-                const uint8_t* tp = packed + (code_idx >> 1) * 3;
-                uint32_t c0, c1;
-                triplet_to_codes(tp[0], tp[1], tp[2], c0, c1);
-                uint32_t code = (code_idx & 1) ? c1 : c0;
-                code = min(code, (uint32_t)(kNumPoints - 1));
-                const float w = (float)nibble_coord(g_trit_nibbles[code], (int)(flat & 7)) *
-                                __half2float(__ushort_as_half(scales[flat / group]));
+                float w;
+                if constexpr (kTwoBit) {
+                    w = ((float)((packed[flat >> 2] >> (2 * (int)(flat & 3))) & 3) - 1.5f) *
+                        __half2float(__ushort_as_half(scales[flat / group]));
+                } else {
+                    const int64_t code_idx = flat >> 3;
+                    const uint8_t* tp = packed + (code_idx >> 1) * 3;
+                    uint32_t c0, c1;
+                    triplet_to_codes(tp[0], tp[1], tp[2], c0, c1);
+                    uint32_t code = (code_idx & 1) ? c1 : c0;
+                    code = min(code, (uint32_t)(kNumPoints - 1));
+                    w = (float)nibble_coord(g_trit_nibbles[code], (int)(flat & 7)) *
+                        __half2float(__ushort_as_half(scales[flat / group]));
+                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                     if (m0 + j < M) acc[j] = fmaf(load_any(x, x_dtype, (m0 + j) * K + k), w, acc[j]);

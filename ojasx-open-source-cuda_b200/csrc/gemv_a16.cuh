@@ -1,5 +1,5 @@
 // Decode-shape linear for 1..16 activation rows (bf16 or fp16) on fp16 tensor cores, weights as the
-// row ("A") operand of mma.sync.m16n8k16.
+// row ("A") operand of mma.sync.m16n8k16; one bf16 row on int8 tensor cores (see "kI8" below).
 //
 //   y[m, n] = sum_k x[m, k] * coord[n, k] * scale[n, k / 32]  (+ bias)      fp32 accumulation
 //
@@ -28,6 +28,15 @@
 // every element within 2^-29 of the maximum, Inf / NaN pass through - and the partial sums are scaled back
 // before they are combined.  Because the scale is folded into the weights, fp32 accumulation runs across the
 // whole slice and nothing is left to do per group.
+//
+// One bf16 activation row (kI8) keeps the skeleton - loader, ring, barrier, reduction, output - and swaps the
+// arithmetic for int8 MMAs (mma.sync.m16n8k32.s8): a rank becomes its two operand registers with TWO byte permutes
+// of a 32-bit entry (eight 4-bit selectors into {0, +1, -1}; four interleaved copies of the table, so a lookup costs
+// ~2.8 shared-memory wavefronts instead of ~6.2), the activations are 28-bit fixed point per scale group, split into
+// four base-128 digits.  The eight accumulator columns serve as (lane quarter, digit pair): lane (g, t) feeds its
+// digits only into column g and only when g >> 1 == t, so after the four steps of a scale group column 2t holds the
+// group's integer sums for digits 0, 1 and column 2t + 1 for digits 2, 3 (two MMAs per step share the decoded
+// weights); they are combined, converted and scaled by weight scale * 2^exponent once per group.
 //
 // A conflict-free alternative to the 3281-entry table was built and measured: a rank r is the base-3 number
 // 2r, so its low and high four digits can index one 81-entry table stored once per lane.  It removed every
@@ -70,6 +79,13 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// int8 MMA with int32 accumulation: D (16 x 8) += A (16 x 32, row-major) * B (32 x 8, column-major).
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // Slow path of a bounded wait, kept out of line so the loop body stays small.
 __device__ __noinline__ void a16_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit) {
     if (*abort_flag != 0) return;               // some wait already gave up: the CTA is only running out its loop
@@ -105,10 +121,11 @@ __device__ __forceinline__ void a16_decode(uint32_t (&a)[4], uint32_t w0, uint32
     a[2] = prmt(pa, pb, sel.y); a[3] = prmt(pa, pb, sel.y >> 16);
 }
 
-template <int NB, bool kXF16>
+template <int NB, bool kXF16, bool kI8 = false>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid_constant__ ojx_e8t_gemv_problem single,
                 int count, int total_items, int M, int y_dtype, int overlap, const __grid_constant__ PeerMap peers) {
+    static_assert(!kI8 || (NB == 1 && !kXF16), "the int8 path serves one bf16 activation row");
     using Cfg = A16Cfg<NB>;
     constexpr int S = Cfg::kStages;
     const ojx_e8t_gemv_problem* probs = probs_dev != nullptr ? probs_dev : &single;
@@ -129,9 +146,19 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
         mbar_init(bar_lut, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // the lookup table's shared-memory image arrives as ONE bulk copy while the kernel sets itself up
-        mbar_expect_tx(bar_lut, kNumPoints * 16);
-        bulk_load(lut, g_lut_f16sel, kNumPoints * 16, bar_lut);
+        if constexpr (!kI8) {
+            // the lookup table's shared-memory image arrives as ONE bulk copy while the kernel sets itself up
+            mbar_expect_tx(bar_lut, kNumPoints * 16);
+            bulk_load(lut, g_lut_f16sel, kNumPoints * 16, bar_lut);
+        }
+    }
+    if constexpr (kI8) {
+        // int8 path: 32-bit entries (eight 4-bit byte-permute selectors), every entry four times so that the four
+        // lanes of a row read four different banks
+        for (int i = tid; i < kNumPoints; i += kGemvThreads) {
+            const uint32_t v = g_trit_nibbles[i];
+            sts_u128(lut + i * 16, make_uint4(v, v, v, v));
+        }
     }
     __syncthreads();
 
@@ -225,9 +252,14 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     const uint32_t lane_or = (uint32_t)((lane & 1) << 3);
     uint32_t xb[NB][8][4];                      // B fragments: [block][rank j][k 0-1, 2-3, 4-5, 6-7 of the rank]
     float up[NB][2];                            // 2^e of activation rows 2t, 2t+1 of the block (this lane's output columns)
+    // int8 path (one activation row): B fragments [rank j][digit pair][k 0-3, 4-7 of the rank] - non-zero only in the lane
+    // that feeds the accumulator column - and the two factors of 2^-shift of this lane's scale groups 2t and 2t + 1
+    uint32_t xq[8][2][2];
+    float ua[2] = {1.f, 1.f}, ub[2] = {1.f, 1.f};
+    bool xbad = false;                          // the slice holds Inf or NaN (same value in every lane of the warp)
     int cur_prob = -1, cur_chunk = -1, cur_K = 0;
 
-    a16_wait(bar_lut, 0u, abort_flag, 55, peers.wait_limit);        // the table has landed
+    if constexpr (!kI8) a16_wait(bar_lut, 0u, abort_flag, 55, peers.wait_limit);    // the table has landed
     int cstage = 0;
     uint32_t cparity = 0;
     for (int n = 0; n < nitems; ++n) {
@@ -248,6 +280,64 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
             cur_chunk = chunk;
             const uint16_t* xp = static_cast<const uint16_t*>(probs[prob].x);
             const int slice = chunk * act + warp;
+            if constexpr (kI8) {
+                // Fixed point per scale group: lane l holds x[8l .. 8l+7] of the slice (rank l); the 32 values of a group
+                // (four lanes) share the exponent E of their largest finite magnitude and become integers
+                // q = rint(x 2^(26 - E)), |q| <= 2^27, written in balanced base 128: q = 128^3 d0 + 128^2 d1 + 128 d2 + d3,
+                // digits in [-64, 64].  Values within 2^-19 of the group's maximum are exact (bf16 carries 8 bits), the
+                // others are rounded at 2^-27 of that maximum.  Inf / NaN become 0 here and are added back in fp32 below.
+                const uint4 q = warp < act ? __ldcg(reinterpret_cast<const uint4*>(xp + slice * 256 + lane * 8)) : make_uint4(0, 0, 0, 0);
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                uint32_t vb[8];
+                uint32_t amax = 0;
+                bool bad = false;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    vb[i] = (i & 1) ? (w[i >> 1] & 0xFFFF0000u) : (w[i >> 1] << 16);
+                    const uint32_t mag = vb[i] & 0x7FFFFFFFu;
+                    if (mag >= 0x7F800000u) { bad = true; vb[i] = 0u; }
+                    else amax = max(amax, mag);
+                }
+                xbad = __any_sync(0xFFFFFFFFu, bad);
+                amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+                amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));          // the four lanes of a group
+                const int ex = (int)(amax >> 23);
+                const int shift = 26 - (ex == 0 ? -126 : ex - 127);               // in [-101, 152]: applied as two factors
+                const int sa = shift >> 1, sb = shift - sa;
+                const float fa = __uint_as_float((uint32_t)(127 + sa) << 23), fb = __uint_as_float((uint32_t)(127 + sb) << 23);
+                uint32_t dw[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};          // [digit][values 0-3, 4-7] as int8 x 4
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int q0 = __float2int_rn(__uint_as_float(vb[i]) * fa * fb);
+                    const int q1 = (q0 + 64) >> 7, d3 = q0 - (q1 << 7);
+                    const int q2 = (q1 + 64) >> 7, d2 = q1 - (q2 << 7);
+                    const int d0 = (q2 + 64) >> 7, d1 = q2 - (d0 << 7);
+                    const int sh = 8 * (i & 3);
+                    dw[0][i >> 2] |= (uint32_t)(d0 & 0xFF) << sh;
+                    dw[1][i >> 2] |= (uint32_t)(d1 & 0xFF) << sh;
+                    dw[2][i >> 2] |= (uint32_t)(d2 & 0xFF) << sh;
+                    dw[3][i >> 2] |= (uint32_t)(d3 & 0xFF) << sh;
+                }
+                // Accumulator column c = 2t' + h takes digits 2h and 2h + 1 of the group that lane quarter t' decodes, so
+                // only lane (g, t) with g >> 1 == t feeds its column (g); every other lane's fragment is zero.
+                const bool owner = (g >> 1) == t;
+                const bool hi_digits = (g & 1) != 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int src = 8 * t + j;                                      // the lane that holds rank j of quarter t
+#pragma unroll
+                    for (int m = 0; m < 2; ++m)
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            const uint32_t lo = __shfl_sync(0xFFFFFFFFu, dw[m][r], src);
+                            const uint32_t hi = __shfl_sync(0xFFFFFFFFu, dw[2 + m][r], src);
+                            xq[j][m][r] = owner ? (hi_digits ? hi : lo) : 0u;
+                        }
+                }
+                const float una = __uint_as_float((uint32_t)(127 - sa) << 23), unb = __uint_as_float((uint32_t)(127 - sb) << 23);
+                ua[0] = __shfl_sync(0xFFFFFFFFu, una, 8 * t);     ub[0] = __shfl_sync(0xFFFFFFFFu, unb, 8 * t);       // group 2t
+                ua[1] = __shfl_sync(0xFFFFFFFFu, una, 8 * t + 4); ub[1] = __shfl_sync(0xFFFFFFFFu, unb, 8 * t + 4);   // group 2t + 1
+            } else {
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
                 const int m = nb * 8 + g;
@@ -295,6 +385,7 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
                 up[nb][0] = __shfl_sync(0xFFFFFFFFu, upg, 8 * t);          // lane (g' = 2t, *) holds activation row 2t
                 up[nb][1] = __shfl_sync(0xFFFFFFFFu, upg, 8 * t + 4);
             }
+            }
         }
 
 
@@ -311,6 +402,45 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
                 const uint32_t a0 = lds_u32(ca), a1 = lds_u32(ca + 4), a2 = lds_u32(ca + 8);
                 const uint32_t b0 = lds_u32(cb2), b1 = lds_u32(cb2 + 4), b2 = lds_u32(cb2 + 8);
                 const uint32_t ssa = lds_u32(sa), ssb = lds_u32(sa + 8 * spitch);
+                if constexpr (kI8) {
+                    // Ranks 0-3 of the lane belong to scale group 2t, ranks 4-7 to group 2t + 1: four steps of two MMAs
+                    // (digit pairs) each, then the integer sums of the group are put together and scaled once.
+                    const uint32_t lane_or4 = (uint32_t)(t << 2);
+                    constexpr uint32_t kTritBytes = 0x00FF0100u;          // selector 0 -> 0, 1 -> +1, 2 -> -1
+                    float og = 0.f, og8 = 0.f;                            // rows g and g + 8 of the tile
+                    auto half_group = [&](auto htag) {
+                        constexpr int H = decltype(htag)::value;
+                        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+                        auto step = [&](auto jtag) {
+                            constexpr int J = decltype(jtag)::value;
+                            const uint32_t ea = lds_u32(lut + ((a16_field<J, 4>(a0, a1, a2) & 0xFFF0u) | lane_or4));
+                            const uint32_t eb = lds_u32(lut + ((a16_field<J, 4>(b0, b1, b2) & 0xFFF0u) | lane_or4));
+                            const uint32_t r0 = prmt(kTritBytes, 0u, ea), r2 = prmt(kTritBytes, 0u, ea >> 16);
+                            const uint32_t r1 = prmt(kTritBytes, 0u, eb), r3 = prmt(kTritBytes, 0u, eb >> 16);
+                            mma_s8(c0, r0, r1, r2, r3, xq[J][0][0], xq[J][0][1]);
+                            mma_s8(c1, r0, r1, r2, r3, xq[J][1][0], xq[J][1][1]);
+                        };
+                        step(std::integral_constant<int, 4 * H + 0>{});
+                        step(std::integral_constant<int, 4 * H + 1>{});
+                        step(std::integral_constant<int, 4 * H + 2>{});
+                        step(std::integral_constant<int, 4 * H + 3>{});
+                        // column 2t holds digits 0 (c0) and 1 (c1), column 2t + 1 digits 2 and 3; rows g (0, 1) and g + 8 (2, 3)
+                        const float sg = fmaf((float)(c0[0] * 128 + c1[0]), 16384.f, (float)(c0[1] * 128 + c1[1]));
+                        const float sg8 = fmaf((float)(c0[2] * 128 + c1[2]), 16384.f, (float)(c0[3] * 128 + c1[3]));
+                        const float wa = __half2float(__ushort_as_half((uint16_t)(H ? (ssa >> 16) : (ssa & 0xFFFFu))));
+                        const float wb = __half2float(__ushort_as_half((uint16_t)(H ? (ssb >> 16) : (ssb & 0xFFFFu))));
+                        og = fmaf(sg * ua[H], wa * ub[H], og);
+                        og8 = fmaf(sg8 * ua[H], wb * ub[H], og8);
+                    };
+                    half_group(std::integral_constant<int, 0>{});
+                    half_group(std::integral_constant<int, 1>{});
+                    og += __shfl_xor_sync(0xFFFFFFFFu, og, 1);
+                    og8 += __shfl_xor_sync(0xFFFFFFFFu, og8, 1);
+                    og += __shfl_xor_sync(0xFFFFFFFFu, og, 2);
+                    og8 += __shfl_xor_sync(0xFFFFFFFFu, og8, 2);
+                    // the summing threads read activation row 0 only: components 0 (row g) and 2 (row g + 8) of the lanes t == 0
+                    if (t == 0) *reinterpret_cast<float4*>(rbuf + (tl * 32 + lane) * 4) = make_float4(og, 0.f, og8, 0.f);
+                } else {
                 float acc[NB][4];
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f;
@@ -346,6 +476,46 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
                 for (int nb = 0; nb < NB; ++nb)
                     *reinterpret_cast<float4*>(rbuf + ((tl * NB + nb) * 32 + lane) * 4) =
                         make_float4(acc[nb][0] * up[nb][0], acc[nb][1] * up[nb][1], acc[nb][2] * up[nb][0], acc[nb][3] * up[nb][1]);
+                }
+            }
+        }
+        if constexpr (kI8) {
+            if (xbad && warp < act) {
+                // Inf / NaN in this warp's slice (they were fed to the MMAs as 0): lane r adds, in fp32, the products of
+                // weight row r with those activations - Inf * 0 and anything * NaN give NaN, as in fp32 arithmetic.
+                const uint32_t cpitch = act * 48 + 16, spitch = act * 16 + 16;
+                const uint16_t* xp = static_cast<const uint16_t*>(probs[prob].x) + (chunk * act + warp) * 256;
+                const uint4 q = __ldcg(reinterpret_cast<const uint4*>(xp + lane * 8));
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                bool mine = false;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mine = mine || ((w[i] << 16) & 0x7FFFFFFFu) >= 0x7F800000u || (w[i] & 0x7FFF0000u) >= 0x7F800000u;
+                uint32_t holders = __ballot_sync(0xFFFFFFFFu, mine);
+                const uint8_t* codes = smem + (stage - lut) + lane * cpitch + warp * 48;        // weight row `lane` of the item
+                const uint16_t* scl = reinterpret_cast<const uint16_t*>(smem + (stage - lut) + kA16ScaleOff + lane * spitch + warp * 16);
+                float corr = 0.f;
+                while (holders != 0u) {
+                    const int l = __ffs(holders) - 1;                      // rank l of the slice = the eight values lane l holds
+                    holders &= holders - 1u;
+                    uint32_t xv[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) xv[i] = __shfl_sync(0xFFFFFFFFu, w[i], l);
+                    const uint32_t b0 = codes[(3 * l) >> 1], b1 = codes[((3 * l) >> 1) + 1];
+                    const uint32_t rank = (l & 1) ? ((b0 >> 4) | (b1 << 4)) : (b0 | ((b1 & 0xFu) << 8));
+                    const uint32_t entry = g_trit_nibbles[rank < (uint32_t)kNumPoints ? rank : 0u];
+                    const float sc = __half2float(__ushort_as_half(scl[l >> 2]));
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t bits = (i & 1) ? (xv[i >> 1] & 0xFFFF0000u) : (xv[i >> 1] << 16);
+                        if ((bits & 0x7FFFFFFFu) >= 0x7F800000u) {
+                            const uint32_t sel = (entry >> (4 * i)) & 0xFu;
+                            const float coord = sel == 1u ? 1.f : (sel == 2u ? -1.f : 0.f);
+                            corr += (coord * sc) * __uint_as_float(bits);
+                        }
+                    }
+                }
+                __syncwarp();                                              // the lanes' own partial sums are written
+                rbuf[((lane >> 4) * 32 + (lane & 7) * 4) * 4 + (((lane >> 3) & 1) << 1)] += corr;
             }
         }
         __syncthreads();           // the stage is free again and every warp's partial sums are visible

@@ -63,7 +63,7 @@ static int32_t launch_maybe_overlapped(void (*kernel)(Params...), int grid, int 
     return OJX_OK;
 }
 
-template <int NB, bool kXF16>
+template <int NB, bool kXF16, bool kI8 = false>
 static int32_t launch_gemv_a16(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
                                int M, int y_dtype, const PeerMap& peers_in, bool overlap, cudaStream_t s) {
     PeerMap peers = peers_in;
@@ -71,18 +71,20 @@ static int32_t launch_gemv_a16(const ojx_e8t_gemv_problem* probs, const ojx_e8t_
     peers.wait_limit = wait_limit_override() != 0 ? wait_limit_override() : kSpinLimit;
     static std::atomic<uint64_t> configured{0};
     using Cfg = A16Cfg<NB>;
-    const int32_t st = ensure_dynamic_smem(gemv_a16_kernel<NB, kXF16>, Cfg::kSmem, configured);
+    const int32_t st = ensure_dynamic_smem(gemv_a16_kernel<NB, kXF16, kI8>, Cfg::kSmem, configured);
     OJX_RETURN_IF(st != OJX_OK, st);
     const int sms = num_sms();
     const int per = (total + sms - 1) / sms;
     const int grid = (total + per - 1) / per;
-    return launch_maybe_overlapped(gemv_a16_kernel<NB, kXF16>, grid, kGemvThreads, Cfg::kSmem, s, overlap,
+    return launch_maybe_overlapped(gemv_a16_kernel<NB, kXF16, kI8>, grid, kGemvThreads, Cfg::kSmem, s, overlap,
                                    probs, single, count, total, M, y_dtype, overlap ? 1 : 0, peers);
 }
 
-// One to eight activation rows take one block of eight columns per MMA, nine to sixteen take two.
+// One bf16 activation row takes the int8 path; one to eight rows take one block of eight columns per fp16 MMA, nine to
+// sixteen take two.
 static int32_t dispatch_gemv(bool bf16, const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count,
                              int total, int M, int y_dtype, const PeerMap& peers, bool overlap, cudaStream_t s) {
+    if (bf16 && M == 1) return launch_gemv_a16<1, false, true>(probs, single, count, total, M, y_dtype, peers, overlap, s);
     if (bf16) return M <= 8 ? launch_gemv_a16<1, false>(probs, single, count, total, M, y_dtype, peers, overlap, s)
                             : launch_gemv_a16<2, false>(probs, single, count, total, M, y_dtype, peers, overlap, s);
     return M <= 8 ? launch_gemv_a16<1, true>(probs, single, count, total, M, y_dtype, peers, overlap, s)
@@ -179,7 +181,20 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
     int64_t warps_needed = N;
     int64_t blocks = (warps_needed * 32 + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    generic_linear_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
+    generic_linear_kernel<false><<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
+    return launch_status();
+}
+
+// y = x . W^T (+ bias) for 2-bit weights: the fused fp32 kernel (one warp per output feature), any shape.
+int32_t linear_2bit_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales, const void* bias,
+                         int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s) {
+    OJX_RETURN_IF(!x || !packed || !scales || !y, OJX_ERR_NULL);
+    OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0 || group <= 0 || group % 8 != 0, OJX_ERR_SHAPE);
+    OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
+    OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
+    int64_t blocks = (N * 32 + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    generic_linear_kernel<true><<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
     return launch_status();
 }
 

@@ -4,6 +4,8 @@
 
 #include "common.cuh"
 #include "codec.cuh"
+#include "codec2.cuh"
+#include "e8_project.cuh"
 #include "gemv.cuh"
 #include "gemv_a16.cuh"
 #include "gemv_host.cuh"
@@ -106,6 +108,30 @@ int32_t ojx_e8t_encode(const void* w, int32_t w_dtype, int64_t rows, int64_t col
 int32_t ojx_e8t_encode_ex(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group, uint32_t flags,
                           uint8_t* packed_out, uint16_t* scales_out, void* stream) {
     return ojx::encode_impl(w, w_dtype, rows, cols, group, flags, packed_out, scales_out, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_encode_2bit(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
+                            uint8_t* packed_out, uint16_t* scales_out, void* stream) {
+    return ojx::encode2_impl(w, w_dtype, rows, cols, group, packed_out, scales_out, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_decode_2bit(const uint8_t* packed, const uint16_t* scales, int64_t rows, int64_t cols, int32_t group,
+                            int32_t out_dtype, void* out, void* stream) {
+    return ojx::decode2_impl(packed, scales, rows, cols, group, out_dtype, out, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_linear_2bit(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                            const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype, void* stream) {
+    return ojx::linear_2bit_impl(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_project(const float* x, int64_t vectors, float* out, void* stream) {
+    if (vectors <= 0 || vectors > (INT64_MAX >> 3)) return OJX_ERR_SHAPE;
+    return ojx::e8_project_impl(x, vectors * 8, out, false, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_ste_quantize(const float* w, int64_t count, float* out, void* stream) {
+    return ojx::e8_project_impl(w, count, out, true, (cudaStream_t)stream);
 }
 
 int32_t ojx_e8t_fwht32(const void* x, int32_t dtype, int64_t count, void* out, void* stream) {

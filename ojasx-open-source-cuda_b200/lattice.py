@@ -24,16 +24,20 @@ from typing import Optional, Tuple, Union
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from . import ops
 
-_SUPPORTED_BITRATE = 1.5
+_SUPPORTED_BITRATES = (1.5, 2.0)
 
 
 def _check_bitrate(bitrate: float) -> None:
-    if float(bitrate) != _SUPPORTED_BITRATE:
+    """1.5 (ternary E8, the tensor-core path) and 2.0 (four codes per byte, fused fp32 kernel) are implemented.
+    The 1.0-bit root packer chooses codes by an argmax over a BLAS product whose rounding differs between
+    libraries, so its output cannot be reproduced bit for bit; it is not offered."""
+    if float(bitrate) not in _SUPPORTED_BITRATES:
         raise NotImplementedError(
-            f"bitrate={bitrate!r}: the B200 backend implements the 1.5-bit ternary-E8 path only")
+            f"bitrate={bitrate!r}: the B200 backend implements the 1.5-bit ternary-E8 and the 2.0-bit E8 formats")
 
 
 class _Fwht32(torch.autograd.Function):
@@ -68,6 +72,50 @@ def fwht_block32(x: torch.Tensor) -> torch.Tensor:
         h = torch.stack([a + b, a - b], dim=2).reshape(-1, 32)
         span *= 2
     return (h * 0.1767766952966369).reshape(x.shape)
+
+
+def conway_sloane_e8_project(x: torch.Tensor, prefer_native: bool = True) -> torch.Tensor:
+    """Snaps every 8-vector along the last dimension to the nearest point of E8 = D8 u (D8 + 1/2)
+    (reference ``lattice.py:162-203``; ``prefer_native`` is accepted for signature compatibility - there is one
+    implementation, the CUDA kernel)."""
+    return ops.e8_project(x)
+
+
+class _E8STEFunction(torch.autograd.Function):
+    """E8 quantization with a straight-through gradient (reference ``lattice.py:853-867``)."""
+
+    @staticmethod
+    def forward(ctx, w: torch.Tensor) -> torch.Tensor:
+        return ops.e8_ste_quantize(w)
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor) -> torch.Tensor:
+        return grad_output
+
+
+class E8QuantizationAwareLinear(nn.Module):
+    """Linear layer that trains dense weights through the E8 quantizer (reference ``lattice.py:870-899``)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True,
+                 device: Optional[torch.device] = None, dtype: Optional[torch.dtype] = None) -> None:
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_features, device=device, dtype=dtype))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+        if self.bias is not None:
+            bound = 1 / math.sqrt(self.in_features) if self.in_features > 0 else 0
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(x, _E8STEFunction.apply(self.weight), self.bias)
 
 
 _LUT_CACHE = {}
@@ -114,9 +162,28 @@ class TernaryE8LatticePacker:
         return ops.decode(packed_codes, scales, (int(shape[0]), int(shape[1])), dtype)
 
 
+class E8LatticePacker:
+    """2.0 bits/weight, four codes per byte (reference ``lattice.py:210-279``): same entry points and errors."""
+
+    @staticmethod
+    def pack(w: torch.Tensor, group_size: int = 8) -> Tuple[torch.Tensor, torch.Tensor, Tuple[int, int]]:
+        m, n = w.shape
+        if group_size <= 0 or group_size % 8 != 0:
+            raise ValueError(f"group_size ({group_size}) must be a positive multiple of 8.")
+        src = w if w.dtype in (torch.float32, torch.float16, torch.bfloat16) else w.to(torch.float32)
+        packed, scales = ops.encode_2bit(src, group_size)
+        return packed, scales, (m, n)
+
+    @staticmethod
+    def unpack(packed_codes: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, int],
+               dtype: torch.dtype = torch.float32, use_workspace: bool = False) -> torch.Tensor:
+        del use_workspace
+        return ops.decode_2bit(packed_codes, scales, (int(shape[0]), int(shape[1])), dtype)
+
+
 def _get_packer_for_bitrate(bitrate: float):
     _check_bitrate(bitrate)
-    return TernaryE8LatticePacker
+    return TernaryE8LatticePacker if float(bitrate) == 1.5 else E8LatticePacker
 
 
 class _FusedE8GEMMFunction(torch.autograd.Function):
@@ -141,7 +208,11 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.use_hadamard = use_hadamard
         ctx.group_size = group_size
+        ctx.bitrate = float(bitrate)
         x_2d = x_rot.reshape(-1, in_features)
+        if float(bitrate) == 2.0:
+            y_2d = ops.linear_2bit(x_2d, packed_weight, block_scales, bias, out_features, in_features, group_size)
+            return y_2d.reshape(*x_rot.shape[:-1], out_features)
         eff = ops.effective_group(group_size)
         if torch.compiler.is_compiling() and in_features % eff == 0:
             # under torch.compile the kernels are reached through the registered operator, which the compiler
@@ -157,7 +228,10 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
         packed_weight, block_scales = ctx.saved_tensors
         gy_2d = grad_y.reshape(-1, ctx.out_features).contiguous()
         eff = ops.effective_group(ctx.group_size)
-        if torch.compiler.is_compiling() and ctx.in_features % eff == 0:
+        if ctx.bitrate == 2.0:
+            w = ops.decode_2bit(packed_weight, block_scales, (ctx.out_features, ctx.in_features), ctx.x_dtype)
+            grad_x = gy_2d.to(ctx.x_dtype).matmul(w).reshape(ctx.x_shape)
+        elif torch.compiler.is_compiling() and ctx.in_features % eff == 0:
             grad_x = torch.ops.ojasx_math_native.fused_ternary_e8_gemm_bwd_dx(
                 gy_2d.to(ctx.x_dtype), packed_weight.view(ctx.out_features, -1), block_scales.view(ctx.out_features, -1),
                 ctx.in_features, eff).reshape(ctx.x_shape)
@@ -187,9 +261,13 @@ class E8LatticeLinear(nn.Module):
         self.scaling = (lora_alpha / rank) if rank > 0 else 0.0
         self.bitrate = float(bitrate)
         self.use_hadamard = bool(use_hadamard and (in_features % 32 == 0))
-        eff_group = group_size if (group_size >= 16 and group_size % 16 == 0) else 16
+        if self.bitrate == 1.5:
+            eff_group = group_size if (group_size >= 16 and group_size % 16 == 0) else 16
+            num_bytes, num_scales = ops.packed_sizes(out_features, in_features, eff_group)
+        else:
+            eff_group = group_size if (group_size >= 8 and group_size % 8 == 0) else 8
+            num_bytes, num_scales = ops.packed_sizes_2bit(out_features, in_features, eff_group)
         self.group_size = eff_group
-        num_bytes, num_scales = ops.packed_sizes(out_features, in_features, eff_group)
         self.register_buffer("packed_weight", torch.zeros(num_bytes, dtype=torch.uint8, device=device))
         self.register_buffer("block_scales", torch.ones(num_scales, dtype=torch.float16, device=device))
         if bias:
@@ -209,19 +287,20 @@ class E8LatticeLinear(nn.Module):
     def from_linear(cls, linear: nn.Linear, rank: int = 0, lora_alpha: float = 16.0, group_size: int = 8,
                     bitrate: float = 2.0, use_hadamard: bool = False) -> "E8LatticeLinear":
         _check_bitrate(bitrate)
-        eff_gs = max(16, group_size)
+        eff_gs = max(16, group_size) if float(bitrate) == 1.5 else group_size
         m = cls(linear.in_features, linear.out_features, bias=(linear.bias is not None), rank=rank,
                 lora_alpha=lora_alpha, group_size=eff_gs, bitrate=bitrate, use_hadamard=use_hadamard,
                 device=linear.weight.device, dtype=linear.weight.dtype)
         with torch.no_grad():
-            ops.encode(linear.weight, m.group_size, out=(m.packed_weight, m.block_scales), hadamard=m.use_hadamard)
+            encode = ops.encode if m.bitrate == 1.5 else ops.encode_2bit
+            encode(linear.weight, m.group_size, out=(m.packed_weight, m.block_scales), hadamard=m.use_hadamard)
             if linear.bias is not None:
                 m.bias.copy_(linear.bias)
         return m
 
     def unpack_weights(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
-        w = TernaryE8LatticePacker.unpack(self.packed_weight, self.block_scales,
-                                          (self.out_features, self.in_features), dtype=dtype)
+        w = _get_packer_for_bitrate(self.bitrate).unpack(self.packed_weight, self.block_scales,
+                                                         (self.out_features, self.in_features), dtype=dtype)
         return fwht_block32(w) if self.use_hadamard else w
 
     def forward_fused(self, x: torch.Tensor) -> torch.Tensor:

@@ -91,6 +91,108 @@ def fwht32(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     return res
 
 
+def packed_sizes_2bit(rows: int, cols: int, group_size: int) -> Tuple[int, int]:
+    if group_size <= 0 or group_size % 8 != 0:
+        raise ValueError(f"group_size ({group_size}) must be a positive multiple of 8.")
+    total = rows * cols
+    padded = total + ((-total) % group_size)
+    return padded // 4, padded // group_size
+
+
+def encode_2bit(w: torch.Tensor, group_size: int = 8, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                hadamard: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``w`` [rows, cols] -> (packed uint8[P/4], scales fp16[P/g]) in the 2.0-bit format; bit-exact with the
+    reference's ``E8LatticePacker.pack`` (``ojasx2/math/lattice.py:210-248``)."""
+    if w.dim() != 2:
+        raise ValueError(f"expected a 2-D weight, got shape {tuple(w.shape)}")
+    dev = _require_cuda(w)
+    rows, cols = int(w.shape[0]), int(w.shape[1])
+    nbytes, nscales = packed_sizes_2bit(rows, cols, group_size)
+    if rows == 0 or cols == 0:
+        raise ValueError("empty weight")
+    wc = w.detach().contiguous()
+    if hadamard and cols % 32 == 0:
+        wc = fwht32(wc)
+    if out is None:
+        packed = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        scales = torch.empty(nscales, dtype=torch.float16, device=dev)
+    else:
+        packed, scales = out
+        if packed.numel() != nbytes or scales.numel() != nscales or packed.dtype != torch.uint8 \
+                or scales.dtype != torch.float16 or not packed.is_contiguous() or not scales.is_contiguous():
+            raise ValueError("output buffers have the wrong size, dtype or layout")
+    with torch.cuda.device(dev):
+        st = _cabi.lib().ojx_e8t_encode_2bit(wc.data_ptr(), _dtype_code(wc.dtype), rows, cols, int(group_size),
+                                             packed.data_ptr(), scales.data_ptr(), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_encode_2bit")
+    return packed, scales
+
+
+def decode_2bit(packed: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, int],
+                dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """2-bit codes + scales -> dense [rows, cols] in ``dtype``; the group size is inferred from the buffer sizes
+    as the reference does (``ojasx2/math/lattice.py:262-264``)."""
+    dev = _require_cuda(packed, scales)
+    rows, cols = int(shape[0]), int(shape[1])
+    group = (packed.numel() * 4) // max(1, scales.numel())
+    out = torch.empty((rows, cols), dtype=dtype, device=dev)
+    with torch.cuda.device(dev):
+        st = _cabi.lib().ojx_e8t_decode_2bit(packed.contiguous().data_ptr(), scales.contiguous().data_ptr(), rows, cols,
+                                             group, _dtype_code(dtype), out.data_ptr(), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_decode_2bit")
+    return out
+
+
+def linear_2bit(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor], n: int, k: int,
+                group_size: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``y = x . W^T (+ bias)`` from 2-bit codes in one fused fp32 kernel."""
+    dev = _require_cuda(x, packed, scales)
+    x2 = x.detach().reshape(-1, k).contiguous()
+    m = int(x2.shape[0])
+    y = torch.empty((m, n), dtype=out_dtype or x2.dtype, device=dev)
+    if m == 0:
+        return y
+    b = None if bias is None else bias.detach().to(x2.dtype).contiguous()
+    with torch.cuda.device(dev):
+        st = _cabi.lib().ojx_e8t_linear_2bit(x2.data_ptr(), _dtype_code(x2.dtype), m, packed.data_ptr(), scales.data_ptr(),
+                                             None if b is None else b.data_ptr(), n, k, int(group_size), y.data_ptr(),
+                                             _dtype_code(y.dtype), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_linear_2bit")
+    return y
+
+
+def _fp32_pass(x: torch.Tensor, name: str, vectors: bool) -> torch.Tensor:
+    dev = _require_cuda(x)
+    src = x.detach().to(torch.float32).contiguous()
+    if src.data_ptr() % 16:
+        src = src.clone()
+    res = torch.empty_like(src)
+    with torch.cuda.device(dev):
+        fn = getattr(_cabi.lib(), name)
+        st = fn(src.data_ptr(), src.numel() // 8 if vectors else src.numel(), res.data_ptr(), _stream_ptr(dev))
+    _cabi.check(st, name)
+    return res if x.dtype == torch.float32 else res.to(x.dtype)
+
+
+def e8_project(x: torch.Tensor) -> torch.Tensor:
+    """Nearest E8 lattice point of every 8-vector along the last dimension (one kernel; bit-identical to the
+    reference's ``conway_sloane_e8_project`` on fp32 tensors; 16-bit tensors are projected in fp32 and
+    rounded back)."""
+    if x.shape[-1] != 8:
+        raise ValueError(f"Last dimension must be 8 for E8 lattice (got {x.shape[-1]}).")
+    if x.numel() == 0:
+        return x.clone()
+    return _fp32_pass(x, "ojx_e8t_project", True)
+
+
+def e8_ste_quantize(w: torch.Tensor) -> torch.Tensor:
+    """Forward of the reference's ``_E8STEFunction``: groups of eight consecutive elements scaled by their rms,
+    projected to E8 and scaled back, one kernel (bit-identical on fp32 tensors)."""
+    if w.numel() == 0:
+        return w.clone()
+    return _fp32_pass(w, "ojx_e8t_ste_quantize", False)
+
+
 def encode(w: torch.Tensor, group_size: int = 32, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
            hadamard: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """``w`` [rows, cols] -> (packed uint8[P*3/16], scales fp16[P/g]); bit-exact with the

@@ -42,10 +42,18 @@ def _validate_row_layout(out_features: int, in_features: int, bitrate: float, gr
     _check_bitrate(bitrate)
 
 
+def _encoder_for(bitrate: float):
+    _check_bitrate(bitrate)
+    return ops.encode if float(bitrate) == 1.5 else ops.encode_2bit
+
+
+def _bytes_per_row(in_features: int, bitrate: float) -> int:
+    return in_features * 3 // 16 if float(bitrate) == 1.5 else in_features // 4
+
+
 def _pack_row_block(block: torch.Tensor, bitrate: float, group_size: int, use_hadamard: bool
                     ) -> Tuple[torch.Tensor, torch.Tensor]:
-    _check_bitrate(bitrate)
-    return ops.encode(block, group_size, hadamard=use_hadamard)
+    return _encoder_for(bitrate)(block, group_size, hadamard=use_hadamard)
 
 
 def pack_weight_rowwise(weight: torch.Tensor, *, bitrate: float = 1.5, group_size: int = 32, row_block: int = 32,
@@ -57,13 +65,13 @@ def pack_weight_rowwise(weight: torch.Tensor, *, bitrate: float = 1.5, group_siz
         raise ValueError("row_block must be positive")
     out_features, in_features = map(int, weight.shape)
     _validate_row_layout(out_features, in_features, bitrate, group_size)
-    nbytes, nscales = ops.packed_sizes(out_features, in_features, group_size)
-    packed = torch.empty(nbytes, dtype=torch.uint8, device=weight.device)
-    scales = torch.empty(nscales, dtype=torch.float16, device=weight.device)
-    bytes_per_row, scales_per_row = in_features * 3 // 16, in_features // group_size
+    encode = _encoder_for(bitrate)
+    bytes_per_row, scales_per_row = _bytes_per_row(in_features, bitrate), in_features // group_size
+    packed = torch.empty(out_features * bytes_per_row, dtype=torch.uint8, device=weight.device)
+    scales = torch.empty(out_features * scales_per_row, dtype=torch.float16, device=weight.device)
     for start in range(0, out_features, row_block):
         stop = min(start + row_block, out_features)
-        ops.encode(weight[start:stop], group_size, hadamard=use_hadamard,
+        encode(weight[start:stop], group_size, hadamard=use_hadamard,
                    out=(packed[start * bytes_per_row: stop * bytes_per_row],
                         scales[start * scales_per_row: stop * scales_per_row]))
     return packed, scales
@@ -78,7 +86,7 @@ def _destination_ranges(layer: E8LatticeLinear, row_start: int, block: torch.Ten
     if not block.dtype.is_floating_point:
         raise TypeError(f"E8 packing requires floating-point source weights, got {block.dtype}")
     rows = int(block.shape[0])
-    bytes_per_row = layer.in_features * 3 // 16
+    bytes_per_row = _bytes_per_row(layer.in_features, layer.bitrate)
     scales_per_row = layer.in_features // layer.group_size
     p0, s0 = row_start * bytes_per_row, row_start * scales_per_row
     if p0 + rows * bytes_per_row > layer.packed_weight.numel():
@@ -94,7 +102,7 @@ def _copy_row_block_into_layer(layer: E8LatticeLinear, row_start: int, block: to
     out = _destination_ranges(layer, row_start, block)
     source = block.to(layer.packed_weight.device)
     with torch.no_grad():
-        ops.encode(source, layer.group_size, out=out, hadamard=use_hadamard)
+        _encoder_for(layer.bitrate)(source, layer.group_size, out=out, hadamard=use_hadamard)
     return int(block.numel() * block.element_size())
 
 
@@ -123,7 +131,7 @@ class _RowBlockPipe:
             staged = host.to(self.device, non_blocking=True)
             self.copied[i] = torch.cuda.Event()
             self.copied[i].record(self.stream)
-            ops.encode(staged, layer.group_size, out=out, hadamard=use_hadamard)
+            _encoder_for(layer.bitrate)(staged, layer.group_size, out=out, hadamard=use_hadamard)
 
     def finish(self) -> None:
         torch.cuda.current_stream(self.device).wait_stream(self.stream)

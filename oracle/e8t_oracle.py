@@ -295,3 +295,103 @@ def gemm_tolerance(x: np.ndarray, k: int) -> Tuple[float, float]:
     """``(max_abs_bound, rel_l2_bound)`` of the GEMM contract:
     max-abs <= 1e-2 * ||x||_inf * sqrt(K), relative L2 <= 2e-3."""
     return 1e-2 * float(np.abs(np.asarray(x, dtype=np.float64)).max()) * math.sqrt(k), 2e-3
+
+
+# ---------------------------------------------------------------------------------------------
+# Nearest E8 lattice point and the straight-through quantizer built on it
+# ---------------------------------------------------------------------------------------------
+
+def _seq_sum_f32(a: np.ndarray) -> np.ndarray:
+    """Sum over the last axis, left to right, every partial sum rounded to fp32 (the order torch's CPU
+    reduction uses for rows of eight)."""
+    s = a[..., 0].astype(np.float32).copy()
+    for i in range(1, a.shape[-1]):
+        s = (s + a[..., i]).astype(np.float32)
+    return s
+
+
+def _d8_candidate(v: np.ndarray) -> np.ndarray:
+    """Nearest point of D8 (integer vectors with an even coordinate sum) to each row of ``v``: round every
+    coordinate; when the sum is odd move the coordinate with the largest rounding error (first one on ties)
+    one step in the direction of its error (+1 when the error is zero)."""
+    f = np.rint(v).astype(np.float32)
+    odd = (_seq_sum_f32(f).astype(np.int64) % 2) != 0
+    diff = (v - f).astype(np.float32)
+    worst = np.argmax(np.abs(diff), axis=-1)
+    sign = np.sign(diff).astype(np.float32)
+    sign[sign == 0] = 1.0
+    rows = np.arange(v.shape[0])
+    fixed = f.copy()
+    fixed[rows, worst] = (f[rows, worst] + sign[rows, worst]).astype(np.float32)
+    return np.where(odd[:, None], fixed, f).astype(np.float32)
+
+
+def conway_sloane_project(x: np.ndarray) -> np.ndarray:
+    """Nearest point of E8 = D8 u (D8 + 1/2) to every 8-vector (rows of ``x`` reshaped to [-1, 8]), fp32.
+    Follows conway_sloane_e8_project (ojasx2/math/lattice.py:162-203) operation by operation: the D8 candidate of x,
+    the D8 candidate of x - 1/2 shifted back, squared distances summed left to right, the first wins ties."""
+    v = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, 8)
+    c1 = _d8_candidate(v)
+    c2 = (_d8_candidate((v - np.float32(0.5)).astype(np.float32)) + np.float32(0.5)).astype(np.float32)
+    e1, e2 = (v - c1).astype(np.float32), (v - c2).astype(np.float32)
+    d1, d2 = _seq_sum_f32((e1 * e1).astype(np.float32)), _seq_sum_f32((e2 * e2).astype(np.float32))
+    return np.where((d1 <= d2)[:, None], c1, c2).astype(np.float32).reshape(np.shape(x))
+
+
+def ste_quantize(w: np.ndarray) -> np.ndarray:
+    """Forward of the straight-through E8 quantizer (_E8STEFunction.forward, ojasx2/math/lattice.py:853-867): groups
+    of eight consecutive elements of the flattened tensor (zero padded) are divided by rms + 1e-8, projected to E8
+    and multiplied back; fp32."""
+    flat = np.ascontiguousarray(w, dtype=np.float32).reshape(-1)
+    total = flat.size
+    pad = (-total) % 8
+    if pad:
+        flat = np.concatenate([flat, np.zeros(pad, dtype=np.float32)])
+    g = flat.reshape(-1, 8)
+    nrm = np.sqrt(_seq_sum_f32((g * g).astype(np.float32))).astype(np.float32)
+    scale = ((nrm / np.float32(math.sqrt(8))).astype(np.float32) + np.float32(1e-8)).astype(np.float32)[:, None]
+    q = conway_sloane_project((g / scale).astype(np.float32))
+    return (q * scale).astype(np.float32).reshape(-1)[:total].reshape(np.shape(w))
+
+
+# ---------------------------------------------------------------------------------------------
+# 2.0-bit format: four 2-bit codes per byte, weight = (code - 1.5) * scale
+# ---------------------------------------------------------------------------------------------
+
+def encode_2bit(w: np.ndarray, group_size: int = 8):
+    """Restatement of ``E8LatticePacker.pack`` (ojasx2/math/lattice.py:210-248).  ``group_size`` must be a positive
+    multiple of 8 (the reference raises otherwise).  Every 8-block of the rms-normalised weights is moved to the
+    half-integer grid {-1.5, -0.5, 0.5, 1.5}^8 with an even sum of the underlying integers: round(x - 1/2) clamped
+    to [-2, 1]; when the sum is odd the coordinate whose move to its other neighbour costs least (first one on
+    ties, clamping included) is moved.  Returns ``(packed uint8[P/4], scales float16[P/g], (rows, cols))``."""
+    rows, cols = w.shape
+    if group_size <= 0 or group_size % 8 != 0:
+        raise ValueError(f"group_size ({group_size}) must be a positive multiple of 8.")
+    flat = np.ascontiguousarray(w, dtype=F32).reshape(-1)
+    pad = (-flat.size) % group_size
+    if pad:
+        flat = np.concatenate([flat, np.zeros(pad, dtype=F32)])
+    groups = flat.reshape(-1, group_size)
+    scale = group_scales_f32(groups)
+    xs = ((groups / scale[:, None]).astype(F32).reshape(-1, 8) - F32(0.5)).astype(F32)
+    f = np.clip(np.rint(xs), -2.0, 1.0).astype(F32)
+    odd = (f.sum(axis=1).astype(np.int64) % 2) != 0
+    alt = np.where(xs >= f, np.clip(f + 1, -2.0, 1.0), np.clip(f - 1, -2.0, 1.0)).astype(F32)
+    da, df = (alt - xs).astype(F32), (f - xs).astype(F32)
+    pen = ((da * da).astype(F32) - (df * df).astype(F32)).astype(F32)
+    worst = pen.argmin(axis=1)
+    idx = np.nonzero(odd)[0]
+    f[idx, worst[idx]] = alt[idx, worst[idx]]
+    codes = np.clip(np.rint((f + F32(0.5)).astype(F32) + F32(1.5)), 0, 3).astype(np.uint8).reshape(-1, 4)
+    packed = (codes[:, 0] | (codes[:, 1] << 2) | (codes[:, 2] << 4) | (codes[:, 3] << 6)).astype(np.uint8)
+    return packed, scale.astype(np.float16), (rows, cols)
+
+
+def decode_2bit(packed: np.ndarray, scales: np.ndarray, shape: Tuple[int, int]) -> np.ndarray:
+    """Restatement of ``E8LatticePacker.unpack`` in fp32 (ojasx2/math/lattice.py:250-279)."""
+    p = np.ascontiguousarray(packed, dtype=np.uint8)
+    codes = np.stack([p & 3, (p >> 2) & 3, (p >> 4) & 3, (p >> 6) & 3], axis=-1).reshape(-1)
+    g = codes.size // max(1, scales.size)
+    vals = (codes.astype(F32) - F32(1.5)).reshape(-1, g) * scales.astype(F32).reshape(-1, 1)
+    total = shape[0] * shape[1]
+    return vals.astype(F32).reshape(-1)[:total].reshape(shape)

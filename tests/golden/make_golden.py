@@ -180,6 +180,43 @@ def main():
                             sha_packed=sha(layer.packed_weight.numpy()))
     print("hadamard", meta["hadamard"]["sha_packed"][:16])
 
+    # nearest E8 point (lattice.py:162-203) and the straight-through quantizer's forward (lattice.py:853-867), fp32:
+    # random vectors at four magnitudes, a quarter-integer grid (exact distance and rounding ties), integer
+    # vectors (zero rounding error, odd sums), and weights whose element count is not a multiple of eight
+    proj_in = np.concatenate([
+        O.gen_normal(90, 384 * 8, 0.3), O.gen_normal(91, 384 * 8, 1.0), O.gen_normal(92, 384 * 8, 3.0),
+        O.gen_normal(93, 128 * 8, 40.0),
+        np.rint(O.gen_normal(94, 384 * 8, 2.0) * 4.0).astype(np.float32) * np.float32(0.25),
+        np.rint(O.gen_normal(95, 128 * 8, 2.0)).astype(np.float32),
+    ]).astype(np.float32).reshape(-1, 8)
+    proj_out = L.conway_sloane_e8_project(torch.from_numpy(proj_in.copy()), prefer_native=False)
+    arrays["project/input"] = proj_in
+    arrays["project/output"] = proj_out.numpy()
+    ste_in = O.gen_normal(96, 37 * 19, 0.05).reshape(37, 19).copy()
+    ste_in[3, :] = 0.0
+    arrays["ste/input"] = ste_in
+    arrays["ste/output"] = L._E8STEFunction.apply(torch.from_numpy(ste_in.copy())).numpy()
+    meta["project"] = dict(vectors=int(proj_in.shape[0]), sha_output=sha(arrays["project/output"]),
+                           sha_ste_output=sha(arrays["ste/output"]))
+    print("project", meta["project"]["sha_output"][:16], meta["project"]["sha_ste_output"][:16])
+
+    # 2.0-bit packer (lattice.py:210-279): two group sizes, a heavy-tailed input (clamping active) and a half-integer
+    # grid (rounding and penalty ties), with a padded tail in the first case
+    two = {
+        "g8": (torch.from_numpy(O.gen_normal(110, 33 * 100, 1.0).reshape(33, 100).copy()), 8),
+        "g32": (torch.from_numpy(O.gen_normal(111, 48 * 256, 0.02).reshape(48, 256).copy()), 32),
+        "heavy": (torch.from_numpy((O.gen_normal(112, 32 * 128, 1.0) ** 3).astype(np.float32).reshape(32, 128).copy()), 8),
+        "grid": (torch.from_numpy((np.rint(O.gen_normal(113, 32 * 128, 2.0)) * 0.5).astype(np.float32).reshape(32, 128).copy()), 32),
+    }
+    for tag, (wt, g) in two.items():
+        p2, s2, _ = L.E8LatticePacker.pack(wt, group_size=g)
+        arrays[f"two_bit/{tag}/input"] = wt.numpy()
+        arrays[f"two_bit/{tag}/group"] = np.int64(g)
+        arrays[f"two_bit/{tag}/packed"] = p2.numpy()
+        arrays[f"two_bit/{tag}/scales"] = s2.view(torch.int16).numpy().view(np.uint16)
+        arrays[f"two_bit/{tag}/decoded"] = L.E8LatticePacker.unpack(p2, s2, tuple(wt.shape), dtype=torch.float32).numpy()
+        print("two_bit", tag, sha(p2.numpy())[:16])
+
     # decode of every code: all 3281 ranks (padded to an even count) with unit scales
     ranks = np.arange(3282, dtype=np.int64) % 3281
     packed_all = O.pack_codes(ranks)

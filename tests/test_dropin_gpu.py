@@ -272,6 +272,33 @@ def test_activation_outliers_nan_and_inf(P, oracle):
         assert (~torch.isfinite(y[m - 1])).all()
         if m > 1:
             assert torch.isfinite(y[: m - 1]).all()
+        # the pattern of NaN / +Inf / -Inf equals that of the dense fp32 product (0 * Inf = NaN, w * Inf = +-Inf)
+        xi[m - 1, 17] = float("-inf")
+        xi[0, 4095] = float("inf")
+        y = P.ops.linear(xi, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+        ref = xi.float() @ wd.t()
+        assert torch.equal(torch.isnan(y), torch.isnan(ref))
+        assert torch.equal(torch.isposinf(y), torch.isposinf(ref)) and torch.equal(torch.isneginf(y), torch.isneginf(ref))
+        fin = torch.isfinite(ref)
+        if bool(fin.any()):
+            assert float(((y - ref)[fin].abs() / (xi.float().abs() @ wd.abs().t())[fin]).max()) < 1e-5
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_power_of_two_scaling_of_activations_is_exact(P, m):
+    """Both tensor-core paths rescale activations by powers of two only, so y(2^s x) == 2^s y(x) bit for bit -
+    for tiny, huge and mixed magnitudes alike (K = 14336 also runs the partial-sum reduction)."""
+    dev = torch.device(DEV)
+    for n, k in ((64, 4096), (40, 14336)):
+        w = P.ops.generate(n * k, 31, 0.02, torch.float16, dev).view(n, k)
+        pk, sc = P.ops.encode(w, 32)
+        x = P.ops.generate(m * k, 32 + m, 1.0, torch.bfloat16, dev).view(m, k).clone()
+        x[:, ::97] *= 2.0 ** -12                                  # a spread of magnitudes inside every group
+        x[:, 5::512] = 0.0
+        y = P.ops.linear(x, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+        for s in (-80, -30, 40, 90):
+            ys = P.ops.linear(x * 2.0 ** s, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+            assert torch.equal(ys, y * 2.0 ** s), (m, n, k, s)
 
 
 def _import_reference():

@@ -92,8 +92,11 @@ def test_layer_buffers_and_errors_on_cpu(P):
     assert tuple(layer.lora_A.shape) == (128, 2) and tuple(layer.lora_B.shape) == (2, 64)
     odd = P.E8LatticeLinear(13, 7, bias=False, group_size=8, bitrate=1.5)      # padded flat layout, group coerced to 16
     assert odd.group_size == 16 and odd.packed_weight.numel() == 96 * 3 // 16 and odd.block_scales.numel() == 6
+    two = P.E8LatticeLinear(64, 8)                     # the reference's defaults: 2.0 bits, groups of 8
+    assert two.bitrate == 2.0 and two.group_size == 8
+    assert two.packed_weight.numel() == 64 * 8 // 4 and two.block_scales.numel() == 64 * 8 // 8
     with pytest.raises(NotImplementedError):
-        P.E8LatticeLinear(64, 8)                       # default bit-rate 2.0 is outside this backend
+        P.E8LatticeLinear(64, 8, bitrate=1.0)          # the root packer is not offered
     with pytest.raises(RuntimeError):
         layer(torch.zeros(1, 128))                     # CPU tensors: the CUDA path is the only path
     with pytest.raises(ValueError):

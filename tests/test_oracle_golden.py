@@ -165,3 +165,44 @@ def test_multithreaded_c_oracle_matches_single(oracle, coracle):
     y1 = coracle.linear(x, p1, s1, 64, 512, threads=1)
     y4 = coracle.linear(x, p1, s1, 64, 512, threads=4)
     assert np.array_equal(y1, y4)
+
+
+def test_e8_projection_oracle_against_reference_outputs(golden, oracle):
+    """conway_sloane_project / ste_quantize restate ojasx2/math/lattice.py:162-203 and :853-867; the golden file
+    holds the reference's own outputs for random vectors at four magnitudes, a quarter-integer grid (ties in
+    rounding, in the largest error and in the distance comparison) and integer vectors."""
+    meta, arrays = golden
+    x, want = arrays["project/input"], arrays["project/output"]
+    got = oracle.conway_sloane_project(x)
+    assert got.dtype == np.float32 and np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert hashlib.sha256(np.ascontiguousarray(got).tobytes()).hexdigest() == meta["project"]["sha_output"]
+    # every output is a lattice point: all integers or all half-integers, even coordinate sum
+    twice = got * 2
+    assert np.array_equal(twice, np.rint(twice))
+    frac = np.abs(got - np.floor(got))
+    assert np.all((frac == 0).all(axis=1) | (frac == 0.5).all(axis=1))
+    assert np.all(np.rint(got.sum(axis=1)) % 2 == 0)
+    # and no lattice point one coordinate step (or the half-shifted twin) away is closer than the chosen one
+    d = ((x - got) ** 2).sum(axis=1)
+    assert np.all(d <= 2.0 + 1e-6)                                   # covering radius of E8 is 1
+    w, wq = arrays["ste/input"], arrays["ste/output"]
+    assert np.array_equal(oracle.ste_quantize(w).view(np.uint32), wq.view(np.uint32))
+    assert np.all(wq[3] == 0)                                        # an all-zero row stays zero
+
+
+def test_two_bit_oracle_against_reference_outputs(golden, oracle):
+    """encode_2bit / decode_2bit restate E8LatticePacker (ojasx2/math/lattice.py:210-279); the golden file holds
+    the reference's own codes, scales and decoded weights."""
+    _, arrays = golden
+    for tag in ("g8", "g32", "heavy", "grid"):
+        w, g = arrays[f"two_bit/{tag}/input"], int(arrays[f"two_bit/{tag}/group"])
+        p, s, shape = oracle.encode_2bit(w, g)
+        assert shape == w.shape
+        assert np.array_equal(p, arrays[f"two_bit/{tag}/packed"]), tag
+        assert np.array_equal(s.view(np.uint16), arrays[f"two_bit/{tag}/scales"]), tag
+        assert np.array_equal(oracle.decode_2bit(p, s, w.shape), arrays[f"two_bit/{tag}/decoded"]), tag
+        # every 8-block is a point of D8 + 1/2 unless clamping blocked the parity fix: half-integers in [-1.5, 1.5]
+        vals = oracle.decode_2bit(p, np.ones_like(s), w.shape)
+        assert set(np.unique(vals)).issubset({-1.5, -0.5, 0.5, 1.5})
+    with pytest.raises(ValueError):
+        oracle.encode_2bit(np.zeros((2, 8), dtype=np.float32), 12)

@@ -274,7 +274,7 @@ def test_module_forward_backward_and_state(P, oracle):
     small = P.E8LatticeLinear.from_linear(torch.nn.Linear(64, 8).to(dev), bitrate=1.5, group_size=8)
     assert small.group_size == 16
     with pytest.raises(NotImplementedError):
-        P.E8LatticeLinear(64, 8, bitrate=2.0)
+        P.E8LatticeLinear(64, 8, bitrate=1.0)
 
 
 def test_seam_signature_and_errors(P):
@@ -374,3 +374,121 @@ def test_gemm_long_rows_take_the_two_pass_normalisation(P):
     for row in (0, 3, 7, 39):
         d = y[row].float() - ref[row]
         assert float(d.norm() / ref[row].norm()) <= 2e-3, row
+
+
+def test_e8_projection_matches_reference_bits(P, golden, oracle):
+    """ojx_e8t_project / ojx_e8t_ste_quantize against the reference's outputs in the golden file and, on a
+    larger seeded input, against the oracle (ojasx2/math/lattice.py:162-203, 853-867)."""
+    _, arrays = golden
+    dev = torch.device(DEV)
+    x = torch.from_numpy(arrays["project/input"]).to(dev)
+    got = P.conway_sloane_e8_project(x).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), arrays["project/output"].view(np.uint32))
+    w = torch.from_numpy(arrays["ste/input"]).to(dev)
+    gq = P._E8STEFunction.apply(w).cpu().numpy()
+    assert np.array_equal(gq.view(np.uint32), arrays["ste/output"].view(np.uint32))
+    for sigma in (0.2, 1.0, 25.0):
+        big = oracle.gen_normal(300, 1 << 20, sigma).reshape(-1, 8)
+        assert np.array_equal(P.ops.e8_project(torch.from_numpy(big).to(dev)).cpu().numpy().view(np.uint32),
+                              oracle.conway_sloane_project(big).view(np.uint32))
+    grid = (np.rint(oracle.gen_normal(301, 1 << 18, 2.0) * 4.0) * 0.25).astype(np.float32).reshape(-1, 8)
+    assert np.array_equal(P.ops.e8_project(torch.from_numpy(grid).to(dev)).cpu().numpy(), oracle.conway_sloane_project(grid))
+    wbig = oracle.gen_normal(302, 1000 * 1003, 0.03).reshape(1000, 1003)          # element count not a multiple of 8
+    assert np.array_equal(P.ops.e8_ste_quantize(torch.from_numpy(wbig).to(dev)).cpu().numpy().view(np.uint32),
+                          oracle.ste_quantize(wbig).view(np.uint32))
+    # idempotence: lattice points project onto themselves
+    again = P.ops.e8_project(torch.from_numpy(got).to(dev)).cpu().numpy()
+    assert np.array_equal(again, got)
+    with pytest.raises(ValueError):
+        P.conway_sloane_e8_project(torch.zeros(4, 7, device=dev))
+    assert P.conway_sloane_e8_project(torch.zeros(0, 8, device=dev)).shape == (0, 8)
+
+
+def test_quantization_aware_linear_trains_through_the_quantizer(P):
+    """E8QuantizationAwareLinear (ojasx2/math/lattice.py:870-899): forward uses quantized weights, the gradient
+    reaches the dense weights unchanged (straight-through)."""
+    dev = torch.device(DEV)
+    torch.manual_seed(5)
+    layer = P.E8QuantizationAwareLinear(64, 24, bias=True, device=dev)
+    x = torch.randn(6, 64, device=dev)
+    wq = P.ops.e8_ste_quantize(layer.weight)
+    y = layer(x)
+    assert torch.allclose(y, torch.nn.functional.linear(x, wq, layer.bias), atol=1e-6)
+    y.sum().backward()
+    assert torch.allclose(layer.weight.grad, x.sum(0).expand(24, 64), atol=1e-5)
+    wb = layer.weight.detach().to(torch.bfloat16)                   # 16-bit tensors: quantized in fp32, rounded back
+    half = P.ops.e8_ste_quantize(wb)
+    assert half.dtype == torch.bfloat16 and torch.equal(half, P.ops.e8_ste_quantize(wb.float()).to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("rows,cols,group,sigma,dtype", [(64, 256, 8, 0.02, "f32"), (33, 100, 8, 1.0, "f32"),
+                                                         (128, 512, 32, 0.02, "f16"), (16, 256, 64, 0.5, "bf16"),
+                                                         (7, 13, 16, 0.3, "f32"), (40, 64, 24, 2.0, "f32"),
+                                                         (512, 4096, 8, 0.02, "bf16")])
+def test_two_bit_packer_matches_oracle_bits(P, oracle, rows, cols, group, sigma, dtype):
+    """ojx_e8t_encode_2bit / ojx_e8t_decode_2bit against the restatement of E8LatticePacker
+    (ojasx2/math/lattice.py:210-279), which the golden vectors pin to the reference: codes and scales bit for
+    bit for every group size and a padded tail, decoded weights bit for bit in fp32."""
+    dev = torch.device(DEV)
+    w = torch.from_numpy(oracle.gen_normal(500 + rows, rows * cols, sigma).reshape(rows, cols).copy()).to(TD[dtype])
+    want_p, want_s, _ = oracle.encode_2bit(w.float().numpy(), group)
+    got_p, got_s, shape = P.E8LatticePacker.pack(w.to(dev), group_size=group)
+    assert shape == (rows, cols)
+    assert np.array_equal(got_p.cpu().numpy(), want_p)
+    assert np.array_equal(got_s.view(torch.int16).cpu().numpy(), want_s.view(np.int16))
+    dec = P.E8LatticePacker.unpack(got_p, got_s, (rows, cols), dtype=torch.float32).cpu().numpy()
+    assert np.array_equal(dec.view(np.uint32), oracle.decode_2bit(want_p, want_s, (rows, cols)).view(np.uint32))
+    unit = torch.from_numpy(oracle.decode_2bit(want_p, np.ones_like(want_s), (rows, cols)))          # code - 1.5
+    per_weight = torch.from_numpy(want_s).repeat_interleave(group)[: rows * cols].view(rows, cols)      # fp16 scales
+    for dt in (torch.float16, torch.bfloat16):            # (code - 1.5) * cast(scale), rounded to the output type
+        d16 = P.E8LatticePacker.unpack(got_p, got_s, (rows, cols), dtype=dt).cpu()
+        assert torch.equal(d16, unit.to(dt) * per_weight.to(dt))
+    with pytest.raises(ValueError):
+        P.E8LatticePacker.pack(w.to(dev), group_size=12)
+
+
+def test_two_bit_golden_and_special_inputs(P, golden, oracle):
+    _, arrays = golden
+    dev = torch.device(DEV)
+    for tag in ("g8", "g32", "heavy", "grid"):
+        w = torch.from_numpy(arrays[f"two_bit/{tag}/input"]).to(dev)
+        g = int(arrays[f"two_bit/{tag}/group"])
+        p, s, _ = P.E8LatticePacker.pack(w, group_size=g)
+        assert np.array_equal(p.cpu().numpy(), arrays[f"two_bit/{tag}/packed"]), tag
+        assert np.array_equal(s.view(torch.int16).cpu().numpy().view(np.uint16), arrays[f"two_bit/{tag}/scales"]), tag
+        d = P.E8LatticePacker.unpack(p, s, tuple(w.shape), dtype=torch.float32).cpu().numpy()
+        assert np.array_equal(d, arrays[f"two_bit/{tag}/decoded"]), tag
+
+
+def test_two_bit_layer_with_reference_defaults(P, oracle):
+    """E8LatticeLinear() with the reference's defaults (2.0 bits, groups of 8): forward against the fp32
+    dequantize-then-matmul of the oracle within the GEMM contract, backward dX, rotation, streaming rows."""
+    dev = torch.device(DEV)
+    torch.manual_seed(9)
+    lin = torch.nn.Linear(256, 96, bias=True).to(dev)
+    for had in (False, True):
+        layer = P.E8LatticeLinear.from_linear(lin, rank=4, use_hadamard=had)
+        assert layer.bitrate == 2.0 and layer.group_size == 8 and layer.packed_weight.numel() == 96 * 256 // 4
+        src = P.fwht_block32(lin.weight.detach()) if had else lin.weight.detach()
+        want_p, want_s, _ = oracle.encode_2bit(src.cpu().numpy(), 8)
+        assert np.array_equal(layer.packed_weight.cpu().numpy(), want_p)
+        wd = torch.from_numpy(oracle.decode_2bit(want_p, want_s, (96, 256))).to(dev)
+        assert torch.equal(layer.unpack_weights(torch.float32), P.fwht_block32(wd) if had else wd)
+        for m, dt in ((1, torch.float32), (5, torch.bfloat16), (33, torch.float16)):
+            x = torch.randn(m, 256, device=dev).to(dt).requires_grad_(True)
+            y = layer(x)
+            xr = P.fwht_block32(x.detach()) if had else x.detach()
+            ref = xr.float() @ wd.t() + lin.bias.detach().to(dt).float()
+            tol_abs, tol_rel = oracle.gemm_tolerance(x.detach().float().cpu().numpy(), 256)
+            err = (y.float() - ref)
+            assert float(err.abs().max()) <= tol_abs and float(err.norm() / ref.norm()) <= max(tol_rel, 4e-3 if dt != torch.float32 else 0)
+            y.float().sum().backward()
+            gref = torch.ones(m, 96, device=dev) @ wd
+            gref = P.fwht_block32(gref) if had else gref
+            assert float((x.grad.float() - gref).abs().max()) <= 2e-2 * float(gref.abs().max())
+    rowwise_p, rowwise_s = P.pack_weight_rowwise(lin.weight.detach(), bitrate=2.0, group_size=32, row_block=7)
+    whole_p, whole_s = P.ops.encode_2bit(lin.weight.detach(), 32)
+    assert torch.equal(rowwise_p, whole_p) and torch.equal(rowwise_s, whole_s)
+    model = P.pack_model_e8(torch.nn.Sequential(torch.nn.Linear(64, 32), torch.nn.ReLU(), torch.nn.Linear(32, 8)).to(dev))
+    assert all(isinstance(model[i], P.E8LatticeLinear) and model[i].bitrate == 2.0 for i in (0, 2))
+    assert model(torch.randn(3, 64, device=dev)).shape == (3, 8)
