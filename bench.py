@@ -809,6 +809,23 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
             gbs = v.numel() * 8.0 / (ms * 1e-3) / 1e9
             out["e8_projection"][name] = {"ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak}
         del v
+        # the 2.0-bit sibling format: packer and unpacker on the same matrix (2 B in + 0.25 B codes + scales out, and back),
+        # and its fused fp32 linear on one 4096 x 4096 matrix at one activation row (a correctness path, not tensor cores)
+        two = {"rows": n, "cols": k, "dtype": "f16"}
+        for g in (8, 32):
+            p2 = torch.empty(n * k // 4, dtype=torch.uint8, device=dev)
+            s2 = torch.empty(n * k // g, dtype=torch.float16, device=dev)
+            bpw = 2.0 + 0.25 + 2.0 / g
+            ms = timed(lambda: ops.encode_2bit(w, g, out=(p2, s2)), 3)
+            two[f"encode_group{g}"] = {"ms": ms, "GBps": n * k * bpw / (ms * 1e-3) / 1e9, "frac_hbm": n * k * bpw / (ms * 1e-3) / 1e9 / hbm_peak}
+            ms = timed(lambda: ops.decode_2bit(p2, s2, (n, k), torch.float16), 3)
+            two[f"decode_group{g}"] = {"ms": ms, "GBps": n * k * bpw / (ms * 1e-3) / 1e9, "frac_hbm": n * k * bpw / (ms * 1e-3) / 1e9 / hbm_peak}
+        x1 = ops.generate(4096, 8, 1.0, torch.bfloat16, dev).view(1, 4096)
+        nl = 4096
+        ms = timed(lambda: ops.linear_2bit(x1, p2[: nl * 4096 // 4], s2[: nl * 4096 // 32], None, nl, 4096, 32), 5)
+        two["linear_4096x4096_1row"] = {"ms": ms, "packed_GBps": nl * 4096 * (0.25 + 2.0 / 32) / (ms * 1e-3) / 1e9}
+        out["two_bit"] = two
+        del p2, s2
         ops.encode(w, 32, out=(pk, sc))
         # decoder (unpack): packed codes + scales -> dense fp16 weights, 0.25 B read + 2 B written per weight
         ms = timed(lambda: ops.decode(pk, sc, (n, k), torch.float16, out=w), 3)

@@ -190,6 +190,20 @@ int32_t ojx_e8t_gemv(const void* x, int32_t x_dtype, int64_t M,
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * ojx_e8t_gemv with the adapter term of E8LatticeLinear.forward_fused (ojasx2/math/lattice.py:826-842) fused into the
+ * epilogue: y = x . W^T (+ bias) + lora_t . lora_b, where lora_t [M, lora_rank] fp32 = scaling * (x . A) and lora_b
+ * [lora_rank, N] has x's dtype.  Only the tensor-core decode shapes up to eight rows are served (1 <= M <= 8, K % 256 == 0, group 32,
+ * 16-bit x, 16-byte aligned buffers, lora_rank <= 64); anything else returns OJX_ERR_UNSUPPORTED and the caller adds
+ * the term itself.
+ */
+int32_t ojx_e8t_gemv_lora(const void* x, int32_t x_dtype, int64_t M,
+                          const uint8_t* packed, const uint16_t* scales, const void* bias,
+                          int64_t N, int64_t K, int32_t group,
+                          const float* lora_t, const void* lora_b, int32_t lora_rank,
+                          void* y, int32_t y_dtype,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * ojx_e8t_gemv for callers that cannot hand over scratch memory (no counterpart in the reference).
  * Meant for hosts where a plug-in only ever sees its input and output buffers: a serving process whose
  * device memory is pre-carved by its own arena, a callback that runs where cudaMalloc is not allowed
@@ -232,6 +246,16 @@ typedef struct {
     int32_t         ldy;          /* distance in elements between consecutive rows of y; 0 means N.  A larger value lets
                                      y be a column block of a wider [M, ldy] matrix (the place of one rank's shard in
                                      the full output of a column-sharded linear) */
+    /* Optional low-rank term added in the epilogue, in fp32, before the one rounding to y's type:
+     *   y[m, n] += sum_r lora_t[m, r] * lora_b[r, n]
+     * lora_t = scaling * (x . A) as fp32 [M, lora_rank] (computed by the caller; it is read after the product, so it may
+     * be produced by work queued just ahead of the launch), lora_b [lora_rank, N] in x's dtype.  lora_rank == 0: none;
+     * honoured for M <= 8.
+     * This is the adapter term of E8LatticeLinear.forward_fused (ojasx2/math/lattice.py:839-842). */
+    const float*    lora_t;
+    const void*     lora_b;
+    int32_t         lora_rank;
+    int32_t         reserved;
 } ojx_e8t_gemv_problem;
 
 int32_t ojx_e8t_gemv_tiles(int64_t N, int64_t K);

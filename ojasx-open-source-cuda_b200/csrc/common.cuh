@@ -36,6 +36,13 @@ inline int dtype_size(int dt) {
     }
 }
 
+// Byte permute: byte i of the result is byte sel[4i+3:4i] of the eight bytes {b, a}.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
@@ -130,7 +137,7 @@ inline int32_t launch_status() {
 }
 
 // Entry points implemented in the individual .cu files (called by api.cu).
-int32_t encode_impl(const void* w, int w_dtype, int64_t rows, int64_t cols, int group,
+int32_t encode_impl(const void* w, int w_dtype, int64_t rows, int64_t cols, int group, uint32_t flags,
                     uint8_t* packed, uint16_t* scales, cudaStream_t s);
 int32_t decode_impl(const uint8_t* packed, const uint16_t* scales, int64_t rows, int64_t cols,
                     int group, int out_dtype, void* out, cudaStream_t s);
@@ -139,7 +146,8 @@ int32_t generate_impl(void* out, int dtype, int64_t count, uint64_t seed, int64_
 size_t  gemv_workspace_bytes_impl(int64_t M, int64_t N, int64_t K);
 int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                   const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
-                  void* workspace, size_t workspace_bytes, cudaStream_t s);
+                  void* workspace, size_t workspace_bytes, cudaStream_t s,
+                  const float* lora_t = nullptr, const void* lora_b = nullptr, int lora_rank = 0);
 size_t  gemv_static_scratch_capacity_impl();
 int32_t gemv_static_scratch_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                                  const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s);

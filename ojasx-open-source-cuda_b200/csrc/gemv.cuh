@@ -25,12 +25,6 @@ __host__ __device__ inline int gemv_kchunks(int K) { return (K / 256) / gemv_act
 // The public tile unit (ojx_e8t_gemv_tiles) is 32 weight rows x one K chunk.
 __host__ __device__ inline int gemv_row_tiles32(int N) { return (N + 31) / 32; }
 
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t r;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-    return r;
-}
-
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -165,9 +159,19 @@ __device__ __forceinline__ float load_any(const void* p, int dt, int64_t i) {
     return static_cast<const float*>(p)[i];
 }
 
-// Sums the K-chunk partials of every problem that has them (fixed order), adds bias, casts, stores - to this rank's
-// buffer and to every peer's window.  16-bit outputs whose rows come in multiples of eight are handled eight rows
-// (one 16-byte vector) per thread.
+// The optional low-rank term of a problem for output (activation row col, weight row row).
+// Kept out of line: it is rare, and inlined into the decode kernels' epilogue it costs them registers they do not have.
+template <bool kBf16>
+__device__ __noinline__ float lora_term(const ojx_e8t_gemv_problem& P, int64_t col, int64_t row) {
+    float acc = 0.f;
+    const float* t = P.lora_t + col * P.lora_rank;
+    for (int r = 0; r < P.lora_rank; ++r) acc = fmaf(t[r], load_act<kBf16>(P.lora_b, (int64_t)r * P.N + row), acc);
+    return acc;
+}
+
+// Sums the K-chunk partials of every problem that has them (fixed order), adds bias and the low-rank term, casts,
+// stores - to this rank's buffer and to every peer's window.  16-bit outputs whose rows come in multiples of eight
+// are handled eight rows (one 16-byte vector) per thread.
 template <bool kBf16>
 __global__ void __launch_bounds__(256, 3) gemv_reduce_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev,
                                                            const __grid_constant__ ojx_e8t_gemv_problem single,
@@ -198,6 +202,7 @@ __global__ void __launch_bounds__(256, 3) gemv_reduce_kernel(const ojx_e8t_gemv_
                 for (int i = 0; i < 4; ++i) {
                     float lo = s8[2 * i], hi = s8[2 * i + 1];
                     if (P.bias != nullptr) { lo += load_act<kBf16>(P.bias, row + 2 * i); hi += load_act<kBf16>(P.bias, row + 2 * i + 1); }
+                    if (P.lora_rank > 0) { lo += lora_term<kBf16>(P, col, row + 2 * i); hi += lora_term<kBf16>(P, col, row + 2 * i + 1); }
                     if (y_dtype == OJX_BF16) {
                         const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
                         w[i] = *reinterpret_cast<const uint32_t*>(&h);
@@ -220,6 +225,7 @@ __global__ void __launch_bounds__(256, 3) gemv_reduce_kernel(const ojx_e8t_gemv_
             for (int c = 0; c < kc; ++c) s += P.partial[(int64_t)c * total + i];
             const int64_t col = i / P.N, row = i - col * P.N;
             if (P.bias != nullptr) s += load_act<kBf16>(P.bias, row);
+            if (P.lora_rank > 0) s += lora_term<kBf16>(P, col, row);
             const int64_t at = col * ld + row;
             store_any(P.y, y_dtype, at, s);
 #pragma unroll 1

@@ -548,6 +548,9 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
                     if (P.partial != nullptr) P.partial[((int64_t)chunk * M + col) * rN + row] = sum;
                     else {
                         if (P.bias != nullptr) sum += load_any(P.bias, kXF16 ? OJX_F16 : OJX_BF16, row);
+                        if constexpr (NB == 1) {                         // the host refuses the low-rank term beyond eight rows
+                            if (P.lora_rank > 0) sum += lora_term<!kXF16>(P, col, row);
+                        }
                         if (vec) {
                             ost[col * kA16Rows + rin] = y_dtype == OJX_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum))
                                                                             : __half_as_ushort(__float2half_rn(sum));

@@ -149,8 +149,11 @@ int32_t peer_wait_impl(ojx_e8t_peer_sync* peer_sync, int world, cudaStream_t s) 
 
 int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                   const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
-                  void* workspace, size_t workspace_bytes, cudaStream_t s) {
+                  void* workspace, size_t workspace_bytes, cudaStream_t s,
+                  const float* lora_t, const void* lora_b, int lora_rank) {
     OJX_RETURN_IF(!x || !packed || !scales || !y, OJX_ERR_NULL);
+    OJX_RETURN_IF(lora_rank < 0 || lora_rank > 64 || (lora_rank > 0 && (!lora_t || !lora_b)), OJX_ERR_SHAPE);
+    OJX_RETURN_IF(lora_rank > 0 && M > 8, OJX_ERR_UNSUPPORTED);        // the 9-16 row kernels have no registers to spare for it
     OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0, OJX_ERR_SHAPE);
     OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
@@ -166,6 +169,7 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         const int kc = gemv_kchunks((int)K);
         h.partial = kc > 1 ? static_cast<float*>(workspace) : nullptr;
         h.N = (int)N; h.K = (int)K; h.tile_begin = 0; h.ldy = 0;
+        h.lora_t = lora_t; h.lora_b = lora_b; h.lora_rank = lora_rank; h.reserved = 0;
         const int total = gemv_row_tiles32((int)N) * kc;
         const bool bf = x_dtype == OJX_BF16;
         const int32_t st = dispatch_gemv(bf, nullptr, h, 1, total, (int)M, y_dtype, peer_map_self(), false, s);
@@ -177,6 +181,7 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         }
         return launch_status();
     }
+    OJX_RETURN_IF(lora_rank > 0, OJX_ERR_UNSUPPORTED);          // the low-rank epilogue exists in the tensor-core kernels only
     // generic path
     int64_t warps_needed = N;
     int64_t blocks = (warps_needed * 32 + 255) / 256;

@@ -152,6 +152,13 @@ int32_t ojx_e8t_gemv(const void* x, int32_t x_dtype, int64_t M, const uint8_t* p
                           (cudaStream_t)stream);
 }
 
+int32_t ojx_e8t_gemv_lora(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                          const void* bias, int64_t N, int64_t K, int32_t group, const float* lora_t, const void* lora_b,
+                          int32_t lora_rank, void* y, int32_t y_dtype, void* workspace, size_t workspace_bytes, void* stream) {
+    return ojx::gemv_impl(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, workspace, workspace_bytes,
+                          (cudaStream_t)stream, lora_t, lora_b, lora_rank);
+}
+
 size_t ojx_e8t_gemv_static_scratch_capacity(void) { return ojx::gemv_static_scratch_capacity_impl(); }
 
 int32_t ojx_e8t_gemv_static_scratch(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,

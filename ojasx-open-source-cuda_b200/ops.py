@@ -280,6 +280,41 @@ def _prep_linear(x2d, packed, scales, bias, n, k):
     return dev, x2d, packed.contiguous(), scales.contiguous(), b
 
 
+def lora_fusable(m: int, k: int, group_size: int, dtype: torch.dtype, rank: int) -> bool:
+    """Shapes for which the adapter term can ride in the decode kernel's epilogue (``ojx_e8t_gemv_lora``)."""
+    return (1 <= m <= 8 and k % 256 == 0 and effective_group(group_size) == 32
+            and dtype in (torch.bfloat16, torch.float16) and 0 < rank <= 64)
+
+
+def linear_lora(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
+                out_features: int, in_features: int, group_size: int, lora_t: torch.Tensor, lora_b: torch.Tensor,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``y = x . dequant(W)^T (+ bias) + lora_t . lora_b`` in ONE decode-shape launch: ``lora_t`` [M, r] fp32 is
+    ``scaling * (x . A)``, ``lora_b`` [r, N]; the low-rank term is accumulated in fp32 in the kernel's epilogue
+    (the reference adds it with three more tensor operations, ``ojasx2/math/lattice.py:839-842``)."""
+    n, k = int(out_features), int(in_features)
+    dev, x2d, pk, sc, b = _prep_linear(x2d, packed, scales, bias, n, k)
+    _cabi.raise_pending()
+    m, r = int(x2d.shape[0]), int(lora_b.shape[0])
+    if not lora_fusable(m, k, group_size, x2d.dtype, r):
+        raise ValueError("this shape cannot take the fused adapter term; add it separately")
+    if tuple(lora_t.shape) != (m, r) or tuple(lora_b.shape) != (r, n):
+        raise ValueError("lora_t must be [M, r] and lora_b [r, N]")
+    t = lora_t.detach().to(torch.float32).contiguous()
+    bb = lora_b.detach().to(x2d.dtype).contiguous()
+    y = torch.empty((m, n), dtype=out_dtype or x2d.dtype, device=dev)
+    lib = _cabi.lib()
+    with torch.cuda.device(dev):
+        need = lib.ojx_e8t_gemv_workspace_bytes(m, n, k)
+        ws = scratch(dev, need, "gemv") if need else None
+        st = lib.ojx_e8t_gemv_lora(x2d.data_ptr(), _dtype_code(x2d.dtype), m, pk.data_ptr(), sc.data_ptr(),
+                                   b.data_ptr() if b is not None else None, n, k, 32, t.data_ptr(), bb.data_ptr(), r,
+                                   y.data_ptr(), _dtype_code(y.dtype), ws.data_ptr() if ws is not None else None,
+                                   ws.numel() if ws is not None else 0, _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_gemv_lora")
+    return y
+
+
 def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
            out_features: int, in_features: int, group_size: int = 32,
            out_dtype: Optional[torch.dtype] = None, force: Optional[str] = None) -> torch.Tensor:

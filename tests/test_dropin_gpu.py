@@ -365,3 +365,62 @@ def test_reference_layer_runs_on_cuda_through_the_patched_seam(P, oracle):
         assert calls and all(calls)
     finally:
         ref.dispatch_tilelang_e8_gemm = stock
+
+
+@pytest.mark.parametrize("m,k,n,dt", [(1, 4096, 96, torch.bfloat16), (4, 4096, 96, torch.float16), (8, 1024, 40, torch.bfloat16),
+                                      (1, 14336, 64, torch.bfloat16), (5, 14336, 64, torch.float16)])
+def test_adapter_term_in_the_decode_epilogue(P, m, k, n, dt):
+    """ojx_e8t_gemv_lora: y = x . W^T + bias + lora_t . lora_b in one launch (also through the K > 4096 reduction),
+    against the fp32 dense computation; the adapter term of E8LatticeLinear.forward_fused
+    (ojasx2/math/lattice.py:839-842)."""
+    dev = torch.device(DEV)
+    w = P.ops.generate(n * k, 41, 0.02, torch.float16, dev).view(n, k)
+    pk, sc = P.ops.encode(w, 32)
+    wd = P.ops.decode(pk, sc, (n, k), torch.float32)
+    x = P.ops.generate(m * k, 42 + m, 1.0, dt, dev).view(m, k)
+    bias = P.ops.generate(n, 43, 0.1, dt, dev)
+    r = 8
+    t = torch.randn(m, r, device=dev) * 3.0
+    b = (torch.randn(r, n, device=dev) * 0.5).to(dt)
+    y = P.ops.linear_lora(x, pk, sc, bias, n, k, 32, t, b, out_dtype=torch.float32)
+    ref = x.float() @ wd.t() + bias.float() + t @ b.float()
+    budget = x.float().abs() @ wd.abs().t() + bias.float().abs() + t.abs() @ b.float().abs()
+    assert float(((y - ref).abs() / budget).max()) < 1e-5
+    plain = P.ops.linear(x, pk, sc, bias, n, k, 32, out_dtype=torch.float32)
+    assert torch.equal(P.ops.linear_lora(x, pk, sc, bias, n, k, 32, torch.zeros_like(t), b, out_dtype=torch.float32), plain)
+    y16 = P.ops.linear_lora(x, pk, sc, None, n, k, 32, t, b)
+    assert y16.dtype == dt
+    assert float((y16.float() - (ref - bias.float())).abs().max()) <= 2.0 ** -7 * float(ref.abs().max()) + 1e-3
+
+
+def test_layer_with_adapter_takes_the_fused_epilogue_at_inference(P):
+    dev = torch.device(DEV)
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(1024, 72, bias=True).to(dev).to(torch.bfloat16)
+    for had in (False, True):
+        layer = P.E8LatticeLinear.from_linear(lin, rank=8, bitrate=1.5, group_size=32, use_hadamard=had)
+        with torch.no_grad():
+            layer.lora_B.copy_(torch.randn_like(layer.lora_B) * 0.1)
+        x = torch.randn(3, 1024, device=dev).to(torch.bfloat16)
+        wd = layer.unpack_weights(torch.float32)              # rotated back when the layer stores rotated weights
+        ref = (x.float() @ wd.t() + lin.bias.float()
+               + layer.scaling * ((x @ layer.lora_A.to(x.dtype)).float() @ layer.lora_B.float()))
+        calls = []
+        orig = P.ops.linear_lora
+        P.ops.linear_lora = lambda *a, **kw: (calls.append(1), orig(*a, **kw))[1]
+        try:
+            with torch.no_grad():
+                y = layer(x)
+            assert len(calls) == 1                             # one launch carries the adapter
+            y_train = layer(x)                                 # adapters require grad: the differentiable route
+            assert len(calls) == 1 and y_train.requires_grad
+            with torch.no_grad():
+                y9 = layer(torch.randn(9, 1024, device=dev).to(torch.bfloat16))   # more than eight rows: separate term
+            assert len(calls) == 1 and y9.shape == (9, 72)
+        finally:
+            P.ops.linear_lora = orig
+        assert float((y.float() - ref).norm() / ref.norm()) < 4e-3
+        assert float((y_train.float() - ref).norm() / ref.norm()) < 8e-3
+    with pytest.raises(ValueError):
+        P.ops.linear_lora(torch.zeros(9, 1024, device=dev, dtype=torch.bfloat16), layer.packed_weight, layer.block_scales,
+                          None, 72, 1024, 32, torch.zeros(9, 8, device=dev), torch.zeros(8, 72, device=dev))

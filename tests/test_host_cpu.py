@@ -51,7 +51,7 @@ def test_pure_host_entry_points(P):
     assert lib.ojx_e8t_gemv_workspace_bytes(4, 4096, 4096) == 0
     assert lib.ojx_e8t_gemv_workspace_bytes(4, 4096, 14336) == 4 * 4 * 4096 * 4
     assert lib.ojx_e8t_gemm_workspace_bytes(2048, 4096, 4096) >= 16
-    assert ctypes.sizeof(P._cabi.GemvProblem) == 64
+    assert ctypes.sizeof(P._cabi.GemvProblem) == 88
 
 
 def test_argument_validation_needs_no_gpu(P):
