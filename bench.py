@@ -40,10 +40,15 @@ WORKLOAD = ("decode GEMV sweep, Llama-3-8B linear shapes (K->N 4096->4096, 4096-
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch from the ncu captures summarised under profiles/
 # (K=4096, N=14336, 16 matrices per launch: 234.9 MB of codes + scales, plus x and y, are the algorithmic bytes).
 NCU_TRAFFIC = {
-    "gemv_a16_kernel<1>": {"dram_bytes": 239.95e6, "algorithmic_bytes": 237.2e6, "captured_at_rows": 4,
-                           "profile": "profiles/gemv_a16_kernel_K4096_N14336_R16_M4.md"},
-    "gemv_a16_kernel<2>": {"dram_bytes": 245.26e6, "algorithmic_bytes": 244.3e6, "captured_at_rows": 16,
-                           "profile": "profiles/gemv_a16_kernel_K4096_N14336_R16_M16.md"},
+    "gemv_a16_kernel<1, 0, 1>": {"dram_bytes": 239.47e6, "algorithmic_bytes": 235.5e6, "captured_at_rows": 1,
+                                        "what": "one bf16 activation row, int8 tensor cores",
+                                        "profile": "profiles/gemv_a16_kernel_int8_K4096_N14336_R16_M1.md"},
+    "gemv_a16_kernel<1, 0, 0>": {"dram_bytes": 239.95e6, "algorithmic_bytes": 237.2e6, "captured_at_rows": 4,
+                                         "what": "2-8 activation rows, fp16 tensor cores",
+                                         "profile": "profiles/gemv_a16_kernel_K4096_N14336_R16_M4.md"},
+    "gemv_a16_kernel<2, 0, 0>": {"dram_bytes": 245.26e6, "algorithmic_bytes": 244.3e6, "captured_at_rows": 16,
+                                         "what": "9-16 activation rows, fp16 tensor cores",
+                                         "profile": "profiles/gemv_a16_kernel_K4096_N14336_R16_M16.md"},
 }
 # Llama-3-70B linear shapes (N, K) of one layer: q, k, v, o, gate, up, down
 L70 = [(8192, 8192), (1024, 8192), (1024, 8192), (8192, 8192), (28672, 8192), (28672, 8192), (8192, 28672)]
@@ -525,7 +530,8 @@ def main():
         return {key: statistics.mean(a.elapsed_time(c) for a, c in v) for key, v in pairs.items()}
     launch_ms = instrumented(max(3, args.steps // 2))
     per_kernel = {}
-    for name, rows in (("gemv_a16_kernel<1>", (1, 4)), ("gemv_a16_kernel<2>", (16,))):
+    for name, rows in (("gemv_a16_kernel<1, 0, 1>", (1,)), ("gemv_a16_kernel<1, 0, 0>", (4,)),
+                       ("gemv_a16_kernel<2, 0, 0>", (16,))):
         keys_k = [(si, b) for (si, b) in launch_ms if b in rows]
         t = sum(launch_ms[k_] for k_ in keys_k)
         algo = sum(R * (SHAPES[si][0] * SHAPES[si][1] // 4 + b * SHAPES[si][0] * 2 + b * SHAPES[si][1] * 2) // world for si, b in keys_k)
