@@ -146,19 +146,11 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
         mbar_init(bar_lut, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        if constexpr (!kI8) {
-            // the lookup table's shared-memory image arrives as ONE bulk copy while the kernel sets itself up
-            mbar_expect_tx(bar_lut, kNumPoints * 16);
-            bulk_load(lut, g_lut_f16sel, kNumPoints * 16, bar_lut);
-        }
-    }
-    if constexpr (kI8) {
-        // int8 path: 32-bit entries (eight 4-bit byte-permute selectors), every entry four times so that the four
-        // lanes of a row read four different banks
-        for (int i = tid; i < kNumPoints; i += kGemvThreads) {
-            const uint32_t v = g_trit_nibbles[i];
-            sts_u128(lut + i * 16, make_uint4(v, v, v, v));
-        }
+        // the lookup table's shared-memory image arrives as ONE bulk copy while the kernel sets itself up.  int8 path:
+        // 32-bit entries (eight 4-bit byte-permute selectors), every entry four times so that the four lanes of a row
+        // read four different banks; fp16 path: 64-bit entries, two copies
+        mbar_expect_tx(bar_lut, kNumPoints * 16);
+        bulk_load(lut, kI8 ? g_lut_i8x4 : g_lut_f16sel, kNumPoints * 16, bar_lut);
     }
     __syncthreads();
 
@@ -259,7 +251,7 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     bool xbad = false;                          // the slice holds Inf or NaN (same value in every lane of the warp)
     int cur_prob = -1, cur_chunk = -1, cur_K = 0;
 
-    if constexpr (!kI8) a16_wait(bar_lut, 0u, abort_flag, 55, peers.wait_limit);    // the table has landed
+    a16_wait(bar_lut, 0u, abort_flag, 55, peers.wait_limit);        // the table has landed
     int cstage = 0;
     uint32_t cparity = 0;
     for (int n = 0; n < nitems; ++n) {
