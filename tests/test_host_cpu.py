@@ -192,6 +192,13 @@ y = lin(torch.from_numpy(x))
 ref = O.linear_fp32(x, packed_np, scales_np, N, K, bias)
 assert tuple(y.shape) == (M, N), y.shape
 assert np.array_equal(y.numpy(), ref), "sharded result differs"
+if len(set(lin.sizes)) != 1:                    # the fused exchange needs equal shards and says so before touching a GPU
+    try:
+        lin.enable_fused_gather(torch.device("cpu"))
+    except ValueError:
+        pass
+    else:
+        raise SystemExit("ragged shards were accepted by enable_fused_gather")
 dist.barrier()
 if rank == 0:
     print("SHARD_OK", lin.sizes)
