@@ -78,6 +78,8 @@ def conway_sloane_e8_project(x: torch.Tensor, prefer_native: bool = True) -> tor
     """Snaps every 8-vector along the last dimension to the nearest point of E8 = D8 u (D8 + 1/2)
     (reference ``lattice.py:162-203``; ``prefer_native`` is accepted for signature compatibility - there is one
     implementation, the CUDA kernel)."""
+    if torch.compiler.is_compiling() and x.numel() > 0:
+        return torch.ops.ojasx_math_native.conway_sloane_e8_project_tensor(x)
     return ops.e8_project(x)
 
 
@@ -211,7 +213,11 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
         ctx.bitrate = float(bitrate)
         x_2d = x_rot.reshape(-1, in_features)
         if float(bitrate) == 2.0:
-            y_2d = ops.linear_2bit(x_2d, packed_weight, block_scales, bias, out_features, in_features, group_size)
+            if torch.compiler.is_compiling() and in_features % group_size == 0:
+                y_2d = torch.ops.ojasx_math_native.fused_e8_gemm_fwd(
+                    x_2d, packed_weight.view(out_features, -1), block_scales.view(out_features, -1), bias, group_size)
+            else:
+                y_2d = ops.linear_2bit(x_2d, packed_weight, block_scales, bias, out_features, in_features, group_size)
             return y_2d.reshape(*x_rot.shape[:-1], out_features)
         eff = ops.effective_group(group_size)
         if torch.compiler.is_compiling() and in_features % eff == 0:
@@ -229,8 +235,13 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
         gy_2d = grad_y.reshape(-1, ctx.out_features).contiguous()
         eff = ops.effective_group(ctx.group_size)
         if ctx.bitrate == 2.0:
-            w = ops.decode_2bit(packed_weight, block_scales, (ctx.out_features, ctx.in_features), ctx.x_dtype)
-            grad_x = gy_2d.to(ctx.x_dtype).matmul(w).reshape(ctx.x_shape)
+            if torch.compiler.is_compiling() and ctx.in_features % ctx.group_size == 0:
+                grad_x = torch.ops.ojasx_math_native.fused_e8_gemm_bwd_dx(
+                    gy_2d.to(ctx.x_dtype), packed_weight.view(ctx.out_features, -1), block_scales.view(ctx.out_features, -1),
+                    ctx.in_features, ctx.group_size).reshape(ctx.x_shape)
+            else:
+                w = ops.decode_2bit(packed_weight, block_scales, (ctx.out_features, ctx.in_features), ctx.x_dtype)
+                grad_x = gy_2d.to(ctx.x_dtype).matmul(w).reshape(ctx.x_shape)
         elif torch.compiler.is_compiling() and ctx.in_features % eff == 0:
             grad_x = torch.ops.ojasx_math_native.fused_ternary_e8_gemm_bwd_dx(
                 gy_2d.to(ctx.x_dtype), packed_weight.view(ctx.out_features, -1), block_scales.view(ctx.out_features, -1),

@@ -1,6 +1,7 @@
-"""``torch.ops.ojasx_math_native.fused_ternary_e8_gemm_fwd`` / ``_bwd_dx`` bound to the sm_100a kernels.
+"""``torch.ops.ojasx_math_native.fused_ternary_e8_gemm_fwd`` / ``_bwd_dx``, their 2.0-bit siblings ``fused_e8_gemm_fwd`` /
+``_bwd_dx`` and ``conway_sloane_e8_project_tensor`` bound to the sm_100a kernels.
 
-The reference registers these two operators (with these schema strings) for its native CPU module
+The reference registers these operators (with these schema strings) for its native CPU module
 (``ojasx2/math/csrc/ojasx_math_bindings.cpp:586-595``) and reaches them as attributes of ``lattice._native``
 (``ojasx2/math/lattice.py:591-608,656-681``).  Here they get a CUDA implementation (the fused decode-shape /
 tcgen05 kernels behind ``hardware.fused_ternary_e8_gemm_fwd`` and the transposed kernel behind ``_bwd_dx``), a
@@ -16,13 +17,46 @@ from typing import Optional
 
 import torch
 
-from . import hardware
+from . import hardware, ops
 
 NAMESPACE = "ojasx_math_native"
 _FWD = "fused_ternary_e8_gemm_fwd(Tensor x, Tensor packed_weight, Tensor block_scales, Tensor? bias=None, int group_size=32) -> Tensor"
 _BWD = "fused_ternary_e8_gemm_bwd_dx(Tensor grad_y, Tensor packed_weight, Tensor block_scales, int in_features, int group_size=32) -> Tensor"
 
+_FWD2 = "fused_e8_gemm_fwd(Tensor x, Tensor packed_weight, Tensor block_scales, Tensor? bias=None, int group_size=32) -> Tensor"
+_BWD2 = "fused_e8_gemm_bwd_dx(Tensor grad_y, Tensor packed_weight, Tensor block_scales, int in_features, int group_size=32) -> Tensor"
+_PROJ = "conway_sloane_e8_project_tensor(Tensor x) -> Tensor"
+
 _lib: Optional[torch.library.Library] = None
+
+
+def _fwd2_cuda(x, packed_weight, block_scales, bias=None, group_size=32):
+    # 2.0-bit operands as the reference's native module takes them: packed [N, K/4], scales [N, K/group]
+    n, k = int(packed_weight.shape[0]), int(x.shape[1])
+    return ops.linear_2bit(x, packed_weight.reshape(-1), block_scales.reshape(-1), bias, n, k, group_size)
+
+
+def _bwd2_cuda(grad_y, packed_weight, block_scales, in_features, group_size=32):
+    n = int(packed_weight.shape[0])
+    w = ops.decode_2bit(packed_weight.reshape(-1), block_scales.reshape(-1), (n, int(in_features)), grad_y.dtype)
+    return grad_y.matmul(w)
+
+
+def _proj_cuda(x):
+    return ops.e8_project(x)
+
+
+def _proj_fake(x):
+    torch._check(x.shape[-1] == 8, lambda: "Last dimension must be 8 for E8 lattice")
+    return torch.empty_like(x)
+
+
+def _backward2(ctx, grad_y):
+    packed_weight, block_scales = ctx.saved_tensors
+    grad_x = torch.ops.ojasx_math_native.fused_e8_gemm_bwd_dx(grad_y.contiguous(), packed_weight, block_scales,
+                                                              ctx.in_features, ctx.group_size)
+    grad_bias = grad_y.sum(dim=0) if ctx.has_bias else None
+    return grad_x, None, None, grad_bias, None
 
 
 def _fwd_cuda(x, packed_weight, block_scales, bias=None, group_size=32):
@@ -61,13 +95,13 @@ def _backward(ctx, grad_y):
 
 
 def register() -> bool:
-    """Defines the two operators (unless another library already did) and attaches the CUDA, fake and autograd
+    """Defines the operators (unless another library already did) and attaches the CUDA, fake and autograd
     implementations.  Idempotent; returns True when the operators are callable afterwards."""
     global _lib
     if _lib is not None:
         return True
     lib = torch.library.Library(NAMESPACE, "FRAGMENT")
-    for schema in (_FWD, _BWD):
+    for schema in (_FWD, _BWD, _FWD2, _BWD2, _PROJ):
         name = schema.split("(")[0]
         if not hasattr(getattr(torch.ops, NAMESPACE), name):
             lib.define(schema)
@@ -76,5 +110,12 @@ def register() -> bool:
     torch.library.register_fake(f"{NAMESPACE}::fused_ternary_e8_gemm_fwd", _fwd_fake, lib=lib)
     torch.library.register_fake(f"{NAMESPACE}::fused_ternary_e8_gemm_bwd_dx", _bwd_fake, lib=lib)
     torch.library.register_autograd(f"{NAMESPACE}::fused_ternary_e8_gemm_fwd", _backward, setup_context=_setup_context, lib=lib)
+    lib.impl("fused_e8_gemm_fwd", _fwd2_cuda, "CUDA")
+    lib.impl("fused_e8_gemm_bwd_dx", _bwd2_cuda, "CUDA")
+    lib.impl("conway_sloane_e8_project_tensor", _proj_cuda, "CUDA")
+    torch.library.register_fake(f"{NAMESPACE}::fused_e8_gemm_fwd", _fwd_fake, lib=lib)
+    torch.library.register_fake(f"{NAMESPACE}::fused_e8_gemm_bwd_dx", _bwd_fake, lib=lib)
+    torch.library.register_fake(f"{NAMESPACE}::conway_sloane_e8_project_tensor", _proj_fake, lib=lib)
+    torch.library.register_autograd(f"{NAMESPACE}::fused_e8_gemm_fwd", _backward2, setup_context=_setup_context, lib=lib)
     _lib = lib
     return True

@@ -144,6 +144,14 @@ def test_native_operator_schemas_and_shape_inference(P):
     ns = torch.ops.ojasx_math_native
     assert "Tensor? bias=None, int group_size=32" in str(ns.fused_ternary_e8_gemm_fwd.default._schema)
     assert "int in_features, int group_size=32" in str(ns.fused_ternary_e8_gemm_bwd_dx.default._schema)
+    assert "Tensor? bias=None, int group_size=32" in str(ns.fused_e8_gemm_fwd.default._schema)          # 2.0-bit siblings
+    assert "int in_features, int group_size=32" in str(ns.fused_e8_gemm_bwd_dx.default._schema)
+    assert str(ns.conway_sloane_e8_project_tensor.default._schema).endswith("(Tensor x) -> Tensor")
+    xm2 = torch.empty(5, 256, device="meta", dtype=torch.bfloat16)
+    y2 = ns.fused_e8_gemm_fwd(xm2, torch.empty(24, 64, device="meta", dtype=torch.uint8),
+                              torch.empty(24, 8, device="meta", dtype=torch.float16), None, 32)
+    assert tuple(y2.shape) == (5, 24) and y2.dtype == torch.bfloat16
+    assert tuple(ns.conway_sloane_e8_project_tensor(torch.empty(7, 8, device="meta")).shape) == (7, 8)
     x = torch.empty(5, 256, device="meta", dtype=torch.float16)
     pk = torch.empty(24, 48, device="meta", dtype=torch.uint8)
     sc = torch.empty(24, 8, device="meta", dtype=torch.float16)

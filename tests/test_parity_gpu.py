@@ -492,3 +492,26 @@ def test_two_bit_layer_with_reference_defaults(P, oracle):
     model = P.pack_model_e8(torch.nn.Sequential(torch.nn.Linear(64, 32), torch.nn.ReLU(), torch.nn.Linear(32, 8)).to(dev))
     assert all(isinstance(model[i], P.E8LatticeLinear) and model[i].bitrate == 2.0 for i in (0, 2))
     assert model(torch.randn(3, 64, device=dev)).shape == (3, 8)
+
+
+def test_two_bit_and_projection_operators_compile_without_graph_breaks(P, oracle):
+    """torch.ops.ojasx_math_native.fused_e8_gemm_fwd / _bwd_dx / conway_sloane_e8_project_tensor (schemas of
+    ojasx2/math/csrc/ojasx_math_bindings.cpp:586-595) carry the 2.0-bit layer and the projection through
+    torch.compile(fullgraph=True)."""
+    dev = torch.device(DEV)
+    torch.manual_seed(2)
+    layer = P.E8LatticeLinear.from_linear(torch.nn.Linear(128, 40).to(dev), group_size=32)      # 2.0 bits
+    x = torch.randn(6, 128, device=dev, requires_grad=True)
+    eager = layer(x)
+    compiled = torch.compile(layer, fullgraph=True, backend="aot_eager")
+    y = compiled(x)
+    assert torch.allclose(y, eager, atol=1e-5)
+    y.sum().backward()
+    wd = layer.unpack_weights(torch.float32)
+    assert torch.allclose(x.grad, torch.ones(6, 40, device=dev) @ wd, atol=1e-4)
+    ns = torch.ops.ojasx_math_native
+    direct = ns.fused_e8_gemm_fwd(x.detach(), layer.packed_weight.view(40, -1), layer.block_scales.view(40, -1), layer.bias, 32)
+    assert torch.allclose(direct, eager, atol=1e-5)
+    v = torch.from_numpy(oracle.gen_normal(9, 64 * 8, 1.5).reshape(64, 8)).to(dev)
+    snap = torch.compile(lambda t: P.conway_sloane_e8_project(t) * 2.0, fullgraph=True, backend="aot_eager")
+    assert np.array_equal(snap(v).cpu().numpy(), oracle.conway_sloane_project(v.cpu().numpy()) * 2.0)
