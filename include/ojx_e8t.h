@@ -132,6 +132,25 @@ int32_t ojx_e8t_linear_2bit(const void* x, int32_t x_dtype, int64_t M, const uin
                             const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype, void* stream);
 
 /*
+ * The 1.0-bit sibling format (one byte per 8 weights: the index of one of 256 vectors - the 240 roots of E8 and 16 axis
+ * vectors, doubled; weight = coordinate * scale, one fp16 least-squares scale per group; group a positive multiple of
+ * 8, anything else is replaced by 8 in the encoder, as the reference does).
+ *   ojx_e8t_encode_1bit   replaces RootE8LatticePacker.pack   (ojasx2/math/lattice.py:475-512): packed_out uint8[P/8],
+ *                         scales_out fp16[P/group].  Bit-exact with the reference's CPU path, where each entry of
+ *                         torch.matmul(v, normalize(table)^T) is a chain of fused multiply-adds over k = 0..7 and
+ *                         torch.sum adds chunks of eight into four vector accumulators in turn; a BLAS that rounds the
+ *                         8-term dot products differently may pick the other of two nearly equal candidates.
+ *   ojx_e8t_decode_1bit   replaces RootE8LatticePacker.unpack (ojasx2/math/lattice.py:514-537)
+ *   ojx_e8t_linear_1bit   y = x . W^T (+ bias) from the codes, one fused fp32 kernel (correctness path, as for 2 bits)
+ */
+int32_t ojx_e8t_encode_1bit(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
+                            uint8_t* packed_out, uint16_t* scales_out, void* stream);
+int32_t ojx_e8t_decode_1bit(const uint8_t* packed, const uint16_t* scales, int64_t rows, int64_t cols, int32_t group,
+                            int32_t out_dtype, void* out, void* stream);
+int32_t ojx_e8t_linear_1bit(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                            const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype, void* stream);
+
+/*
  * Nearest point of the E8 lattice (integer vectors with an even sum, or all of them shifted by 1/2) for
  * each of `vectors` consecutive 8-vectors.  Replaces conway_sloane_e8_project (ojasx2/math/lattice.py:162-203;
  * native form ojasx_math_core.hpp:385-425) bit for bit on fp32 input: round-half-even, first index wins the

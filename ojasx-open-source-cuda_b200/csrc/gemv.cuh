@@ -243,8 +243,9 @@ __global__ void __launch_bounds__(256, 3) gemv_reduce_kernel(const ojx_e8t_gemv_
 // Generic path: any N, K (flat packing where groups may cross rows included), any dtypes.
 // One warp per output feature; correctness path for shapes the fast kernels do not cover.
 // ---------------------------------------------------------------------------------------------
-// kTwoBit: the weights are 2-bit codes, (code - 1.5) * scale (E8LatticePacker, ojasx2/math/lattice.py:210-279).
-template <bool kTwoBit>
+// kFmt: 0 ternary (1.5 bits), 2 two-bit codes, (code - 1.5) * scale (E8LatticePacker, ojasx2/math/lattice.py:210-279),
+// 1 one byte per 8-block indexing the 256-vector table (RootE8LatticePacker, ojasx2/math/lattice.py:475-537).
+template <int kFmt>
 __global__ void __launch_bounds__(256) generic_linear_kernel(const void* __restrict__ x, int x_dtype, int64_t M,
                                                               const uint8_t* __restrict__ packed,
                                                               const uint16_t* __restrict__ scales,
@@ -261,8 +262,12 @@ __global__ void __launch_bounds__(256) generic_linear_kernel(const void* __restr
             for (int64_t k = lane; k < K; k += 32) {
                 const int64_t flat = n * K + k;
                 float w;
-                if constexpr (kTwoBit) {
+                if constexpr (kFmt == 2) {
                     w = ((float)((packed[flat >> 2] >> (2 * (int)(flat & 3))) & 3) - 1.5f) *
+                        __half2float(__ushort_as_half(scales[flat / group]));
+                } else if constexpr (kFmt == 1) {
+                    const uint32_t word = g_root_coords[2 * (int)packed[flat >> 3] + (int)((flat >> 2) & 1)];
+                    w = (float)(int)(int8_t)((word >> (8 * (int)(flat & 3))) & 0xFFu) *
                         __half2float(__ushort_as_half(scales[flat / group]));
                 } else {
                     const int64_t code_idx = flat >> 3;

@@ -186,20 +186,22 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
     int64_t warps_needed = N;
     int64_t blocks = (warps_needed * 32 + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    generic_linear_kernel<false><<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
+    generic_linear_kernel<0><<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
     return launch_status();
 }
 
-// y = x . W^T (+ bias) for 2-bit weights: the fused fp32 kernel (one warp per output feature), any shape.
-int32_t linear_2bit_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales, const void* bias,
-                         int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s) {
+// y = x . W^T (+ bias) for the 2.0-bit (bits == 2) and 1.0-bit (bits == 1) formats: the fused fp32 kernel (one warp per
+// output feature), any shape.
+int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                           const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s) {
     OJX_RETURN_IF(!x || !packed || !scales || !y, OJX_ERR_NULL);
     OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0 || group <= 0 || group % 8 != 0, OJX_ERR_SHAPE);
     OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
     int64_t blocks = (N * 32 + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    generic_linear_kernel<true><<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
+    if (bits == 2) generic_linear_kernel<2><<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
+    else generic_linear_kernel<1><<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);
     return launch_status();
 }
 

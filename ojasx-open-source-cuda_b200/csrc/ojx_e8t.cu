@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "codec.cuh"
 #include "codec2.cuh"
+#include "codec1.cuh"
 #include "e8_project.cuh"
 #include "gemv.cuh"
 #include "gemv_a16.cuh"
@@ -122,7 +123,22 @@ int32_t ojx_e8t_decode_2bit(const uint8_t* packed, const uint16_t* scales, int64
 
 int32_t ojx_e8t_linear_2bit(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                             const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype, void* stream) {
-    return ojx::linear_2bit_impl(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream);
+    return ojx::linear_lowbit_impl(2, x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_encode_1bit(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
+                            uint8_t* packed_out, uint16_t* scales_out, void* stream) {
+    return ojx::encode1_impl(w, w_dtype, rows, cols, group, packed_out, scales_out, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_decode_1bit(const uint8_t* packed, const uint16_t* scales, int64_t rows, int64_t cols, int32_t group,
+                            int32_t out_dtype, void* out, void* stream) {
+    return ojx::decode1_impl(packed, scales, rows, cols, group, out_dtype, out, (cudaStream_t)stream);
+}
+
+int32_t ojx_e8t_linear_1bit(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                            const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype, void* stream) {
+    return ojx::linear_lowbit_impl(1, x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream);
 }
 
 int32_t ojx_e8t_project(const float* x, int64_t vectors, float* out, void* stream) {

@@ -1,19 +1,23 @@
-"""Host-side mirror of the reference's ternary-E8 interface, backed by the sm_100a kernels.
+"""Host-side mirror of the reference's E8 quantized-linear interface, backed by the sm_100a kernels.
 
 Same names, argument meaning and error behaviour as the reference module
-``ojasx2/math/lattice.py`` (re-exported there as ``ojasx3.lattice``), restricted to the
-1.5-bit ternary-E8 path:
+``ojasx2/math/lattice.py`` (re-exported there as ``ojasx3.lattice``):
 
-* :class:`TernaryE8LatticePacker`   (reference ``lattice.py:335-419``)
+* :class:`TernaryE8LatticePacker`   (reference ``lattice.py:335-419``)  1.5 bits - the tensor-core path
+* :class:`E8LatticePacker`          (reference ``lattice.py:207-279``)  2.0 bits
+* :class:`RootE8LatticePacker`      (reference ``lattice.py:472-537``)  1.0 bit
 * :class:`_FusedE8GEMMFunction`     (reference ``lattice.py:548-717``)
 * :class:`E8LatticeLinear`          (reference ``lattice.py:724-846``)
 * :func:`pack_model_e8`             (reference ``lattice.py:901-945``)
 * :func:`fwht_block32`              (reference ``lattice.py:91-102``)
+* :func:`conway_sloane_e8_project`, :class:`_E8STEFunction`, :class:`E8QuantizationAwareLinear`
+                                    (reference ``lattice.py:162-203, 853-899``)
 * :func:`_get_ternary_e8_luts`      (reference ``lattice.py:292-332``)
 
 Differences, all deliberate: tensors must live on a CUDA device (the kernels are the only
-implementation; nothing falls back to CPU or to PyTorch ops), other bit-rates raise
-``NotImplementedError``, and no dense weight matrix is ever materialised in the forward pass.
+implementation; nothing falls back to CPU or to PyTorch ops), and no dense weight matrix is ever
+materialised in the forward pass (the 2.0- and 1.0-bit formats run one fused fp32 kernel instead of the
+tensor-core kernels; their backward decodes the weights).
 """
 
 from __future__ import annotations
@@ -28,16 +32,14 @@ import torch.nn.functional as F
 
 from . import ops
 
-_SUPPORTED_BITRATES = (1.5, 2.0)
+_SUPPORTED_BITRATES = (1.0, 1.5, 2.0)
 
 
 def _check_bitrate(bitrate: float) -> None:
-    """1.5 (ternary E8, the tensor-core path) and 2.0 (four codes per byte, fused fp32 kernel) are implemented.
-    The 1.0-bit root packer chooses codes by an argmax over a BLAS product whose rounding differs between
-    libraries, so its output cannot be reproduced bit for bit; it is not offered."""
+    """1.5 (ternary E8: the tensor-core path), 2.0 (four codes per byte) and 1.0 (one byte per 8-block) - the
+    latter two with bit-exact packers and a fused fp32 linear."""
     if float(bitrate) not in _SUPPORTED_BITRATES:
-        raise NotImplementedError(
-            f"bitrate={bitrate!r}: the B200 backend implements the 1.5-bit ternary-E8 and the 2.0-bit E8 formats")
+        raise ValueError(f"Unsupported E8 bitrate {bitrate!r}; expected one of {list(_SUPPORTED_BITRATES)}")
 
 
 class _Fwht32(torch.autograd.Function):
@@ -183,9 +185,34 @@ class E8LatticePacker:
         return ops.decode_2bit(packed_codes, scales, (int(shape[0]), int(shape[1])), dtype)
 
 
+class RootE8LatticePacker:
+    """1.0 bit/weight, one byte per 8-block indexing the 240 roots of E8 plus 16 axis vectors (reference
+    ``lattice.py:472-537``): same entry points; codes and scales equal the reference's CPU results bit for bit."""
+
+    @staticmethod
+    def pack(w: torch.Tensor, group_size: int = 32) -> Tuple[torch.Tensor, torch.Tensor, Tuple[int, int]]:
+        m, n = w.shape
+        src = w if w.dtype in (torch.float32, torch.float16, torch.bfloat16) else w.to(torch.float32)
+        packed, scales = ops.encode_1bit(src, group_size)
+        return packed, scales, (m, n)
+
+    @staticmethod
+    def unpack(packed_codes: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, int],
+               dtype: torch.dtype = torch.float32, use_workspace: bool = False) -> torch.Tensor:
+        del use_workspace
+        return ops.decode_1bit(packed_codes, scales, (int(shape[0]), int(shape[1])), dtype)
+
+
 def _get_packer_for_bitrate(bitrate: float):
-    _check_bitrate(bitrate)
-    return TernaryE8LatticePacker if float(bitrate) == 1.5 else E8LatticePacker
+    if float(bitrate) == 1.0:
+        return RootE8LatticePacker
+    if float(bitrate) == 1.5:
+        return TernaryE8LatticePacker
+    return E8LatticePacker                      # the reference's default branch (lattice.py:536-541)
+
+
+def _lowbit(bitrate: float) -> int:
+    return 1 if float(bitrate) == 1.0 else 2
 
 
 class _FusedE8GEMMFunction(torch.autograd.Function):
@@ -212,6 +239,9 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
         ctx.group_size = group_size
         ctx.bitrate = float(bitrate)
         x_2d = x_rot.reshape(-1, in_features)
+        if float(bitrate) == 1.0:
+            y_2d = ops.linear_1bit(x_2d, packed_weight, block_scales, bias, out_features, in_features, group_size)
+            return y_2d.reshape(*x_rot.shape[:-1], out_features)
         if float(bitrate) == 2.0:
             if torch.compiler.is_compiling() and in_features % group_size == 0:
                 y_2d = torch.ops.ojasx_math_native.fused_e8_gemm_fwd(
@@ -234,7 +264,10 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
         packed_weight, block_scales = ctx.saved_tensors
         gy_2d = grad_y.reshape(-1, ctx.out_features).contiguous()
         eff = ops.effective_group(ctx.group_size)
-        if ctx.bitrate == 2.0:
+        if ctx.bitrate == 1.0:
+            w = ops.decode_1bit(packed_weight, block_scales, (ctx.out_features, ctx.in_features), ctx.x_dtype)
+            grad_x = gy_2d.to(ctx.x_dtype).matmul(w).reshape(ctx.x_shape)
+        elif ctx.bitrate == 2.0:
             if torch.compiler.is_compiling() and ctx.in_features % ctx.group_size == 0:
                 grad_x = torch.ops.ojasx_math_native.fused_e8_gemm_bwd_dx(
                     gy_2d.to(ctx.x_dtype), packed_weight.view(ctx.out_features, -1), block_scales.view(ctx.out_features, -1),
@@ -277,7 +310,7 @@ class E8LatticeLinear(nn.Module):
             num_bytes, num_scales = ops.packed_sizes(out_features, in_features, eff_group)
         else:
             eff_group = group_size if (group_size >= 8 and group_size % 8 == 0) else 8
-            num_bytes, num_scales = ops.packed_sizes_2bit(out_features, in_features, eff_group)
+            num_bytes, num_scales = ops.packed_sizes_lowbit(_lowbit(self.bitrate), out_features, in_features, eff_group)
         self.group_size = eff_group
         self.register_buffer("packed_weight", torch.zeros(num_bytes, dtype=torch.uint8, device=device))
         self.register_buffer("block_scales", torch.ones(num_scales, dtype=torch.float16, device=device))
@@ -303,7 +336,7 @@ class E8LatticeLinear(nn.Module):
                 lora_alpha=lora_alpha, group_size=eff_gs, bitrate=bitrate, use_hadamard=use_hadamard,
                 device=linear.weight.device, dtype=linear.weight.dtype)
         with torch.no_grad():
-            encode = ops.encode if m.bitrate == 1.5 else ops.encode_2bit
+            encode = ops.encode if m.bitrate == 1.5 else (ops.encode_1bit if m.bitrate == 1.0 else ops.encode_2bit)
             encode(linear.weight, m.group_size, out=(m.packed_weight, m.block_scales), hadamard=m.use_hadamard)
             if linear.bias is not None:
                 m.bias.copy_(linear.bias)

@@ -91,23 +91,35 @@ def fwht32(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     return res
 
 
-def packed_sizes_2bit(rows: int, cols: int, group_size: int) -> Tuple[int, int]:
+def _lowbit_group(bits: int, group_size: int) -> int:
+    """Group size as the reference's packers treat it: the 2.0-bit packer raises for anything that is not a positive
+    multiple of 8 (``lattice.py:219-220``), the 1.0-bit packer replaces it by 8 (``lattice.py:485-486``)."""
     if group_size <= 0 or group_size % 8 != 0:
-        raise ValueError(f"group_size ({group_size}) must be a positive multiple of 8.")
+        if bits == 2:
+            raise ValueError(f"group_size ({group_size}) must be a positive multiple of 8.")
+        return 8
+    return int(group_size)
+
+
+def packed_sizes_lowbit(bits: int, rows: int, cols: int, group_size: int) -> Tuple[int, int]:
+    """(code bytes, scales) of the 2.0-bit (four codes per byte) or 1.0-bit (one byte per eight weights) format."""
+    g = _lowbit_group(bits, group_size)
     total = rows * cols
-    padded = total + ((-total) % group_size)
-    return padded // 4, padded // group_size
+    padded = total + ((-total) % g)
+    return (padded // 4 if bits == 2 else padded // 8), padded // g
 
 
-def encode_2bit(w: torch.Tensor, group_size: int = 8, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                hadamard: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``w`` [rows, cols] -> (packed uint8[P/4], scales fp16[P/g]) in the 2.0-bit format; bit-exact with the
-    reference's ``E8LatticePacker.pack`` (``ojasx2/math/lattice.py:210-248``)."""
+def packed_sizes_2bit(rows: int, cols: int, group_size: int) -> Tuple[int, int]:
+    return packed_sizes_lowbit(2, rows, cols, group_size)
+
+
+def _encode_lowbit(bits: int, w: torch.Tensor, group_size: int, out, hadamard: bool) -> Tuple[torch.Tensor, torch.Tensor]:
     if w.dim() != 2:
         raise ValueError(f"expected a 2-D weight, got shape {tuple(w.shape)}")
     dev = _require_cuda(w)
     rows, cols = int(w.shape[0]), int(w.shape[1])
-    nbytes, nscales = packed_sizes_2bit(rows, cols, group_size)
+    g = _lowbit_group(bits, group_size)
+    nbytes, nscales = packed_sizes_lowbit(bits, rows, cols, g)
     if rows == 0 or cols == 0:
         raise ValueError("empty weight")
     wc = w.detach().contiguous()
@@ -121,31 +133,29 @@ def encode_2bit(w: torch.Tensor, group_size: int = 8, out: Optional[Tuple[torch.
         if packed.numel() != nbytes or scales.numel() != nscales or packed.dtype != torch.uint8 \
                 or scales.dtype != torch.float16 or not packed.is_contiguous() or not scales.is_contiguous():
             raise ValueError("output buffers have the wrong size, dtype or layout")
+    name = "ojx_e8t_encode_2bit" if bits == 2 else "ojx_e8t_encode_1bit"
     with torch.cuda.device(dev):
-        st = _cabi.lib().ojx_e8t_encode_2bit(wc.data_ptr(), _dtype_code(wc.dtype), rows, cols, int(group_size),
-                                             packed.data_ptr(), scales.data_ptr(), _stream_ptr(dev))
-    _cabi.check(st, "ojx_e8t_encode_2bit")
+        st = getattr(_cabi.lib(), name)(wc.data_ptr(), _dtype_code(wc.dtype), rows, cols, g, packed.data_ptr(),
+                                        scales.data_ptr(), _stream_ptr(dev))
+    _cabi.check(st, name)
     return packed, scales
 
 
-def decode_2bit(packed: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, int],
-                dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """2-bit codes + scales -> dense [rows, cols] in ``dtype``; the group size is inferred from the buffer sizes
-    as the reference does (``ojasx2/math/lattice.py:262-264``)."""
+def _decode_lowbit(bits: int, packed: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, int], dtype: torch.dtype) -> torch.Tensor:
     dev = _require_cuda(packed, scales)
     rows, cols = int(shape[0]), int(shape[1])
-    group = (packed.numel() * 4) // max(1, scales.numel())
+    group = (packed.numel() * (4 if bits == 2 else 8)) // max(1, scales.numel())
     out = torch.empty((rows, cols), dtype=dtype, device=dev)
+    name = "ojx_e8t_decode_2bit" if bits == 2 else "ojx_e8t_decode_1bit"
     with torch.cuda.device(dev):
-        st = _cabi.lib().ojx_e8t_decode_2bit(packed.contiguous().data_ptr(), scales.contiguous().data_ptr(), rows, cols,
-                                             group, _dtype_code(dtype), out.data_ptr(), _stream_ptr(dev))
-    _cabi.check(st, "ojx_e8t_decode_2bit")
+        st = getattr(_cabi.lib(), name)(packed.contiguous().data_ptr(), scales.contiguous().data_ptr(), rows, cols, group,
+                                        _dtype_code(dtype), out.data_ptr(), _stream_ptr(dev))
+    _cabi.check(st, name)
     return out
 
 
-def linear_2bit(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor], n: int, k: int,
-                group_size: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``y = x . W^T (+ bias)`` from 2-bit codes in one fused fp32 kernel."""
+def _linear_lowbit(bits: int, x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
+                   n: int, k: int, group_size: int, out_dtype: Optional[torch.dtype]) -> torch.Tensor:
     dev = _require_cuda(x, packed, scales)
     x2 = x.detach().reshape(-1, k).contiguous()
     m = int(x2.shape[0])
@@ -153,12 +163,52 @@ def linear_2bit(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bia
     if m == 0:
         return y
     b = None if bias is None else bias.detach().to(x2.dtype).contiguous()
+    name = "ojx_e8t_linear_2bit" if bits == 2 else "ojx_e8t_linear_1bit"
     with torch.cuda.device(dev):
-        st = _cabi.lib().ojx_e8t_linear_2bit(x2.data_ptr(), _dtype_code(x2.dtype), m, packed.data_ptr(), scales.data_ptr(),
-                                             None if b is None else b.data_ptr(), n, k, int(group_size), y.data_ptr(),
-                                             _dtype_code(y.dtype), _stream_ptr(dev))
-    _cabi.check(st, "ojx_e8t_linear_2bit")
+        st = getattr(_cabi.lib(), name)(x2.data_ptr(), _dtype_code(x2.dtype), m, packed.data_ptr(), scales.data_ptr(),
+                                        None if b is None else b.data_ptr(), n, k, int(group_size), y.data_ptr(),
+                                        _dtype_code(y.dtype), _stream_ptr(dev))
+    _cabi.check(st, name)
     return y
+
+
+def encode_2bit(w: torch.Tensor, group_size: int = 8, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                hadamard: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``w`` [rows, cols] -> (packed uint8[P/4], scales fp16[P/g]) in the 2.0-bit format; bit-exact with the
+    reference's ``E8LatticePacker.pack`` (``ojasx2/math/lattice.py:210-248``)."""
+    return _encode_lowbit(2, w, group_size, out, hadamard)
+
+
+def decode_2bit(packed: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, int],
+                dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """2-bit codes + scales -> dense [rows, cols] in ``dtype``; the group size is inferred from the buffer sizes
+    as the reference does (``ojasx2/math/lattice.py:262-264``)."""
+    return _decode_lowbit(2, packed, scales, shape, dtype)
+
+
+def linear_2bit(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor], n: int, k: int,
+                group_size: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``y = x . W^T (+ bias)`` from 2-bit codes in one fused fp32 kernel."""
+    return _linear_lowbit(2, x, packed, scales, bias, n, k, group_size, out_dtype)
+
+
+def encode_1bit(w: torch.Tensor, group_size: int = 32, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                hadamard: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``w`` [rows, cols] -> (packed uint8[P/8], scales fp16[P/g]) in the 1.0-bit format; bit-exact with the
+    reference's ``RootE8LatticePacker.pack`` on its CPU path (``ojasx2/math/lattice.py:475-512``)."""
+    return _encode_lowbit(1, w, group_size, out, hadamard)
+
+
+def decode_1bit(packed: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, int],
+                dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Root codes + scales -> dense [rows, cols] in ``dtype`` (``ojasx2/math/lattice.py:514-537``)."""
+    return _decode_lowbit(1, packed, scales, shape, dtype)
+
+
+def linear_1bit(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor], n: int, k: int,
+                group_size: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``y = x . W^T (+ bias)`` from root codes in one fused fp32 kernel."""
+    return _linear_lowbit(1, x, packed, scales, bias, n, k, group_size, out_dtype)
 
 
 def _fp32_pass(x: torch.Tensor, name: str, vectors: bool) -> torch.Tensor:

@@ -44,11 +44,11 @@ def _validate_row_layout(out_features: int, in_features: int, bitrate: float, gr
 
 def _encoder_for(bitrate: float):
     _check_bitrate(bitrate)
-    return ops.encode if float(bitrate) == 1.5 else ops.encode_2bit
+    return {1.0: ops.encode_1bit, 1.5: ops.encode, 2.0: ops.encode_2bit}[float(bitrate)]
 
 
 def _bytes_per_row(in_features: int, bitrate: float) -> int:
-    return in_features * 3 // 16 if float(bitrate) == 1.5 else in_features // 4
+    return {1.0: in_features // 8, 1.5: in_features * 3 // 16, 2.0: in_features // 4}[float(bitrate)]
 
 
 def _pack_row_block(block: torch.Tensor, bitrate: float, group_size: int, use_hadamard: bool

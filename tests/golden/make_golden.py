@@ -217,6 +217,27 @@ def main():
         arrays[f"two_bit/{tag}/decoded"] = L.E8LatticePacker.unpack(p2, s2, tuple(wt.shape), dtype=torch.float32).numpy()
         print("two_bit", tag, sha(p2.numpy())[:16])
 
+    # 1.0-bit root packer (lattice.py:472-537): two group sizes, a quarter-integer grid (many equal dot products: the
+    # first maximum must win) and a sparse input with all-zero blocks
+    sparse = np.zeros((16, 64), dtype=np.float32)
+    sparse[1, :8] = 1.0
+    sparse[2, 5] = -3.0
+    sparse[3, 8:16] = O.gen_normal(123, 8, 1.0)
+    one = {
+        "g32": (torch.from_numpy(O.gen_normal(120, 48 * 256, 0.02).reshape(48, 256).copy()), 32),
+        "g8": (torch.from_numpy(O.gen_normal(121, 33 * 100, 1.0).reshape(33, 100).copy()), 8),
+        "grid": (torch.from_numpy((np.rint(O.gen_normal(122, 32 * 128, 2.0)) * 0.25).astype(np.float32).reshape(32, 128).copy()), 32),
+        "sparse": (torch.from_numpy(sparse), 32),
+    }
+    for tag, (wt, g) in one.items():
+        p1, s1, _ = L.RootE8LatticePacker.pack(wt, group_size=g)
+        arrays[f"one_bit/{tag}/input"] = wt.numpy()
+        arrays[f"one_bit/{tag}/group"] = np.int64(g)
+        arrays[f"one_bit/{tag}/packed"] = p1.numpy()
+        arrays[f"one_bit/{tag}/scales"] = s1.view(torch.int16).numpy().view(np.uint16)
+        arrays[f"one_bit/{tag}/decoded"] = L.RootE8LatticePacker.unpack(p1, s1, tuple(wt.shape), dtype=torch.float32).numpy()
+        print("one_bit", tag, sha(p1.numpy())[:16])
+
     # decode of every code: all 3281 ranks (padded to an even count) with unit scales
     ranks = np.arange(3282, dtype=np.int64) % 3281
     packed_all = O.pack_codes(ranks)

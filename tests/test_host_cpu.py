@@ -95,8 +95,10 @@ def test_layer_buffers_and_errors_on_cpu(P):
     two = P.E8LatticeLinear(64, 8)                     # the reference's defaults: 2.0 bits, groups of 8
     assert two.bitrate == 2.0 and two.group_size == 8
     assert two.packed_weight.numel() == 64 * 8 // 4 and two.block_scales.numel() == 64 * 8 // 8
-    with pytest.raises(NotImplementedError):
-        P.E8LatticeLinear(64, 8, bitrate=1.0)          # the root packer is not offered
+    one = P.E8LatticeLinear(64, 8, bitrate=1.0, group_size=32)
+    assert one.packed_weight.numel() == 64 * 8 // 8 and one.block_scales.numel() == 64 * 8 // 32
+    with pytest.raises(ValueError):
+        P.E8LatticeLinear(64, 8, bitrate=3.0)
     with pytest.raises(RuntimeError):
         layer(torch.zeros(1, 128))                     # CPU tensors: the CUDA path is the only path
     with pytest.raises(ValueError):

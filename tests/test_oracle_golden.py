@@ -206,3 +206,19 @@ def test_two_bit_oracle_against_reference_outputs(golden, oracle):
         assert set(np.unique(vals)).issubset({-1.5, -0.5, 0.5, 1.5})
     with pytest.raises(ValueError):
         oracle.encode_2bit(np.zeros((2, 8), dtype=np.float32), 12)
+
+
+def test_one_bit_oracle_against_reference_outputs(golden, oracle):
+    """encode_1bit / decode_1bit restate RootE8LatticePacker (ojasx2/math/lattice.py:472-537); the golden file holds
+    the reference's own codes, least-squares scales and decoded weights, ties and all-zero blocks included."""
+    _, arrays = golden
+    table = oracle.root_e8_table()
+    assert table.shape == (256, 8) and len({tuple(r) for r in table}) == 256
+    assert np.all((table * table).sum(axis=1)[:240] == 8) and np.all((table * table).sum(axis=1)[240:] == 4)
+    for tag in ("g32", "g8", "grid", "sparse"):
+        w, g = arrays[f"one_bit/{tag}/input"], int(arrays[f"one_bit/{tag}/group"])
+        p, s, shape = oracle.encode_1bit(w, g)
+        assert shape == w.shape
+        assert np.array_equal(p, arrays[f"one_bit/{tag}/packed"]), tag
+        assert np.array_equal(s.view(np.uint16), arrays[f"one_bit/{tag}/scales"]), tag
+        assert np.array_equal(oracle.decode_1bit(p, s, w.shape), arrays[f"one_bit/{tag}/decoded"]), tag

@@ -273,8 +273,8 @@ def test_module_forward_backward_and_state(P, oracle):
     # group_size below 16 is coerced to 16, other bit-rates are refused
     small = P.E8LatticeLinear.from_linear(torch.nn.Linear(64, 8).to(dev), bitrate=1.5, group_size=8)
     assert small.group_size == 16
-    with pytest.raises(NotImplementedError):
-        P.E8LatticeLinear(64, 8, bitrate=1.0)
+    with pytest.raises(ValueError):
+        P.E8LatticeLinear(64, 8, bitrate=3.0)
 
 
 def test_seam_signature_and_errors(P):
@@ -515,3 +515,50 @@ def test_two_bit_and_projection_operators_compile_without_graph_breaks(P, oracle
     v = torch.from_numpy(oracle.gen_normal(9, 64 * 8, 1.5).reshape(64, 8)).to(dev)
     snap = torch.compile(lambda t: P.conway_sloane_e8_project(t) * 2.0, fullgraph=True, backend="aot_eager")
     assert np.array_equal(snap(v).cpu().numpy(), oracle.conway_sloane_project(v.cpu().numpy()) * 2.0)
+
+
+@pytest.mark.parametrize("rows,cols,group,sigma,dtype", [(64, 256, 32, 0.02, "f32"), (33, 100, 8, 1.0, "f32"),
+                                                         (128, 512, 32, 0.02, "f16"), (16, 256, 64, 0.5, "bf16"),
+                                                         (7, 13, 16, 0.3, "f32"), (40, 64, 24, 2.0, "f32"),
+                                                         (64, 256, 128, 1.0, "f32"), (256, 4096, 32, 0.02, "bf16")])
+def test_one_bit_packer_matches_oracle_bits(P, oracle, rows, cols, group, sigma, dtype):
+    """ojx_e8t_encode_1bit / ojx_e8t_decode_1bit against the restatement of RootE8LatticePacker
+    (ojasx2/math/lattice.py:472-537), which the golden vectors pin to the reference: codes, least-squares scales
+    and decoded weights bit for bit, every group size (one that is not a multiple of 8 becomes 8), padded tails."""
+    dev = torch.device(DEV)
+    w = torch.from_numpy(oracle.gen_normal(700 + rows, rows * cols, sigma).reshape(rows, cols).copy()).to(TD[dtype])
+    want_p, want_s, _ = oracle.encode_1bit(w.float().numpy(), group)
+    got_p, got_s, shape = P.RootE8LatticePacker.pack(w.to(dev), group_size=group)
+    assert shape == (rows, cols)
+    assert np.array_equal(got_p.cpu().numpy(), want_p)
+    assert np.array_equal(got_s.view(torch.int16).cpu().numpy(), want_s.view(np.int16))
+    dec = P.RootE8LatticePacker.unpack(got_p, got_s, (rows, cols), dtype=torch.float32).cpu().numpy()
+    assert np.array_equal(dec.view(np.uint32), oracle.decode_1bit(want_p, want_s, (rows, cols)).view(np.uint32))
+    odd_p, odd_s, _ = P.RootE8LatticePacker.pack(w.to(dev), group_size=12)          # replaced by 8, as the reference does
+    ref_p, ref_s, _ = oracle.encode_1bit(w.float().numpy(), 12)
+    assert np.array_equal(odd_p.cpu().numpy(), ref_p) and odd_s.numel() == ref_s.size
+
+
+def test_one_bit_golden_ties_and_layer(P, golden, oracle):
+    _, arrays = golden
+    dev = torch.device(DEV)
+    for tag in ("g32", "g8", "grid", "sparse"):
+        w = torch.from_numpy(arrays[f"one_bit/{tag}/input"]).to(dev)
+        g = int(arrays[f"one_bit/{tag}/group"])
+        p, s, _ = P.RootE8LatticePacker.pack(w, group_size=g)
+        assert np.array_equal(p.cpu().numpy(), arrays[f"one_bit/{tag}/packed"]), tag
+        assert np.array_equal(s.view(torch.int16).cpu().numpy().view(np.uint16), arrays[f"one_bit/{tag}/scales"]), tag
+        d = P.RootE8LatticePacker.unpack(p, s, tuple(w.shape), dtype=torch.float32).cpu().numpy()
+        assert np.array_equal(d, arrays[f"one_bit/{tag}/decoded"]), tag
+    torch.manual_seed(4)
+    lin = torch.nn.Linear(256, 48, bias=True).to(dev)
+    layer = P.E8LatticeLinear.from_linear(lin, rank=2, bitrate=1.0, group_size=32)
+    wd = layer.unpack_weights(torch.float32)
+    x = torch.randn(5, 256, device=dev, requires_grad=True)
+    y = layer(x)
+    assert torch.allclose(y, x.detach() @ wd.t() + lin.bias.detach(), atol=1e-4)
+    y.sum().backward()
+    assert torch.allclose(x.grad, torch.ones(5, 48, device=dev) @ wd, atol=1e-4)
+    rp, rs = P.pack_weight_rowwise(lin.weight.detach(), bitrate=1.0, group_size=32, row_block=5)
+    wp, ws = P.ops.encode_1bit(lin.weight.detach(), 32)
+    assert torch.equal(rp, wp) and torch.equal(rs, ws)
