@@ -832,6 +832,17 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
         two["linear_4096x4096_1row"] = {"ms": ms, "packed_GBps": nl * 4096 * (0.25 + 2.0 / 32) / (ms * 1e-3) / 1e9}
         out["two_bit"] = two
         del p2, s2
+        # the 1.0-bit root format: packer (argmax over 256 candidate vectors per 8 weights) and unpacker, groups of 32
+        p1 = torch.empty(n * k // 8, dtype=torch.uint8, device=dev)
+        s1 = torch.empty(n * k // 32, dtype=torch.float16, device=dev)
+        bpw1 = 2.0 + 0.125 + 2.0 / 32
+        one = {"rows": n, "cols": k, "dtype": "f16", "group": 32}
+        ms = timed(lambda: ops.encode_1bit(w, 32, out=(p1, s1)), 3)
+        one["encode"] = {"ms": ms, "GBps": n * k * bpw1 / (ms * 1e-3) / 1e9, "frac_hbm": n * k * bpw1 / (ms * 1e-3) / 1e9 / hbm_peak}
+        ms = timed(lambda: ops.decode_1bit(p1, s1, (n, k), torch.float16), 3)
+        one["decode"] = {"ms": ms, "GBps": n * k * bpw1 / (ms * 1e-3) / 1e9, "frac_hbm": n * k * bpw1 / (ms * 1e-3) / 1e9 / hbm_peak}
+        out["one_bit"] = one
+        del p1, s1
         ops.encode(w, 32, out=(pk, sc))
         # decoder (unpack): packed codes + scales -> dense fp16 weights, 0.25 B read + 2 B written per weight
         ms = timed(lambda: ops.decode(pk, sc, (n, k), torch.float16, out=w), 3)
