@@ -830,6 +830,22 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
         nl = 4096
         ms = timed(lambda: ops.linear_2bit(x1, p2[: nl * 4096 // 4], s2[: nl * 4096 // 32], None, nl, 4096, 32), 5)
         two["linear_4096x4096_1row"] = {"ms": ms, "packed_GBps": nl * 4096 * (0.25 + 2.0 / 32) / (ms * 1e-3) / 1e9}
+        # four distinct 14336 x 4096 matrices back to back (cold weights), one and four activation rows
+        for rows_x in (1, 4):
+            xr = ops.generate(rows_x * 4096, 9, 1.0, torch.bfloat16, dev).view(rows_x, 4096)
+            per = 14336 * 4096
+            def four():
+                for j in range(4):
+                    ops.linear_2bit(xr, p2[j * per // 4: (j + 1) * per // 4], s2[j * per // 32: (j + 1) * per // 32], None, 14336, 4096, 32)
+            four()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()                      # replayed from a graph: the host wrapper costs more than the kernel
+            with torch.cuda.graph(graph):
+                four()
+            ms = timed(graph.replay, 3) / 4
+            del graph
+            gbs = per * (0.25 + 2.0 / 32) / (ms * 1e-3) / 1e9
+            two[f"linear_14336x4096_{rows_x}row"] = {"ms": ms, "packed_GBps": gbs, "frac_hbm": gbs / hbm_peak}
         out["two_bit"] = two
         del p2, s2
         # the 1.0-bit root format: packer (argmax over 256 candidate vectors per 8 weights) and unpacker, groups of 32

@@ -7,6 +7,7 @@
 
 #include "gemv.cuh"
 #include "gemv_a16.cuh"
+#include "gemv_lowbit.cuh"
 
 namespace ojx {
 
@@ -190,6 +191,37 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
     return launch_status();
 }
 
+// Routes a low-bit decode-shape linear to lowbit_gemv_kernel when its shared-memory image of x fits; returns false when
+// the caller has to use the generic kernel.
+template <int kFmt>
+static bool launch_lowbit_gemv(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                               const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s,
+                               int32_t* status) {
+    const size_t smem = lowbit_smem_bytes(M, K, kFmt);
+    if (M < 1 || M > 8 || K % 16 != 0 || K > (1 << 24) || N >= (1 << 30) || smem > 200 * 1024 ||
+        (reinterpret_cast<uintptr_t>(packed) & 3) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+        return false;
+    const int sms = num_sms();
+    const int per_sm = (int)((220 * 1024) / (smem + 1024)) < 1 ? 1 : (int)((220 * 1024) / (smem + 1024));
+    int64_t blocks = (N + 31) / 32;                           // at least four weight rows per warp: every CTA stages x once
+    const int64_t cap = (int64_t)sms * (per_sm > 8 ? 8 : per_sm);
+    if (blocks > cap) blocks = cap;
+    int shift = -1;
+    for (int b = 3; b < 20; ++b)
+        if ((1 << b) == group) shift = b;
+    auto run = [&](auto kernel, std::atomic<uint64_t>& done) {
+        *status = ensure_dynamic_smem(kernel, 200 * 1024, done);
+        if (*status != OJX_OK) return;
+        kernel<<<(unsigned)blocks, 256, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, group, shift, y, y_dtype);
+        *status = launch_status();
+    };
+    static std::atomic<uint64_t> done1{0}, done4{0}, done8{0};
+    if (M == 1) run(lowbit_gemv_kernel<kFmt, 1>, done1);
+    else if (M <= 4) run(lowbit_gemv_kernel<kFmt, 4>, done4);
+    else run(lowbit_gemv_kernel<kFmt, 8>, done8);
+    return true;
+}
+
 // y = x . W^T (+ bias) for the 2.0-bit (bits == 2) and 1.0-bit (bits == 1) formats: the fused fp32 kernel (one warp per
 // output feature), any shape.
 int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
@@ -198,6 +230,10 @@ int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, cons
     OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0 || group <= 0 || group % 8 != 0, OJX_ERR_SHAPE);
     OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
+    int32_t st = OJX_OK;                                      // small batches: the shared-memory kernel when x fits
+    if (bits == 2 ? launch_lowbit_gemv<2>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, s, &st)
+                  : launch_lowbit_gemv<1>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, s, &st))
+        return st;
     int64_t blocks = (N * 32 + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     if (bits == 2) generic_linear_kernel<2><<<(unsigned)blocks, 256, 0, s>>>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype);

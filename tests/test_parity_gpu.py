@@ -562,3 +562,27 @@ def test_one_bit_golden_ties_and_layer(P, golden, oracle):
     rp, rs = P.pack_weight_rowwise(lin.weight.detach(), bitrate=1.0, group_size=32, row_block=5)
     wp, ws = P.ops.encode_1bit(lin.weight.detach(), 32)
     assert torch.equal(rp, wp) and torch.equal(rs, ws)
+
+
+@pytest.mark.parametrize("bits", [2, 1])
+@pytest.mark.parametrize("m,k,n,group,dt", [(1, 4096, 4096, 32, torch.bfloat16), (3, 256, 40, 8, torch.float16),
+                                             (8, 4096, 96, 64, torch.bfloat16), (1, 14336, 64, 32, torch.float32),
+                                             (2, 1024, 33, 16, torch.bfloat16), (9, 512, 24, 32, torch.bfloat16)])
+def test_low_bit_decode_linear_matches_dense_product(P, oracle, bits, m, k, n, group, dt):
+    """ojx_e8t_linear_2bit / _1bit at decode shapes (the shared-memory kernel for up to eight rows, the generic kernel
+    beyond) against the fp32 product with the decoded weights: fp32 accumulation of exact products, so the error stays
+    within 1e-5 of sum |x||w| per output."""
+    dev = torch.device(DEV)
+    w = torch.from_numpy(oracle.gen_normal(900 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
+    enc, dec, lin = ((P.ops.encode_2bit, P.ops.decode_2bit, P.ops.linear_2bit) if bits == 2
+                     else (P.ops.encode_1bit, P.ops.decode_1bit, P.ops.linear_1bit))
+    pk, sc = enc(w, group)
+    wd = dec(pk, sc, (n, k), torch.float32)
+    x = torch.from_numpy(oracle.gen_normal(901 + m, m * k, 1.0).reshape(m, k).copy()).to(dt).to(dev)
+    bias = torch.from_numpy(oracle.gen_normal(902, n, 0.1).copy()).to(dt).to(dev)
+    y = lin(x, pk, sc, bias, n, k, group, out_dtype=torch.float32)
+    ref = x.float() @ wd.t() + bias.float()
+    budget = x.float().abs() @ wd.abs().t() + bias.float().abs()
+    assert float(((y - ref).abs() / budget).max()) < 1e-5
+    y16 = lin(x, pk, sc, None, n, k, group)
+    assert y16.dtype == dt and float((y16.float() - (ref - bias.float())).abs().max()) <= 2.0 ** -7 * float(ref.abs().max()) + 1e-3
