@@ -347,7 +347,7 @@ def main():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
                     help="N > 1: kernels store their column shard into every rank's output window (fused), NCCL all-gather "
                          "per launch, or no exchange at all (sharded compute only, for attribution)")
-    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "gemm_dx", "encode", "decode", "project"],
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "gemm_dx", "encode", "decode", "project", "linear_2bit", "linear_1bit"],
                     help="run a few launches of ONE kernel on a small case and exit (used for ncu captures)")
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--N", type=int, default=4096)
@@ -699,6 +699,18 @@ def run_case(args):
         sc = torch.empty(n * k // 32, dtype=torch.float16, device=dev)
         fn = lambda: ops.encode(w, 32, out=(pk, sc))
         info["bytes_per_launch"] = n * k * 2.25
+    elif args.case in ("linear_2bit", "linear_1bit"):           # low-bit decode-shape linear, `rotation` cold matrices per timing
+        enc, lin = (ops.encode_2bit, ops.linear_2bit) if args.case == "linear_2bit" else (ops.encode_1bit, ops.linear_1bit)
+        mats = []
+        for r in range(args.rotation):
+            ops.generate(n * k, 100 + r, 0.02, torch.float16, dev, out=w.view(-1))
+            mats.append(enc(w, 32))
+        x = ops.generate(m * k, 7, 1.0, torch.bfloat16, dev).view(m, k)
+
+        def fn():
+            for pk, sc in mats:
+                lin(x, pk, sc, None, n, k, 32)
+        info["bytes_per_launch"] = args.rotation * n * k * ((0.25 if args.case == "linear_2bit" else 0.125) + 2.0 / 32)
     elif args.case == "project":                                # nearest E8 point of N*K/8 fp32 8-vectors: 4 B in + 4 B out per value
         v = ops.generate(n * k, 60, 1.0, torch.float32, dev).view(-1, 8)
         fn = lambda: ops.e8_project(v)

@@ -121,8 +121,9 @@ int32_t ojx_e8t_fwht32(const void* x, int32_t dtype, int64_t count, void* out, v
  *   ojx_e8t_linear_2bit   y[M, N] = x[M, K] . W^T (+ bias) from the packed codes in one fp32 kernel (any shape,
  *                         any of the three dtypes for x, bias (x's dtype) and y); replaces the 2.0-bit branch of
  *                         _FusedE8GEMMFunction.forward (ojasx2/math/lattice.py:596-624) and the native
- *                         fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444).  This is a correctness path:
- *                         the tensor-core kernels of this library serve the 1.5-bit format only.
+ *                         fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444).  Up to eight rows with
+ *                         K % 16 == 0 and 16-byte aligned x run a shared-memory decode kernel, everything else a
+ *                         scalar kernel; the tensor-core kernels of this library serve the 1.5-bit format only.
  */
 int32_t ojx_e8t_encode_2bit(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
                             uint8_t* packed_out, uint16_t* scales_out, void* stream);

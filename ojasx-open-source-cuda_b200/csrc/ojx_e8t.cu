@@ -67,7 +67,7 @@ uint32_t& wait_limit_override() {
 
 extern "C" {
 
-int32_t ojx_e8t_version(void) { return 200; }
+int32_t ojx_e8t_version(void) { return 300; }
 
 const char* ojx_e8t_status_string(int32_t st) {
     switch (st) {
