@@ -1,0 +1,257 @@
+// Decode GEMV for the 2.0-bit format and ONE activation row on int8 tensor cores, with no lookup table at all.
+//
+//   y[n] = sum over scale groups of  scale[n, g] * ( sum_k code[n,k] x[k]  -  1.5 * sum_k x[k] )      (+ bias)
+//
+// Replaces the 2.0-bit branch of _FusedE8GEMMFunction.forward (ojasx2/math/lattice.py:596-624) and the native
+// fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444) for one row, group size 32, K % 2048 == 0.
+//
+// Why this format is cheap: a 32-bit word holds sixteen 2-bit codes, and (word >> 2t) & 0x03030303, t = 0..3, ARE four
+// int8 operand registers of mma.sync.m16n8k32 (codes t, 4+t, 8+t, 12+t in the four bytes) - seven shift/mask
+// operations per sixteen weights, no table, no permute.  The order of k inside an MMA does not matter as long as the
+// activation operand uses the same order, and a word never crosses a scale group.
+//
+// Work decomposition: a CTA of 8 warps takes tiles of 16 weight rows; the 256-wide rounds of K are dealt to the warps
+// in turn (round r to warp r mod 8), so one tile's codes are read by all eight warps at once, 64 contiguous bytes per
+// row and round, straight from global memory into registers (three rounds in flight per warp; no shared-memory ring is
+// needed because nothing is shared between rows).  Lane (g, t) owns rows g and g + 8 and the 64 codes 64t..64t+63 of
+// the round (two scale groups); its eight steps (word q = 0..3, register pair p = 0, 1) feed two MMAs each.
+//
+// Activations: 28-bit fixed point per scale group exactly as in the ternary one-row kernel (gemv_a16.cuh, kI8): the
+// group's largest finite magnitude fixes the exponent, the integers are split into four base-128 digits; accumulator
+// column 2t' + h takes digits 2h, 2h + 1 of the group that lane quarter t' decodes, so only lane (g, t) with
+// g >> 1 == t supplies a non-zero operand.  The operand fragments depend on the round only, so every CTA builds them
+// once (each warp for its own rounds) and keeps them in shared memory in the owning lanes' final layout, with the
+// groups' sums of x for the -1.5 term.  A row of x that holds Inf or NaN sends the whole CTA down a scalar fp32 path,
+// which reproduces the dense product's NaN / Inf pattern.
+#pragma once
+
+#include "gemv_a16.cuh"
+
+namespace ojx {
+
+constexpr int kB2Warps = 8;
+constexpr int kB2Ahead = 3;                       // rounds in flight per warp
+
+__host__ __device__ inline size_t b2_smem_bytes(int K) {
+    const int rounds = K / 256;
+    return (size_t)rounds * (8 * 32 * 4 + 8 * 4 * 4) + kB2Warps * 16 * 4 * 2 + 16;     // fragments, group factors, partial sums, flag
+}
+
+struct B2Loads {
+    uint4 ca, cb;                                 // 64 codes of rows g and g + 8
+    uint32_t sa, sb;                              // their two fp16 scales each
+};
+
+__global__ void __launch_bounds__(kB2Warps * 32, 2)
+gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
+               const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype) {
+    extern __shared__ __align__(16) uint8_t b2_smem[];
+    const int rounds = K / 256;
+    uint32_t* frag = reinterpret_cast<uint32_t*>(b2_smem);                             // [round][owner 0..7][32 words]
+    float* gf = reinterpret_cast<float*>(b2_smem + (size_t)rounds * 8 * 32 * 4);       // [round][group 0..7][ua, ub, -1.5 sum x, pad]
+    float* red = gf + (size_t)rounds * 8 * 4;                                          // [2][warp][16 rows]
+    int* bad_flag = reinterpret_cast<int*>(red + 2 * kB2Warps * 16);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    if (tid == 0) *bad_flag = 0;
+    __syncthreads();
+
+    // ---- prologue: fixed-point digits of x in the operand layout, once per CTA ----
+    for (int r = warp; r < rounds; r += kB2Warps) {
+        float v[8];                                                               // x is 16-byte aligned: one or two vector loads
+        if (x_dtype == OJX_F32) {
+            const float4* src = reinterpret_cast<const float4*>(x) + ((int64_t)r * 256 + lane * 8) / 4;
+            const float4 a = __ldg(src), c = __ldg(src + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+        } else {
+            const uint4 qv = __ldg(reinterpret_cast<const uint4*>(x) + ((int64_t)r * 256 + lane * 8) / 8);
+            const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (x_dtype == OJX_BF16) {
+                    v[2 * i] = __uint_as_float(w[i] << 16);
+                    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+                } else {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+                }
+            }
+        }
+        uint32_t amax = 0;
+        bool bad = false;
+        float sum8 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t mag = __float_as_uint(v[i]) & 0x7FFFFFFFu;
+            if (mag >= 0x7F800000u) bad = true;
+            else amax = max(amax, mag);
+            sum8 += v[i];
+        }
+        if (__any_sync(0xFFFFFFFFu, bad) && lane == 0) *bad_flag = 1;
+        amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+        amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));                 // the four lanes of a group
+        sum8 += __shfl_xor_sync(0xFFFFFFFFu, sum8, 1);
+        sum8 += __shfl_xor_sync(0xFFFFFFFFu, sum8, 2);                           // sum of the group's 32 activations
+        const int ex = (int)(amax >> 23);
+        const int shift = 26 - (ex == 0 ? -126 : ex - 127);                      // in [-101, 152]: applied as two factors
+        const int sa = shift >> 1, sb = shift - sa;
+        const float fa = __uint_as_float((uint32_t)(127 + sa) << 23), fb = __uint_as_float((uint32_t)(127 + sb) << 23);
+        uint32_t dw[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};             // [digit][values 0-3, 4-7] as int8 x 4
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int q0 = __float2int_rn(v[i] * fa * fb);
+            const int q1 = (q0 + 64) >> 7, d3 = q0 - (q1 << 7);
+            const int q2 = (q1 + 64) >> 7, d2 = q1 - (q2 << 7);
+            const int d0 = (q2 + 64) >> 7, d1 = q2 - (d0 << 7);
+            const int sh = 8 * (i & 3);
+            dw[0][i >> 2] |= (uint32_t)(d0 & 0xFF) << sh;
+            dw[1][i >> 2] |= (uint32_t)(d1 & 0xFF) << sh;
+            dw[2][i >> 2] |= (uint32_t)(d2 & 0xFF) << sh;
+            dw[3][i >> 2] |= (uint32_t)(d3 & 0xFF) << sh;
+        }
+        // hp[d][c] = the digit-d bytes of this lane's values c and c + 4 (c = 0..3): the pairs an operand register takes
+        uint32_t hp[4][4];
+#pragma unroll
+        for (int d = 0; d < 4; ++d)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) hp[d][c] = prmt(dw[d][0], dw[d][1], 0x4040u | (uint32_t)c | ((uint32_t)(4 + c) << 4)) & 0xFFFFu;
+        // Step (q, p) of lane quarter t uses codes 2p + {0, 4, 8, 12} (first register) and 2p + 1 + {0, 4, 8, 12} (second)
+        // of word q, i.e. k = 64 t + 16 q + ...: values 2p (+1) and 2p + 4 (+1) of lane 8t + 2q, then the same of lane 8t + 2q + 1.
+        const bool owner = (g >> 1) == t;
+        const bool hi_digits = (g & 1) != 0;
+        uint32_t* mine = frag + ((size_t)r * 8 + g) * 32;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int p = 0; p < 2; ++p)
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int reg = 0; reg < 2; ++reg) {
+                        const int c = 2 * p + reg, l0 = 8 * t + 2 * q;
+                        const uint32_t lo0 = __shfl_sync(0xFFFFFFFFu, hp[m][c], l0), lo1 = __shfl_sync(0xFFFFFFFFu, hp[m][c], l0 + 1);
+                        const uint32_t hi0 = __shfl_sync(0xFFFFFFFFu, hp[2 + m][c], l0), hi1 = __shfl_sync(0xFFFFFFFFu, hp[2 + m][c], l0 + 1);
+                        if (owner) mine[((q * 2 + p) * 2 + m) * 2 + reg] = hi_digits ? (hi0 | (hi1 << 16)) : (lo0 | (lo1 << 16));
+                    }
+        if (t == 0) {                                                           // lane 4G describes group G of the round
+            float* f = gf + ((size_t)r * 8 + g) * 4;
+            f[0] = __uint_as_float((uint32_t)(127 - sa) << 23);
+            f[1] = __uint_as_float((uint32_t)(127 - sb) << 23);
+            f[2] = -1.5f * sum8;
+            f[3] = 0.f;
+        }
+    }
+    __syncthreads();
+
+    const int tiles = (N + 15) / 16;
+    const int64_t row_codes = K / 4, row_scales = K / 32;
+    if (*bad_flag != 0) {
+        // Inf / NaN in x: every product in fp32, one warp per weight row
+        for (int n = blockIdx.x * kB2Warps + warp; n < N; n += gridDim.x * kB2Warps) {
+            float acc = 0.f;
+            for (int k = lane; k < K; k += 32) {
+                const float w = ((float)((packed[n * row_codes + (k >> 2)] >> (2 * (k & 3))) & 3) - 1.5f) *
+                                __half2float(__ushort_as_half(scales[n * row_scales + (k >> 5)]));
+                acc = fmaf(load_any(x, x_dtype, k), w, acc);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+            if (lane == 0) {
+                if (bias != nullptr) acc += load_any(bias, x_dtype, n);
+                store_any(y, y_dtype, n, acc);
+            }
+        }
+        return;
+    }
+
+    // ---- main loop: this warp's (tile, round) pairs in order, kB2Ahead of them in flight ----
+    const int my_rounds = (rounds - warp + kB2Warps - 1) / kB2Warps;              // rounds warp, warp + 8, ...
+    const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int64_t total = (int64_t)my_tiles * my_rounds;
+    auto fetch = [&](int64_t it, B2Loads& L) {
+        const int ti = (int)(it / my_rounds), ri = (int)(it - (int64_t)ti * my_rounds);
+        const int tile = blockIdx.x + ti * gridDim.x, r = warp + ri * kB2Warps;
+        const int na = min(tile * 16 + g, N - 1), nb = min(tile * 16 + g + 8, N - 1);     // rows beyond N re-read the last row
+        L.ca = __ldg(reinterpret_cast<const uint4*>(packed + na * row_codes + r * 64 + t * 16));
+        L.cb = __ldg(reinterpret_cast<const uint4*>(packed + nb * row_codes + r * 64 + t * 16));
+        L.sa = __ldg(reinterpret_cast<const uint32_t*>(scales + na * row_scales + r * 8 + t * 2));
+        L.sb = __ldg(reinterpret_cast<const uint32_t*>(scales + nb * row_scales + r * 8 + t * 2));
+    };
+    B2Loads ring[kB2Ahead];
+#pragma unroll
+    for (int i = 0; i < kB2Ahead; ++i)
+        if (i < total) fetch(i, ring[i]);
+
+    const bool owner = (g >> 1) == t;
+    float og = 0.f, og8 = 0.f;                      // this warp's partial sums of rows g and g + 8 of the current tile
+    int tiles_done = 0;
+    for (int64_t it0 = 0; it0 < total; it0 += kB2Ahead) {
+#pragma unroll
+        for (int slot = 0; slot < kB2Ahead; ++slot) {
+            const int64_t it = it0 + slot;
+            if (it >= total) break;
+            const B2Loads L = ring[slot];
+            if (it + kB2Ahead < total) fetch(it + kB2Ahead, ring[slot]);
+            const int ti = (int)(it / my_rounds), ri = (int)(it - (int64_t)ti * my_rounds);
+            const int r = warp + ri * kB2Warps;
+            const uint32_t* xf = frag + ((size_t)r * 8 + g) * 32;                  // this lane's operand words (owners only)
+            const uint32_t wa[4] = {L.ca.x, L.ca.y, L.ca.z, L.ca.w}, wb[4] = {L.cb.x, L.cb.y, L.cb.z, L.cb.w};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {                                          // scale group 2t + h of the round: words 2h, 2h + 1
+                int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int qq = 0; qq < 2; ++qq) {
+                    const int q = 2 * h + qq;
+                    uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = make_uint4(0u, 0u, 0u, 0u);
+                    if (owner) {                                                   // [p = 0: m0 r0, m0 r1, m1 r0, m1 r1], [p = 1: ...]
+                        xa = *reinterpret_cast<const uint4*>(xf + q * 8);
+                        xb = *reinterpret_cast<const uint4*>(xf + q * 8 + 4);
+                    }
+                    const uint32_t a0 = wa[q] & 0x03030303u, a1 = (wa[q] >> 2) & 0x03030303u;
+                    const uint32_t a2 = (wa[q] >> 4) & 0x03030303u, a3 = (wa[q] >> 6) & 0x03030303u;
+                    const uint32_t b0 = wb[q] & 0x03030303u, b1 = (wb[q] >> 2) & 0x03030303u;
+                    const uint32_t b2 = (wb[q] >> 4) & 0x03030303u, b3 = (wb[q] >> 6) & 0x03030303u;
+                    // p = 0: codes {0,4,8,12} and {1,5,9,13} of the word; p = 1: {2,6,10,14} and {3,7,11,15}
+                    mma_s8(c0, a0, b0, a1, b1, xa.x, xa.y);
+                    mma_s8(c1, a0, b0, a1, b1, xa.z, xa.w);
+                    mma_s8(c0, a2, b2, a3, b3, xb.x, xb.y);
+                    mma_s8(c1, a2, b2, a3, b3, xb.z, xb.w);
+                }
+                // column 2t: digits 0 (c0) and 1 (c1); column 2t + 1: digits 2 and 3; rows g (0, 1) and g + 8 (2, 3)
+                const float4 f = *reinterpret_cast<const float4*>(gf + ((size_t)r * 8 + 2 * t + h) * 4);
+                const float sg = fmaf((float)(c0[0] * 128 + c1[0]), 16384.f, (float)(c0[1] * 128 + c1[1]));
+                const float sg8 = fmaf((float)(c0[2] * 128 + c1[2]), 16384.f, (float)(c0[3] * 128 + c1[3]));
+                const float wsa = __half2float(__ushort_as_half((uint16_t)(h ? (L.sa >> 16) : (L.sa & 0xFFFFu))));
+                const float wsb = __half2float(__ushort_as_half((uint16_t)(h ? (L.sb >> 16) : (L.sb & 0xFFFFu))));
+                og = fmaf(wsa, fmaf(sg * f.x, f.y, f.z), og);
+                og8 = fmaf(wsb, fmaf(sg8 * f.x, f.y, f.z), og8);
+            }
+            if (ri == my_rounds - 1) {
+                // the warp's last round of this tile: combine the four lane quarters, park, and let warp 0 add the warps
+                og += __shfl_xor_sync(0xFFFFFFFFu, og, 1);
+                og8 += __shfl_xor_sync(0xFFFFFFFFu, og8, 1);
+                og += __shfl_xor_sync(0xFFFFFFFFu, og, 2);
+                og8 += __shfl_xor_sync(0xFFFFFFFFu, og8, 2);
+                float* mybuf = red + ((size_t)(tiles_done & 1) * kB2Warps + warp) * 16;
+                if (t == 0) { mybuf[g] = og; mybuf[g + 8] = og8; }
+                og = og8 = 0.f;
+                asm volatile("bar.sync 1, %0;" ::"r"(kB2Warps * 32) : "memory");       // every warp reaches its tile ends in the same order
+                if (warp == 0 && lane < 16) {
+                    const int tile = blockIdx.x + ti * gridDim.x, n = tile * 16 + lane;
+                    if (n < N) {
+                        const float* b = red + (size_t)(tiles_done & 1) * kB2Warps * 16 + lane;
+                        float sum = 0.f;
+#pragma unroll
+                        for (int w = 0; w < kB2Warps; ++w) sum += b[w * 16];           // the host only launches with rounds % 8 == 0
+                        if (bias != nullptr) sum += load_any(bias, x_dtype, n);
+                        store_any(y, y_dtype, n, sum);
+                    }
+                }
+                ++tiles_done;
+            }
+        }
+    }
+}
+
+}  // namespace ojx

@@ -586,3 +586,37 @@ def test_low_bit_decode_linear_matches_dense_product(P, oracle, bits, m, k, n, g
     assert float(((y - ref).abs() / budget).max()) < 1e-5
     y16 = lin(x, pk, sc, None, n, k, group)
     assert y16.dtype == dt and float((y16.float() - (ref - bias.float())).abs().max()) <= 2.0 ** -7 * float(ref.abs().max()) + 1e-3
+
+
+@pytest.mark.parametrize("k,n,dt", [(2048, 40, torch.bfloat16), (4096, 4096, torch.bfloat16), (14336, 100, torch.float16),
+                                    (8192, 17, torch.float32)])
+def test_two_bit_one_row_tensor_core_kernel(P, oracle, k, n, dt):
+    """gemv_b2_kernel (one row, groups of 32, K % 2048 == 0) against the dense fp32 product: within 1e-5 of
+    sum |x||w| per output (row counts that are not multiples of 16 included), outliers do not hurt their neighbours,
+    scaling x by a power of two scales y exactly, Inf / NaN give the dense product's pattern."""
+    dev = torch.device(DEV)
+    w = torch.from_numpy(oracle.gen_normal(950 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
+    pk, sc = P.ops.encode_2bit(w, 32)
+    wd = P.ops.decode_2bit(pk, sc, (n, k), torch.float32)
+    x = torch.from_numpy(oracle.gen_normal(951, k, 1.0).reshape(1, k).copy()).to(dt).to(dev)
+    x[0, 7::256] *= 1.0e3                                            # one outlier per 256-wide round
+    bias = torch.from_numpy(oracle.gen_normal(952, n, 0.1).copy()).to(dt).to(dev)
+    y = P.ops.linear_2bit(x, pk, sc, bias, n, k, 32, out_dtype=torch.float32)
+    ref = x.float() @ wd.t() + bias.float()
+    budget = x.float().abs() @ wd.abs().t() + bias.float().abs()
+    assert float(((y - ref).abs() / budget).max()) < 1e-5
+    y0 = P.ops.linear_2bit(x, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+    for s in (-30, 20):
+        if dt == torch.float16:
+            continue                                                 # would leave fp16's range
+        ys = P.ops.linear_2bit(x * 2.0 ** s, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+        assert torch.equal(ys, y0 * 2.0 ** s), s
+    xi = x.clone()
+    xi[0, 5] = float("inf")
+    xi[0, k - 1] = float("-inf")
+    yi = P.ops.linear_2bit(xi, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+    ri = xi.float() @ wd.t()
+    assert torch.equal(torch.isnan(yi), torch.isnan(ri)) and torch.equal(torch.isposinf(yi), torch.isposinf(ri))
+    xn = x.clone()
+    xn[0, 100] = float("nan")
+    assert torch.isnan(P.ops.linear_2bit(xn, pk, sc, None, n, k, 32, out_dtype=torch.float32)).all()
