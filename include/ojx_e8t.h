@@ -121,9 +121,10 @@ int32_t ojx_e8t_fwht32(const void* x, int32_t dtype, int64_t count, void* out, v
  *   ojx_e8t_linear_2bit   y[M, N] = x[M, K] . W^T (+ bias) from the packed codes in one fp32 kernel (any shape,
  *                         any of the three dtypes for x, bias (x's dtype) and y); replaces the 2.0-bit branch of
  *                         _FusedE8GEMMFunction.forward (ojasx2/math/lattice.py:596-624) and the native
- *                         fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444).  Up to eight rows with
- *                         K % 16 == 0 and 16-byte aligned x run a shared-memory decode kernel, everything else a
- *                         scalar kernel; the tensor-core kernels of this library serve the 1.5-bit format only.
+ *                         fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444).  One row with group 32
+ *                         and K % 2048 == 0 runs on int8 tensor cores (activations as 28-bit fixed point per scale
+ *                         group, as in ojx_e8t_gemv for one bf16 row); up to eight rows with K % 16 == 0 and 16-byte
+ *                         aligned x run a shared-memory fp32 kernel, everything else a scalar fp32 kernel.
  */
 int32_t ojx_e8t_encode_2bit(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
                             uint8_t* packed_out, uint16_t* scales_out, void* stream);
