@@ -19,9 +19,9 @@
 // Activations: 28-bit fixed point per scale group exactly as in the ternary one-row kernel (gemv_a16.cuh, kI8): the
 // group's largest finite magnitude fixes the exponent, the integers are split into four base-128 digits; accumulator
 // column 2t' + h takes digits 2h, 2h + 1 of the group that lane quarter t' decodes, so only lane (g, t) with
-// g >> 1 == t supplies a non-zero operand.  The operand fragments depend on the round only, so every CTA builds them
-// once (each warp for its own rounds) and keeps them in shared memory in the owning lanes' final layout, with the
-// groups' sums of x for the -1.5 term.  A row of x that holds Inf or NaN sends the whole CTA down a scalar fp32 path,
+// g >> 1 == t supplies a non-zero operand.  The operand words depend on the round only, so every CTA builds them once
+// (each warp for its own rounds: quantise, then sixteen 16-bit stores per lane, no shuffles) and keeps them in shared
+// memory in the byte order of the shift/mask code words, with the groups' sums of x for the -1.5 term.  A row of x that holds Inf or NaN sends the whole CTA down a scalar fp32 path,
 // which reproduces the dense product's NaN / Inf pattern.
 #pragma once
 
@@ -47,7 +47,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
                const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype) {
     extern __shared__ __align__(16) uint8_t b2_smem[];
     const int rounds = K / 256;
-    uint32_t* frag = reinterpret_cast<uint32_t*>(b2_smem);                             // [round][owner 0..7][32 words]
+    uint32_t* frag = reinterpret_cast<uint32_t*>(b2_smem);                             // [round][digit][word group 0..15][4 words]
     float* gf = reinterpret_cast<float*>(b2_smem + (size_t)rounds * 8 * 32 * 4);       // [round][group 0..7][ua, ub, -1.5 sum x, pad]
     float* red = gf + (size_t)rounds * 8 * 4;                                          // [2][warp][16 rows]
     int* bad_flag = reinterpret_cast<int*>(red + 2 * kB2Warps * 16);
@@ -110,30 +110,16 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
             dw[2][i >> 2] |= (uint32_t)(d2 & 0xFF) << sh;
             dw[3][i >> 2] |= (uint32_t)(d3 & 0xFF) << sh;
         }
-        // hp[d][c] = the digit-d bytes of this lane's values c and c + 4 (c = 0..3): the pairs an operand register takes
-        uint32_t hp[4][4];
+        // Operand layout in shared memory: frag[round][digit][word group 0..15][c 0..3] - the 32-bit word (group, c) holds
+        // the digit bytes of k = 16 group + c + {0, 4, 8, 12}, exactly the bytes that meet the code bytes of
+        // (code word >> 2c) & 0x03030303.  This lane holds k = 8 lane .. 8 lane + 7: values c and c + 4 are the low (even
+        // lane) or high (odd lane) half of word (lane >> 1, c).
+        uint16_t* half = reinterpret_cast<uint16_t*>(frag + (size_t)r * 256) + (lane >> 1) * 8 + (lane & 1);
 #pragma unroll
         for (int d = 0; d < 4; ++d)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) hp[d][c] = prmt(dw[d][0], dw[d][1], 0x4040u | (uint32_t)c | ((uint32_t)(4 + c) << 4)) & 0xFFFFu;
-        // Step (q, p) of lane quarter t uses codes 2p + {0, 4, 8, 12} (first register) and 2p + 1 + {0, 4, 8, 12} (second)
-        // of word q, i.e. k = 64 t + 16 q + ...: values 2p (+1) and 2p + 4 (+1) of lane 8t + 2q, then the same of lane 8t + 2q + 1.
-        const bool owner = (g >> 1) == t;
-        const bool hi_digits = (g & 1) != 0;
-        uint32_t* mine = frag + ((size_t)r * 8 + g) * 32;
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-            for (int p = 0; p < 2; ++p)
-#pragma unroll
-                for (int m = 0; m < 2; ++m)
-#pragma unroll
-                    for (int reg = 0; reg < 2; ++reg) {
-                        const int c = 2 * p + reg, l0 = 8 * t + 2 * q;
-                        const uint32_t lo0 = __shfl_sync(0xFFFFFFFFu, hp[m][c], l0), lo1 = __shfl_sync(0xFFFFFFFFu, hp[m][c], l0 + 1);
-                        const uint32_t hi0 = __shfl_sync(0xFFFFFFFFu, hp[2 + m][c], l0), hi1 = __shfl_sync(0xFFFFFFFFu, hp[2 + m][c], l0 + 1);
-                        if (owner) mine[((q * 2 + p) * 2 + m) * 2 + reg] = hi_digits ? (hi0 | (hi1 << 16)) : (lo0 | (lo1 << 16));
-                    }
+            for (int c = 0; c < 4; ++c)
+                half[d * 128 + c * 2] = (uint16_t)prmt(dw[d][0], dw[d][1], 0x4040u | (uint32_t)c | ((uint32_t)(4 + c) << 4));
         if (t == 0) {                                                           // lane 4G describes group G of the round
             float* f = gf + ((size_t)r * 8 + g) * 4;
             f[0] = __uint_as_float((uint32_t)(127 - sa) << 23);
@@ -169,33 +155,48 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
     const int my_rounds = (rounds - warp + kB2Warps - 1) / kB2Warps;              // rounds warp, warp + 8, ...
     const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const int64_t total = (int64_t)my_tiles * my_rounds;
-    auto fetch = [&](int64_t it, B2Loads& L) {
-        const int ti = (int)(it / my_rounds), ri = (int)(it - (int64_t)ti * my_rounds);
-        const int tile = blockIdx.x + ti * gridDim.x, r = warp + ri * kB2Warps;
+    // The fetcher and the consumer each walk the (tile, round) pairs with their own counters: no divisions, 32-bit offsets
+    // from two row pointers that move once per tile.
+    int f_ti = 0, f_ri = 0;
+    const uint8_t* f_ca = nullptr; const uint8_t* f_cb = nullptr;
+    const uint16_t* f_sa = nullptr; const uint16_t* f_sb = nullptr;
+    auto fetch_rows = [&]() {
+        const int tile = blockIdx.x + f_ti * gridDim.x;
         const int na = min(tile * 16 + g, N - 1), nb = min(tile * 16 + g + 8, N - 1);     // rows beyond N re-read the last row
-        L.ca = __ldg(reinterpret_cast<const uint4*>(packed + na * row_codes + r * 64 + t * 16));
-        L.cb = __ldg(reinterpret_cast<const uint4*>(packed + nb * row_codes + r * 64 + t * 16));
-        L.sa = __ldg(reinterpret_cast<const uint32_t*>(scales + na * row_scales + r * 8 + t * 2));
-        L.sb = __ldg(reinterpret_cast<const uint32_t*>(scales + nb * row_scales + r * 8 + t * 2));
+        f_ca = packed + na * row_codes + t * 16; f_cb = packed + nb * row_codes + t * 16;
+        f_sa = scales + na * row_scales + t * 2; f_sb = scales + nb * row_scales + t * 2;
+    };
+    auto fetch = [&](B2Loads& L) {
+        const int r = warp + f_ri * kB2Warps;
+        L.ca = __ldg(reinterpret_cast<const uint4*>(f_ca + r * 64));
+        L.cb = __ldg(reinterpret_cast<const uint4*>(f_cb + r * 64));
+        L.sa = __ldg(reinterpret_cast<const uint32_t*>(f_sa + r * 8));
+        L.sb = __ldg(reinterpret_cast<const uint32_t*>(f_sb + r * 8));
+        if (++f_ri == my_rounds) {
+            f_ri = 0;
+            ++f_ti;
+            if (f_ti < my_tiles) fetch_rows();
+        }
     };
     B2Loads ring[kB2Ahead];
+    if (total > 0) fetch_rows();
 #pragma unroll
     for (int i = 0; i < kB2Ahead; ++i)
-        if (i < total) fetch(i, ring[i]);
+        if (i < total) fetch(ring[i]);
 
     const bool owner = (g >> 1) == t;
     float og = 0.f, og8 = 0.f;                      // this warp's partial sums of rows g and g + 8 of the current tile
-    int tiles_done = 0;
+    int tiles_done = 0, ti = 0, ri = 0;             // the consumer's position
     for (int64_t it0 = 0; it0 < total; it0 += kB2Ahead) {
 #pragma unroll
         for (int slot = 0; slot < kB2Ahead; ++slot) {
             const int64_t it = it0 + slot;
             if (it >= total) break;
             const B2Loads L = ring[slot];
-            if (it + kB2Ahead < total) fetch(it + kB2Ahead, ring[slot]);
-            const int ti = (int)(it / my_rounds), ri = (int)(it - (int64_t)ti * my_rounds);
+            if (it + kB2Ahead < total) fetch(ring[slot]);
             const int r = warp + ri * kB2Warps;
-            const uint32_t* xf = frag + ((size_t)r * 8 + g) * 32;                  // this lane's operand words (owners only)
+            // this lane's operand words (owners only): digits 2 (g & 1) and 2 (g & 1) + 1 of word groups 4t .. 4t + 3
+            const uint32_t* xf = frag + (size_t)r * 256 + (size_t)(2 * (g & 1)) * 64 + 16 * t;
             const uint32_t wa[4] = {L.ca.x, L.ca.y, L.ca.z, L.ca.w}, wb[4] = {L.cb.x, L.cb.y, L.cb.z, L.cb.w};
 #pragma unroll
             for (int h = 0; h < 2; ++h) {                                          // scale group 2t + h of the round: words 2h, 2h + 1
@@ -204,18 +205,18 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
                 for (int qq = 0; qq < 2; ++qq) {
                     const int q = 2 * h + qq;
                     uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = make_uint4(0u, 0u, 0u, 0u);
-                    if (owner) {                                                   // [p = 0: m0 r0, m0 r1, m1 r0, m1 r1], [p = 1: ...]
-                        xa = *reinterpret_cast<const uint4*>(xf + q * 8);
-                        xb = *reinterpret_cast<const uint4*>(xf + q * 8 + 4);
+                    if (owner) {                                                   // words c = 0..3 of the first and the second digit
+                        xa = *reinterpret_cast<const uint4*>(xf + q * 4);
+                        xb = *reinterpret_cast<const uint4*>(xf + 64 + q * 4);
                     }
                     const uint32_t a0 = wa[q] & 0x03030303u, a1 = (wa[q] >> 2) & 0x03030303u;
                     const uint32_t a2 = (wa[q] >> 4) & 0x03030303u, a3 = (wa[q] >> 6) & 0x03030303u;
                     const uint32_t b0 = wb[q] & 0x03030303u, b1 = (wb[q] >> 2) & 0x03030303u;
                     const uint32_t b2 = (wb[q] >> 4) & 0x03030303u, b3 = (wb[q] >> 6) & 0x03030303u;
-                    // p = 0: codes {0,4,8,12} and {1,5,9,13} of the word; p = 1: {2,6,10,14} and {3,7,11,15}
+                    // codes {0,4,8,12} and {1,5,9,13} of the word, then {2,6,10,14} and {3,7,11,15}; c0 / c1: the two digits
                     mma_s8(c0, a0, b0, a1, b1, xa.x, xa.y);
-                    mma_s8(c1, a0, b0, a1, b1, xa.z, xa.w);
-                    mma_s8(c0, a2, b2, a3, b3, xb.x, xb.y);
+                    mma_s8(c1, a0, b0, a1, b1, xb.x, xb.y);
+                    mma_s8(c0, a2, b2, a3, b3, xa.z, xa.w);
                     mma_s8(c1, a2, b2, a3, b3, xb.z, xb.w);
                 }
                 // column 2t: digits 0 (c0) and 1 (c1); column 2t + 1: digits 2 and 3; rows g (0, 1) and g + 8 (2, 3)
@@ -250,6 +251,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
                 }
                 ++tiles_done;
             }
+            if (++ri == my_rounds) { ri = 0; ++ti; }
         }
     }
 }
