@@ -3,6 +3,7 @@ the header and the binding agree, the host mirror keeps the reference's names/si
 and the column-sharding logic works across two gloo ranks."""
 
 import ctypes
+import importlib
 import inspect
 import os
 import re
@@ -226,3 +227,50 @@ def test_column_sharding_two_gloo_ranks(tmp_path, n_rows):
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
     assert "SHARD_OK" in proc.stdout
+
+
+def test_checkpoint_file_discovery_and_layout_rules(P, tmp_path):
+    """Host-only parts of checkpoint ingestion (ojasx2/streaming_e8.py:90-109, 231-252): which shard files a
+    directory yields, refusal of shards outside it, and the row-layout rules of the three formats."""
+    import json
+    se = importlib.import_module(P.__name__ + ".streaming_e8")
+    with pytest.raises(FileNotFoundError):
+        se._checkpoint_files(tmp_path)
+    (tmp_path / "b.safetensors").write_bytes(b"x")
+    (tmp_path / "a.safetensors").write_bytes(b"x")
+    assert [f.name for f in se._checkpoint_files(tmp_path)] == ["a.safetensors", "b.safetensors"]
+    (tmp_path / "model.safetensors").write_bytes(b"x")
+    assert [f.name for f in se._checkpoint_files(tmp_path)] == ["model.safetensors"]
+    index = tmp_path / "model.safetensors.index.json"
+    index.write_text(json.dumps({"weight_map": {"w1": "b.safetensors", "w2": "a.safetensors", "w3": "b.safetensors"}}))
+    assert [f.name for f in se._checkpoint_files(tmp_path)] == ["a.safetensors", "b.safetensors"]
+    index.write_text(json.dumps({"weight_map": {"w": "missing.safetensors"}}))
+    with pytest.raises(FileNotFoundError):
+        se._checkpoint_files(tmp_path)
+    index.write_text(json.dumps({"weight_map": {"w": "../escape.safetensors"}}))
+    (tmp_path.parent / "escape.safetensors").write_bytes(b"x")
+    with pytest.raises(ValueError, match="inside the checkpoint directory"):
+        se._checkpoint_files(tmp_path)
+    index.write_text(json.dumps({"weight_map": {}}))
+    with pytest.raises(ValueError, match="weight_map"):
+        se._checkpoint_files(tmp_path)
+
+    for bitrate in (1.0, 1.5, 2.0):
+        se._validate_row_layout(64, 256, bitrate, 32)
+        with pytest.raises(ValueError):
+            se._validate_row_layout(64, 100, bitrate, 32)          # a row would not own whole groups
+        with pytest.raises(ValueError):
+            se._validate_row_layout(64, 256, bitrate, 8)           # row packing wants groups of 32 k
+    with pytest.raises(ValueError):
+        se._validate_row_layout(64, 256, 3.0, 32)
+    assert se._bytes_per_row(4096, 1.0) == 512 and se._bytes_per_row(4096, 1.5) == 768 and se._bytes_per_row(4096, 2.0) == 1024
+    ops = P.ops
+    assert ops.packed_sizes_lowbit(2, 7, 13, 8) == (24, 12)            # 91 weights padded to 96
+    assert ops.packed_sizes_lowbit(1, 7, 13, 12) == (12, 12)           # group 12 -> 8, as the reference's root packer
+    with pytest.raises(ValueError):
+        ops.packed_sizes_lowbit(2, 7, 13, 12)                          # the 2-bit packer raises instead
+    assert se._matches_any("model.layers.0.mlp.up_proj", ("*.mlp.*",)) and not se._matches_any("lm_head", ("model.*",))
+    with pytest.raises(ValueError, match="row_block"):
+        P.load_hf_checkpoint_e8(str(tmp_path), row_block=0)
+    with pytest.raises(NotADirectoryError):
+        P.load_hf_checkpoint_e8(str(tmp_path / "nowhere"))
