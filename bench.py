@@ -62,7 +62,11 @@ FUSED_TEXT = ("output-column shards; the kernels store their shard into every ra
 def sweep_config(rotation, launches_per_step, parallelism, packed_gb):
     return {"workload": WORKLOAD, "rotation": rotation,
             "l2": "inputs larger than L2: %.2f GB of packed weights per pass, a matrix is revisited only after the whole sweep" % packed_gb,
-            "parallelism": parallelism, "launches_per_step": launches_per_step}
+            "parallelism": parallelism, "launches_per_step": launches_per_step,
+            "launch_order": "the launches of a pass work on different matrices with their own activations and outputs and are "
+                            "declared independent: a launch's CTAs start as multiprocessors become free instead of after the "
+                            "previous launch has drained; the per-kernel figures under roofline come from a separate pass with "
+                            "ordered launches"}
 
 
 def measured_peaks():
@@ -433,12 +437,13 @@ def main():
                 # of every window themselves
                 y_all = windows[(si, b)].local.view(world, R, b, nl)[rank]
                 groups[(si, b)] = ops.GroupedGemv([(x, pk, sc, None, y_all[r]) for r, (pk, sc) in enumerate(mats)],
-                                                  [(nl, k)] * R, peer_delta=windows[(si, b)].delta, static_weights=True)
+                                                  [(nl, k)] * R, peer_delta=windows[(si, b)].delta, static_weights=True,
+                                                  independent=True)
             else:
                 y_all = y_plain
             # the same launch without any exchange (the baseline of the NCCL mode, and the attribution run)
             plain_groups[(si, b)] = ops.GroupedGemv([(x, pk, sc, None, y_plain[r]) for r, (pk, sc) in enumerate(mats)],
-                                                    [(nl, k)] * R, static_weights=True)
+                                                    [(nl, k)] * R, static_weights=True, independent=True)
             if not fused:
                 groups[(si, b)] = plain_groups[(si, b)]
             launches_per_step += 1 + groups[(si, b)].needs_reduce
@@ -522,7 +527,7 @@ def main():
             for b in BATCHES:
                 for si in range(len(SHAPES)):
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record(); groups[(si, b)](); e1.record()
+                    e0.record(); groups[(si, b)](independent=False); e1.record()      # ordered launches: clean per-launch times
                     pairs[(si, b)].append((e0, e1))
             if fused:
                 arena.fence()

@@ -316,6 +316,12 @@ int32_t ojx_e8t_gemv_grouped_peers(const ojx_e8t_gemv_problem* problems, int32_t
  *       predecessor only before its first read of x and its first write of y (programmatic dependent launch).
  *       Activations, outputs, bias and partial buffers may depend on the predecessor as usual.  Without the flag
  *       the launch is ordered like any other kernel.  Works inside stream capture.
+ *   OJX_GEMV_INDEPENDENT     (implies OJX_GEMV_STATIC_WEIGHTS) the caller promises more: NOTHING this launch reads
+ *       or writes - activations, bias, outputs, partial buffers - is written or read by the kernels queued ahead of
+ *       it in `stream` that may still be running (for example the previous launches of a sweep over different
+ *       matrices with their own outputs).  The launch then never waits for its predecessor: its CTAs start as
+ *       multiprocessors become free, so the tail of one launch is filled by the head of the next.  Work queued
+ *       AFTER the launch is ordered after it as usual.  Not allowed together with the peer flags.
  *   OJX_GEMV_SIGNAL_PEERS    (needs peer_sync and peer_delta) once every result of the launch has been stored into
  *       every rank's window, this rank publishes its next epoch into flag[this rank] of every rank's block
  *       (release at system scope, plain stores over NVLink) and advances its own epoch.
@@ -337,6 +343,7 @@ typedef struct {
 #define OJX_GEMV_STATIC_WEIGHTS 1
 #define OJX_GEMV_SIGNAL_PEERS   2
 #define OJX_GEMV_WAIT_PEERS     4
+#define OJX_GEMV_INDEPENDENT    16
 #define OJX_GEMV_TEST_LOSE_COPY 8   /* tests only: the first work item's copies are never reported complete, so the
                                        wait on them runs into its limit (set a small one) and the error path runs */
 int32_t ojx_e8t_gemv_grouped_ex(const ojx_e8t_gemv_problem* problems, int32_t count, int32_t total_tiles,

@@ -21,6 +21,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libojx_e8t.so")
 
 OJX_F32, OJX_F16, OJX_BF16 = 0, 1, 2
 OJX_GEMV_STATIC_WEIGHTS, OJX_GEMV_SIGNAL_PEERS, OJX_GEMV_WAIT_PEERS, OJX_GEMV_TEST_LOSE_COPY = 1, 2, 4, 8
+OJX_GEMV_INDEPENDENT = 16
 OJX_ENCODE_HADAMARD = 1
 PEER_SYNC_BYTES = 48        # sizeof(ojx_e8t_peer_sync): epoch, arrived, status, spin_limit, flag[8]
 

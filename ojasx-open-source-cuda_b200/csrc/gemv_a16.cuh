@@ -163,7 +163,7 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     const bool signal = peers.sync != nullptr && (peers.mode & OJX_GEMV_SIGNAL_PEERS) != 0 && (peers.mode & 0x100) == 0;
     if (i0 >= i1) {
         if (signal && tid == 0) {
-            if (overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (overlap == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
             peer_signal(peers);
         }
         return;
@@ -233,8 +233,8 @@ gemv_a16_kernel(const ojx_e8t_gemv_problem* __restrict__ probs_dev, const __grid
     };
     // packed weights never depend on the previous launch: their copies start before that launch has drained
     for (int n = 0; n < S - 1 && n < nitems; ++n) issue_next();
-    // activations (and the output buffers) do
-    if (overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // activations (and the output buffers) do, unless the caller declared the launch independent (overlap == 2)
+    if (overlap == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
     // ... and, in a column-sharded chain, on the same launch of every other rank
     if (peers.sync != nullptr && (peers.mode & OJX_GEMV_WAIT_PEERS)) {
         if (tid == 0) peer_wait(peers);

@@ -67,7 +67,7 @@ static int32_t launch_maybe_overlapped(void (*kernel)(Params...), int grid, int 
 
 template <int NB, bool kXF16, bool kI8 = false>
 static int32_t launch_gemv_a16(const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count, int total,
-                               int M, int y_dtype, const PeerMap& peers_in, bool overlap, cudaStream_t s) {
+                               int M, int y_dtype, const PeerMap& peers_in, int overlap, cudaStream_t s) {
     PeerMap peers = peers_in;
     peers.host_status = host_status_device_ptr();
     peers.wait_limit = wait_limit_override() != 0 ? wait_limit_override() : kSpinLimit;
@@ -78,14 +78,14 @@ static int32_t launch_gemv_a16(const ojx_e8t_gemv_problem* probs, const ojx_e8t_
     const int sms = num_sms();
     const int per = (total + sms - 1) / sms;
     const int grid = (total + per - 1) / per;
-    return launch_maybe_overlapped(gemv_a16_kernel<NB, kXF16, kI8>, grid, kGemvThreads, Cfg::kSmem, s, overlap,
-                                   probs, single, count, total, M, y_dtype, overlap ? 1 : 0, peers);
+    return launch_maybe_overlapped(gemv_a16_kernel<NB, kXF16, kI8>, grid, kGemvThreads, Cfg::kSmem, s, overlap != 0,
+                                   probs, single, count, total, M, y_dtype, overlap, peers);
 }
 
 // One bf16 activation row takes the int8 path; one to eight rows take one block of eight columns per fp16 MMA, nine to
 // sixteen take two.
 static int32_t dispatch_gemv(bool bf16, const ojx_e8t_gemv_problem* probs, const ojx_e8t_gemv_problem& single, int count,
-                             int total, int M, int y_dtype, const PeerMap& peers, bool overlap, cudaStream_t s) {
+                             int total, int M, int y_dtype, const PeerMap& peers, int overlap, cudaStream_t s) {
     if (bf16 && M == 1) return launch_gemv_a16<1, false, true>(probs, single, count, total, M, y_dtype, peers, overlap, s);
     if (bf16) return M <= 8 ? launch_gemv_a16<1, false>(probs, single, count, total, M, y_dtype, peers, overlap, s)
                             : launch_gemv_a16<2, false>(probs, single, count, total, M, y_dtype, peers, overlap, s);
@@ -109,8 +109,10 @@ int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int t
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
     const bool bf = x_dtype == OJX_BF16;
     ojx_e8t_gemv_problem none = {};
-    constexpr int kKnown = OJX_GEMV_STATIC_WEIGHTS | OJX_GEMV_SIGNAL_PEERS | OJX_GEMV_WAIT_PEERS | OJX_GEMV_TEST_LOSE_COPY;
+    constexpr int kKnown = OJX_GEMV_STATIC_WEIGHTS | OJX_GEMV_SIGNAL_PEERS | OJX_GEMV_WAIT_PEERS | OJX_GEMV_TEST_LOSE_COPY |
+                           OJX_GEMV_INDEPENDENT;
     OJX_RETURN_IF((flags & ~kKnown) != 0, OJX_ERR_UNSUPPORTED);
+    OJX_RETURN_IF((flags & OJX_GEMV_INDEPENDENT) != 0 && (flags & (OJX_GEMV_SIGNAL_PEERS | OJX_GEMV_WAIT_PEERS)) != 0, OJX_ERR_UNSUPPORTED);
     const int sync_mode = flags & (OJX_GEMV_SIGNAL_PEERS | OJX_GEMV_WAIT_PEERS);
     OJX_RETURN_IF(sync_mode != 0 && peer_sync == nullptr, OJX_ERR_NULL);
     OJX_RETURN_IF((reinterpret_cast<uintptr_t>(peer_sync) & 3) != 0, OJX_ERR_ALIGN);
@@ -120,7 +122,8 @@ int32_t gemv_grouped_impl(const ojx_e8t_gemv_problem* problems, int count, int t
         peers.mode = sync_mode | (needs_reduce ? 0x100 : 0);
     }
     peers.lose_copy = (flags & OJX_GEMV_TEST_LOSE_COPY) ? 1 : 0;
-    const bool overlap = (flags & OJX_GEMV_STATIC_WEIGHTS) != 0;
+    // 0: ordered like any kernel; 1: starts early, waits for its predecessor before touching x and y; 2: never waits
+    const int overlap = (flags & OJX_GEMV_INDEPENDENT) ? 2 : ((flags & OJX_GEMV_STATIC_WEIGHTS) ? 1 : 0);
     const int32_t st = dispatch_gemv(bf, problems, none, count, total_tiles, (int)M, y_dtype, peers, overlap, s);
     OJX_RETURN_IF(st != OJX_OK, st);
     if (!needs_reduce) return OJX_OK;

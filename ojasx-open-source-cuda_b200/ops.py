@@ -469,12 +469,14 @@ class GroupedGemv:
     def __init__(self, entries: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor], torch.Tensor]],
                  shapes: Sequence[Tuple[int, int]], peer_delta: Optional[Sequence[int]] = None,
                  static_weights: bool = False, peer_sync: Optional[int] = None, wait_peers: bool = False,
-                 signal_peers: bool = False, extra_flags: int = 0):
+                 signal_peers: bool = False, extra_flags: int = 0, independent: bool = False):
         # entries: (x[M,K], packed, scales, bias-or-None, y[M,N]);  shapes: (N, K)
         # peer_delta: byte distances from this rank's output window to every rank's (see sharding.PeerWindow);
         #             when given, each result is stored into all ranks' windows by the kernel itself
         # static_weights: promise that nothing queued ahead of a call in its stream writes the packed buffers; the
         #             launch may then begin (set-up, first weight copies) while the previous kernel drains
+        # independent: promise that nothing this launch reads or writes is touched by kernels queued ahead of it that may
+        #             still be running (a sweep over different matrices with their own outputs): it never waits for them
         # peer_sync:  device address of this rank's ojx_e8t_peer_sync block inside the peer window (PeerWindow.sync_ptr);
         #             wait_peers: wait on the device until every rank has published the launch that produced x;
         #             signal_peers: publish this launch to every rank once all results are stored
@@ -534,7 +536,7 @@ class GroupedGemv:
         if signal_peers and peer_delta is None:
             raise ValueError("signal_peers needs peer_delta")
         self.peer_sync = int(peer_sync) if peer_sync is not None else None
-        self.flags = ((_cabi.OJX_GEMV_STATIC_WEIGHTS if static_weights else 0) |
+        self.flags = ((_cabi.OJX_GEMV_STATIC_WEIGHTS if static_weights else 0) | (_cabi.OJX_GEMV_INDEPENDENT if independent else 0) |
                       (_cabi.OJX_GEMV_WAIT_PEERS if wait_peers else 0) | (_cabi.OJX_GEMV_SIGNAL_PEERS if signal_peers else 0) |
                       int(extra_flags))
         self._peers = None
@@ -543,12 +545,16 @@ class GroupedGemv:
                 raise ValueError("peer_delta needs one entry per rank, at most 8")
             self._peers = (ctypes.c_int64 * len(peer_delta))(*[int(d) for d in peer_delta])
 
-    def __call__(self) -> None:
+    def __call__(self, independent: Optional[bool] = None) -> None:
+        """Launches the group; ``independent`` overrides the constructor's choice for this call."""
+        flags = self.flags
+        if independent is not None:
+            flags = (flags | _cabi.OJX_GEMV_INDEPENDENT) if independent else (flags & ~_cabi.OJX_GEMV_INDEPENDENT)
         _cabi.raise_pending()
         with torch.cuda.device(self.device):
             st = _cabi.lib().ojx_e8t_gemv_grouped_ex(
                 self.table.data_ptr(), self.count, self.total_tiles, self.M, _dtype_code(self.x_dtype),
                 _dtype_code(self.y_dtype), self.needs_reduce,
                 ctypes.addressof(self._peers) if self._peers is not None else None,
-                len(self._peers) if self._peers is not None else 1, self.peer_sync, self.flags, _stream_ptr(self.device))
+                len(self._peers) if self._peers is not None else 1, self.peer_sync, flags, _stream_ptr(self.device))
         _cabi.check(st, "ojx_e8t_gemv_grouped_ex")
