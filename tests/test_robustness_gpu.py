@@ -127,3 +127,37 @@ def test_two_devices_in_one_process(P):
         outs.append(P.ops.linear(x, pk, sc, None, 512, 4096, 32).cpu())
         outs.append(P.ops.linear(x.repeat(8, 1), pk, sc, None, 512, 4096, 32, force="gemm")[:16].cpu())
     assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])
+
+
+def test_independent_launches_overlap_without_changing_results(P):
+    """OJX_GEMV_INDEPENDENT: launches over different matrices with their own activations and outputs never wait for
+    the launch queued ahead of them; their results equal the ordered launches' bit for bit, a dependent reader queued
+    after them sees complete outputs, and the flag is refused together with the cross-GPU ordering flags."""
+    dev = torch.device(DEV)
+    groups, ordered = [], []
+    for i, (n, k, m) in enumerate([(512, 4096, 1), (1024, 14336, 4), (384, 4096, 16), (2048, 4096, 1)]):
+        mats = [_problem(P, n, k, m, 40 + 10 * i + j) for j in range(6)]
+        y_a = torch.zeros((6, m, n), dtype=torch.bfloat16, device=dev)
+        y_b = torch.zeros((6, m, n), dtype=torch.bfloat16, device=dev)
+        groups.append((P.ops.GroupedGemv([(x, pk, sc, None, y_a[j]) for j, (pk, sc, x) in enumerate(mats)], [(n, k)] * 6,
+                                         static_weights=True, independent=True), y_a))
+        ordered.append((P.ops.GroupedGemv([(x, pk, sc, None, y_b[j]) for j, (pk, sc, x) in enumerate(mats)], [(n, k)] * 6), y_b))
+    for grp, _ in ordered:
+        grp()
+    for _ in range(3):                                      # back to back: the tail of one launch is filled by the next
+        for grp, _ in groups:
+            grp()
+    total = sum(y.float().sum() for _, y in groups)         # a dependent reader, queued after the launches
+    torch.cuda.synchronize()
+    for (_, ya), (_, yb) in zip(groups, ordered):
+        assert torch.equal(ya, yb)
+    assert torch.isfinite(total)
+    groups[0][0](independent=False)                         # per-call override back to an ordered launch
+    torch.cuda.synchronize()
+    assert torch.equal(groups[0][1], ordered[0][1])
+    lib = P._cabi.lib()
+    g0 = groups[0][0]
+    sync = torch.zeros(16, dtype=torch.int32, device=dev)
+    st = lib.ojx_e8t_gemv_grouped_ex(g0.table.data_ptr(), g0.count, g0.total_tiles, g0.M, 2, 2, g0.needs_reduce, None, 1,
+                                     sync.data_ptr(), P._cabi.OJX_GEMV_INDEPENDENT | P._cabi.OJX_GEMV_WAIT_PEERS, None)
+    assert st == -9
