@@ -1,9 +1,12 @@
-// Decode GEMV for the 2.0-bit format and ONE activation row on int8 tensor cores, with no lookup table at all.
+// Decode GEMV for the 2.0-bit format and 1..8 activation rows on int8 tensor cores, with no lookup table at all.
 //
-//   y[n] = sum over scale groups of  scale[n, g] * ( sum_k code[n,k] x[k]  -  1.5 * sum_k x[k] )      (+ bias)
+//   y[m, n] = sum over scale groups of  scale[n, g] * ( sum_k code[n,k] x[m,k]  -  1.5 * sum_k x[m,k] )      (+ bias)
 //
 // Replaces the 2.0-bit branch of _FusedE8GEMMFunction.forward (ojasx2/math/lattice.py:596-624) and the native
-// fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444) for one row, group size 32, K % 2048 == 0.
+// fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444) for small batches, group size 32, K % 2048 == 0.
+// With several activation rows the decoded operand registers of a scale group are used once per row (the rows take
+// turns on the same eight accumulator columns), so the decode cost is shared and only MMAs and the per-group scaling
+// repeat.
 //
 // Why this format is cheap: a 32-bit word holds sixteen 2-bit codes, and (word >> 2t) & 0x03030303, t = 0..3, ARE four
 // int8 operand registers of mma.sync.m16n8k32 (codes t, 4+t, 8+t, 12+t in the four bytes) - seven shift/mask
@@ -32,9 +35,9 @@ namespace ojx {
 constexpr int kB2Warps = 8;
 constexpr int kB2Ahead = 3;                       // rounds in flight per warp
 
-__host__ __device__ inline size_t b2_smem_bytes(int K) {
+__host__ __device__ inline size_t b2_smem_bytes(int M, int K) {
     const int rounds = K / 256;
-    return (size_t)rounds * (8 * 32 * 4 + 8 * 4 * 4) + kB2Warps * 16 * 4 * 2 + 16;     // fragments, group factors, partial sums, flag
+    return (size_t)M * rounds * (8 * 32 * 4 + 8 * 4 * 4) + (size_t)M * kB2Warps * 16 * 4 * 2 + 16;   // operands, group factors, partial sums, flag
 }
 
 struct B2Loads {
@@ -42,15 +45,16 @@ struct B2Loads {
     uint32_t sa, sb;                              // their two fp16 scales each
 };
 
+template <int kM>
 __global__ void __launch_bounds__(kB2Warps * 32, 2)
-gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
+gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
                const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype) {
     extern __shared__ __align__(16) uint8_t b2_smem[];
     const int rounds = K / 256;
-    uint32_t* frag = reinterpret_cast<uint32_t*>(b2_smem);                             // [round][digit][word group 0..15][4 words]
-    float* gf = reinterpret_cast<float*>(b2_smem + (size_t)rounds * 8 * 32 * 4);       // [round][group 0..7][ua, ub, -1.5 sum x, pad]
-    float* red = gf + (size_t)rounds * 8 * 4;                                          // [2][warp][16 rows]
-    int* bad_flag = reinterpret_cast<int*>(red + 2 * kB2Warps * 16);
+    uint32_t* frag = reinterpret_cast<uint32_t*>(b2_smem);                             // [m][round][digit][word group 0..15][4 words]
+    float* gf = reinterpret_cast<float*>(b2_smem + (size_t)M * rounds * 8 * 32 * 4);   // [m][round][group 0..7][ua, ub, -1.5 sum x, pad]
+    float* red = gf + (size_t)M * rounds * 8 * 4;                                      // [2][warp][m][16 rows]
+    int* bad_flag = reinterpret_cast<int*>(red + (size_t)2 * kB2Warps * M * 16);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -58,14 +62,16 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
     __syncthreads();
 
     // ---- prologue: fixed-point digits of x in the operand layout, once per CTA ----
-    for (int r = warp; r < rounds; r += kB2Warps) {
+    for (int mr = warp; mr < M * rounds; mr += kB2Warps) {
+        const int xm = mr / rounds, r = mr - xm * rounds;                         // activation row, round
+        const int64_t x0 = (int64_t)xm * K + (int64_t)r * 256 + lane * 8;
         float v[8];                                                               // x is 16-byte aligned: one or two vector loads
         if (x_dtype == OJX_F32) {
-            const float4* src = reinterpret_cast<const float4*>(x) + ((int64_t)r * 256 + lane * 8) / 4;
+            const float4* src = reinterpret_cast<const float4*>(x) + x0 / 4;
             const float4 a = __ldg(src), c = __ldg(src + 1);
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
         } else {
-            const uint4 qv = __ldg(reinterpret_cast<const uint4*>(x) + ((int64_t)r * 256 + lane * 8) / 8);
+            const uint4 qv = __ldg(reinterpret_cast<const uint4*>(x) + x0 / 8);
             const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -114,14 +120,14 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
         // the digit bytes of k = 16 group + c + {0, 4, 8, 12}, exactly the bytes that meet the code bytes of
         // (code word >> 2c) & 0x03030303.  This lane holds k = 8 lane .. 8 lane + 7: values c and c + 4 are the low (even
         // lane) or high (odd lane) half of word (lane >> 1, c).
-        uint16_t* half = reinterpret_cast<uint16_t*>(frag + (size_t)r * 256) + (lane >> 1) * 8 + (lane & 1);
+        uint16_t* half = reinterpret_cast<uint16_t*>(frag + (size_t)mr * 256) + (lane >> 1) * 8 + (lane & 1);
 #pragma unroll
         for (int d = 0; d < 4; ++d)
 #pragma unroll
             for (int c = 0; c < 4; ++c)
                 half[d * 128 + c * 2] = (uint16_t)prmt(dw[d][0], dw[d][1], 0x4040u | (uint32_t)c | ((uint32_t)(4 + c) << 4));
         if (t == 0) {                                                           // lane 4G describes group G of the round
-            float* f = gf + ((size_t)r * 8 + g) * 4;
+            float* f = gf + ((size_t)mr * 8 + g) * 4;
             f[0] = __uint_as_float((uint32_t)(127 - sa) << 23);
             f[1] = __uint_as_float((uint32_t)(127 - sb) << 23);
             f[2] = -1.5f * sum8;
@@ -135,17 +141,19 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
     if (*bad_flag != 0) {
         // Inf / NaN in x: every product in fp32, one warp per weight row
         for (int n = blockIdx.x * kB2Warps + warp; n < N; n += gridDim.x * kB2Warps) {
-            float acc = 0.f;
-            for (int k = lane; k < K; k += 32) {
-                const float w = ((float)((packed[n * row_codes + (k >> 2)] >> (2 * (k & 3))) & 3) - 1.5f) *
-                                __half2float(__ushort_as_half(scales[n * row_scales + (k >> 5)]));
-                acc = fmaf(load_any(x, x_dtype, k), w, acc);
-            }
+            for (int m = 0; m < M; ++m) {
+                float acc = 0.f;
+                for (int k = lane; k < K; k += 32) {
+                    const float w = ((float)((packed[n * row_codes + (k >> 2)] >> (2 * (k & 3))) & 3) - 1.5f) *
+                                    __half2float(__ushort_as_half(scales[n * row_scales + (k >> 5)]));
+                    acc = fmaf(load_any(x, x_dtype, (int64_t)m * K + k), w, acc);
+                }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-            if (lane == 0) {
-                if (bias != nullptr) acc += load_any(bias, x_dtype, n);
-                store_any(y, y_dtype, n, acc);
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+                if (lane == 0) {
+                    if (bias != nullptr) acc += load_any(bias, x_dtype, n);
+                    store_any(y, y_dtype, (int64_t)m * N + n, acc);
+                }
             }
         }
         return;
@@ -185,7 +193,9 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
         if (i < total) fetch(ring[i]);
 
     const bool owner = (g >> 1) == t;
-    float og = 0.f, og8 = 0.f;                      // this warp's partial sums of rows g and g + 8 of the current tile
+    float og[kM], og8[kM];                          // this warp's partial sums of rows g and g + 8 of the current tile, per row of x
+#pragma unroll
+    for (int m = 0; m < kM; ++m) og[m] = og8[m] = 0.f;
     int tiles_done = 0, ti = 0, ri = 0;             // the consumer's position
     for (int64_t it0 = 0; it0 < total; it0 += kB2Ahead) {
 #pragma unroll
@@ -195,58 +205,75 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, const uint8_t* __restric
             const B2Loads L = ring[slot];
             if (it + kB2Ahead < total) fetch(ring[slot]);
             const int r = warp + ri * kB2Warps;
-            // this lane's operand words (owners only): digits 2 (g & 1) and 2 (g & 1) + 1 of word groups 4t .. 4t + 3
-            const uint32_t* xf = frag + (size_t)r * 256 + (size_t)(2 * (g & 1)) * 64 + 16 * t;
             const uint32_t wa[4] = {L.ca.x, L.ca.y, L.ca.z, L.ca.w}, wb[4] = {L.cb.x, L.cb.y, L.cb.z, L.cb.w};
 #pragma unroll
             for (int h = 0; h < 2; ++h) {                                          // scale group 2t + h of the round: words 2h, 2h + 1
-                int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+                // the sixteen operand registers of the group (rows g and g + 8, two words), decoded once for all rows of x
+                uint32_t ar[2][4], br[2][4];
 #pragma unroll
-                for (int qq = 0; qq < 2; ++qq) {
-                    const int q = 2 * h + qq;
-                    uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = make_uint4(0u, 0u, 0u, 0u);
-                    if (owner) {                                                   // words c = 0..3 of the first and the second digit
-                        xa = *reinterpret_cast<const uint4*>(xf + q * 4);
-                        xb = *reinterpret_cast<const uint4*>(xf + 64 + q * 4);
+                for (int qq = 0; qq < 2; ++qq)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        ar[qq][c] = (wa[2 * h + qq] >> (2 * c)) & 0x03030303u;
+                        br[qq][c] = (wb[2 * h + qq] >> (2 * c)) & 0x03030303u;
                     }
-                    const uint32_t a0 = wa[q] & 0x03030303u, a1 = (wa[q] >> 2) & 0x03030303u;
-                    const uint32_t a2 = (wa[q] >> 4) & 0x03030303u, a3 = (wa[q] >> 6) & 0x03030303u;
-                    const uint32_t b0 = wb[q] & 0x03030303u, b1 = (wb[q] >> 2) & 0x03030303u;
-                    const uint32_t b2 = (wb[q] >> 4) & 0x03030303u, b3 = (wb[q] >> 6) & 0x03030303u;
-                    // codes {0,4,8,12} and {1,5,9,13} of the word, then {2,6,10,14} and {3,7,11,15}; c0 / c1: the two digits
-                    mma_s8(c0, a0, b0, a1, b1, xa.x, xa.y);
-                    mma_s8(c1, a0, b0, a1, b1, xb.x, xb.y);
-                    mma_s8(c0, a2, b2, a3, b3, xa.z, xa.w);
-                    mma_s8(c1, a2, b2, a3, b3, xb.z, xb.w);
-                }
-                // column 2t: digits 0 (c0) and 1 (c1); column 2t + 1: digits 2 and 3; rows g (0, 1) and g + 8 (2, 3)
-                const float4 f = *reinterpret_cast<const float4*>(gf + ((size_t)r * 8 + 2 * t + h) * 4);
-                const float sg = fmaf((float)(c0[0] * 128 + c1[0]), 16384.f, (float)(c0[1] * 128 + c1[1]));
-                const float sg8 = fmaf((float)(c0[2] * 128 + c1[2]), 16384.f, (float)(c0[3] * 128 + c1[3]));
                 const float wsa = __half2float(__ushort_as_half((uint16_t)(h ? (L.sa >> 16) : (L.sa & 0xFFFFu))));
                 const float wsb = __half2float(__ushort_as_half((uint16_t)(h ? (L.sb >> 16) : (L.sb & 0xFFFFu))));
-                og = fmaf(wsa, fmaf(sg * f.x, f.y, f.z), og);
-                og8 = fmaf(wsb, fmaf(sg8 * f.x, f.y, f.z), og8);
+#pragma unroll
+                for (int m = 0; m < kM; ++m) {
+                    if (kM > 1 && m >= M) break;
+                    // this lane's operand words (owners only): digits 2 (g & 1) and 2 (g & 1) + 1 of word groups 4t .. 4t + 3
+                    const uint32_t* xf = frag + ((size_t)m * rounds + r) * 256 + (size_t)(2 * (g & 1)) * 64 + 16 * t;
+                    int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int qq = 0; qq < 2; ++qq) {
+                        const int q = 2 * h + qq;
+                        uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = make_uint4(0u, 0u, 0u, 0u);
+                        if (owner) {                                               // words c = 0..3 of the first and the second digit
+                            xa = *reinterpret_cast<const uint4*>(xf + q * 4);
+                            xb = *reinterpret_cast<const uint4*>(xf + 64 + q * 4);
+                        }
+                        // codes {0,4,8,12} and {1,5,9,13} of the word, then {2,6,10,14} and {3,7,11,15}; c0 / c1: the two digits
+                        mma_s8(c0, ar[qq][0], br[qq][0], ar[qq][1], br[qq][1], xa.x, xa.y);
+                        mma_s8(c1, ar[qq][0], br[qq][0], ar[qq][1], br[qq][1], xb.x, xb.y);
+                        mma_s8(c0, ar[qq][2], br[qq][2], ar[qq][3], br[qq][3], xa.z, xa.w);
+                        mma_s8(c1, ar[qq][2], br[qq][2], ar[qq][3], br[qq][3], xb.z, xb.w);
+                    }
+                    // column 2t: digits 0 (c0) and 1 (c1); column 2t + 1: digits 2 and 3; rows g (0, 1) and g + 8 (2, 3)
+                    const float4 f = *reinterpret_cast<const float4*>(gf + (((size_t)m * rounds + r) * 8 + 2 * t + h) * 4);
+                    const float sg = fmaf((float)(c0[0] * 128 + c1[0]), 16384.f, (float)(c0[1] * 128 + c1[1]));
+                    const float sg8 = fmaf((float)(c0[2] * 128 + c1[2]), 16384.f, (float)(c0[3] * 128 + c1[3]));
+                    og[m] = fmaf(wsa, fmaf(sg * f.x, f.y, f.z), og[m]);
+                    og8[m] = fmaf(wsb, fmaf(sg8 * f.x, f.y, f.z), og8[m]);
+                }
             }
             if (ri == my_rounds - 1) {
                 // the warp's last round of this tile: combine the four lane quarters, park, and let warp 0 add the warps
-                og += __shfl_xor_sync(0xFFFFFFFFu, og, 1);
-                og8 += __shfl_xor_sync(0xFFFFFFFFu, og8, 1);
-                og += __shfl_xor_sync(0xFFFFFFFFu, og, 2);
-                og8 += __shfl_xor_sync(0xFFFFFFFFu, og8, 2);
-                float* mybuf = red + ((size_t)(tiles_done & 1) * kB2Warps + warp) * 16;
-                if (t == 0) { mybuf[g] = og; mybuf[g + 8] = og8; }
-                og = og8 = 0.f;
-                asm volatile("bar.sync 1, %0;" ::"r"(kB2Warps * 32) : "memory");       // every warp reaches its tile ends in the same order
-                if (warp == 0 && lane < 16) {
-                    const int tile = blockIdx.x + ti * gridDim.x, n = tile * 16 + lane;
-                    if (n < N) {
-                        const float* b = red + (size_t)(tiles_done & 1) * kB2Warps * 16 + lane;
-                        float sum = 0.f;
+                float* mybuf = red + ((size_t)(tiles_done & 1) * kB2Warps + warp) * M * 16;
 #pragma unroll
-                        for (int w = 0; w < kB2Warps; ++w) sum += b[w * 16];           // the host only launches with rounds % 8 == 0
-                        if (bias != nullptr) sum += load_any(bias, x_dtype, n);
-                        store_any(y, y_dtype, n, sum);
+                for (int m = 0; m < kM; ++m) {
+                    if (kM > 1 && m >= M) break;
+                    float a = og[m], b = og8[m];
+                    a += __shfl_xor_sync(0xFFFFFFFFu, a, 1);
+                    b += __shfl_xor_sync(0xFFFFFFFFu, b, 1);
+                    a += __shfl_xor_sync(0xFFFFFFFFu, a, 2);
+                    b += __shfl_xor_sync(0xFFFFFFFFu, b, 2);
+                    if (t == 0) { mybuf[m * 16 + g] = a; mybuf[m * 16 + g + 8] = b; }
+                    og[m] = og8[m] = 0.f;
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(kB2Warps * 32) : "memory");       // every warp reaches its tile ends in the same order
+                if (warp == 0) {
+                    const int tile = blockIdx.x + ti * gridDim.x;
+                    for (int e = lane; e < M * 16; e += 32) {                           // element (m, row) of the tile
+                        const int m = e >> 4, n = tile * 16 + (e & 15);
+                        if (n < N) {
+                            const float* b = red + (size_t)(tiles_done & 1) * kB2Warps * M * 16 + e;
+                            float sum = 0.f;
+#pragma unroll
+                            for (int w = 0; w < kB2Warps; ++w) sum += b[(size_t)w * M * 16];   // the host only launches with rounds % 8 == 0
+                            if (bias != nullptr) sum += load_any(bias, x_dtype, n);
+                            store_any(y, y_dtype, (int64_t)m * N + n, sum);
+                        }
                     }
                 }
                 ++tiles_done;

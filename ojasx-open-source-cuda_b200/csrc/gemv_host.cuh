@@ -234,18 +234,26 @@ int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, cons
     OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0 || group <= 0 || group % 8 != 0, OJX_ERR_SHAPE);
     OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
-    // one row of the 2.0-bit format with groups of 32 and K a multiple of 2048: int8 tensor cores, no table
-    if (bits == 2 && M == 1 && group == 32 && K % 2048 == 0 && K <= (1 << 20) && N < (1 << 30) &&
+    // up to eight rows of the 2.0-bit format with groups of 32 and K a multiple of 2048: int8 tensor cores, no table
+    if (bits == 2 && M >= 1 && M <= 8 && group == 32 && K % 2048 == 0 && K <= (1 << 20) && N < (1 << 30) &&
+        b2_smem_bytes((int)M, (int)K) <= 200 * 1024 &&
         ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(scales) & 3) == 0) {
-        static std::atomic<uint64_t> configured{0};
-        const size_t smem = b2_smem_bytes((int)K);
-        const int32_t sc = ensure_dynamic_smem(gemv_b2_kernel, 200 * 1024, configured);
-        OJX_RETURN_IF(sc != OJX_OK, sc);
+        const size_t smem = b2_smem_bytes((int)M, (int)K);
         const int tiles = (int)((N + 15) / 16);
-        const int grid = tiles < 2 * num_sms() ? tiles : 2 * num_sms();
-        gemv_b2_kernel<<<grid, kB2Warps * 32, smem, s>>>(x, x_dtype, packed, scales, bias, (int)N, (int)K, y, y_dtype);
-        return launch_status();
+        const int ctas = (smem <= 100 * 1024 ? 2 : 1) * num_sms();          // two CTAs per SM while the operands of x leave room
+        const int grid = tiles < ctas ? tiles : ctas;
+        auto run = [&](auto kernel, std::atomic<uint64_t>& done) -> int32_t {
+            const int32_t sc = ensure_dynamic_smem(kernel, 200 * 1024, done);
+            OJX_RETURN_IF(sc != OJX_OK, sc);
+            kernel<<<grid, kB2Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
+            return launch_status();
+        };
+        static std::atomic<uint64_t> d1{0}, d2{0}, d4{0}, d8{0};
+        if (M == 1) return run(gemv_b2_kernel<1>, d1);
+        if (M == 2) return run(gemv_b2_kernel<2>, d2);
+        if (M <= 4) return run(gemv_b2_kernel<4>, d4);
+        return run(gemv_b2_kernel<8>, d8);
     }
     int32_t st = OJX_OK;                                      // small batches: the shared-memory kernel when x fits
     if (bits == 2 ? launch_lowbit_gemv<2>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, s, &st)
