@@ -833,7 +833,7 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
             out["e8_projection"][name] = {"ms": ms, "GBps": gbs, "frac_hbm": gbs / hbm_peak}
         del v
         # the 2.0-bit sibling format: packer and unpacker on the same matrix (2 B in + 0.25 B codes + scales out, and back),
-        # and its fused fp32 linear on one 4096 x 4096 matrix at one activation row (a correctness path, not tensor cores)
+        # and its fused linear on one 4096 x 4096 matrix at one activation row
         two = {"rows": n, "cols": k, "dtype": "f16"}
         for g in (8, 32):
             p2 = torch.empty(n * k // 4, dtype=torch.uint8, device=dev)
@@ -874,6 +874,22 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
         one["encode"] = {"ms": ms, "GBps": n * k * bpw1 / (ms * 1e-3) / 1e9, "frac_hbm": n * k * bpw1 / (ms * 1e-3) / 1e9 / hbm_peak}
         ms = timed(lambda: ops.decode_1bit(p1, s1, (n, k), torch.float16), 3)
         one["decode"] = {"ms": ms, "GBps": n * k * bpw1 / (ms * 1e-3) / 1e9, "frac_hbm": n * k * bpw1 / (ms * 1e-3) / 1e9 / hbm_peak}
+        # four distinct 14336 x 4096 matrices back to back (cold weights), one and four activation rows
+        for rows_x in (1, 4):
+            xr = ops.generate(rows_x * 4096, 9, 1.0, torch.bfloat16, dev).view(rows_x, 4096)
+            per = 14336 * 4096
+            def four1():
+                for j in range(4):
+                    ops.linear_1bit(xr, p1[j * per // 8: (j + 1) * per // 8], s1[j * per // 32: (j + 1) * per // 32], None, 14336, 4096, 32)
+            four1()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                four1()
+            ms = timed(graph.replay, 3) / 4
+            del graph
+            gbs = per * (0.125 + 2.0 / 32) / (ms * 1e-3) / 1e9
+            one[f"linear_14336x4096_{rows_x}row"] = {"ms": ms, "packed_GBps": gbs, "frac_hbm": gbs / hbm_peak}
         out["one_bit"] = one
         del p1, s1
         ops.encode(w, 32, out=(pk, sc))

@@ -121,10 +121,12 @@ int32_t ojx_e8t_fwht32(const void* x, int32_t dtype, int64_t count, void* out, v
  *   ojx_e8t_linear_2bit   y[M, N] = x[M, K] . W^T (+ bias) from the packed codes in one fp32 kernel (any shape,
  *                         any of the three dtypes for x, bias (x's dtype) and y); replaces the 2.0-bit branch of
  *                         _FusedE8GEMMFunction.forward (ojasx2/math/lattice.py:596-624) and the native
- *                         fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444).  One row with group 32
- *                         and K % 2048 == 0 runs on int8 tensor cores (activations as 28-bit fixed point per scale
- *                         group, as in ojx_e8t_gemv for one bf16 row); up to eight rows with K % 16 == 0 and 16-byte
- *                         aligned x run a shared-memory fp32 kernel, everything else a scalar fp32 kernel.
+ *                         fused_e8_gemm_forward<T> (ojasx2/math/csrc/ojasx_math_core.hpp:444).  One to eight rows
+ *                         with group 32, K % 2048 == 0 and 16-byte aligned operands run on int8 tensor cores
+ *                         (activations as 28-bit fixed point per scale group, as in ojx_e8t_gemv for one bf16 row;
+ *                         Inf / NaN in x give the dense product's pattern); other shapes of up to eight rows with
+ *                         K % 16 == 0 and 16-byte aligned x run a shared-memory fp32 kernel (a row of x with Inf
+ *                         comes out as NaN there), everything else a scalar fp32 kernel.
  */
 int32_t ojx_e8t_encode_2bit(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
                             uint8_t* packed_out, uint16_t* scales_out, void* stream);
@@ -143,7 +145,9 @@ int32_t ojx_e8t_linear_2bit(const void* x, int32_t x_dtype, int64_t M, const uin
  *                         torch.sum adds chunks of eight into four vector accumulators in turn; a BLAS that rounds the
  *                         8-term dot products differently may pick the other of two nearly equal candidates.
  *   ojx_e8t_decode_1bit   replaces RootE8LatticePacker.unpack (ojasx2/math/lattice.py:514-537)
- *   ojx_e8t_linear_1bit   y = x . W^T (+ bias) from the codes, one fused fp32 kernel (correctness path, as for 2 bits)
+ *   ojx_e8t_linear_1bit   y = x . W^T (+ bias) from the codes; the same three kernels as for 2 bits: int8 tensor
+ *                         cores for one to eight rows with group 32 and K % 2048 == 0 (a code byte is looked up as
+ *                         eight int8 operand bytes), the shared-memory fp32 kernel, the scalar fp32 kernel
  */
 int32_t ojx_e8t_encode_1bit(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
                             uint8_t* packed_out, uint16_t* scales_out, void* stream);

@@ -54,14 +54,49 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
     uint32_t* frag = reinterpret_cast<uint32_t*>(b2_smem);                             // [m][round][digit][word group 0..15][4 words]
     float* gf = reinterpret_cast<float*>(b2_smem + (size_t)M * rounds * 8 * 32 * 4);   // [m][round][group 0..7][ua, ub, -1.5 sum x, pad]
     float* red = gf + (size_t)M * rounds * 8 * 4;                                      // [2][warp][m][16 rows]
-    int* bad_flag = reinterpret_cast<int*>(red + (size_t)2 * kB2Warps * M * 16);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    if (tid == 0) *bad_flag = 0;
-    __syncthreads();
+
+    const int tiles = (N + 15) / 16;
+    const int64_t row_codes = K / 4, row_scales = K / 32;
+    // ---- this warp's (tile, round) pairs in order, kB2Ahead of them in flight: the first loads are issued before the
+    // prologue, whose shared-memory work then hides their latency ----
+    const int my_rounds = (rounds - warp + kB2Warps - 1) / kB2Warps;              // rounds warp, warp + 8, ...
+    const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int64_t total = (int64_t)my_tiles * my_rounds;
+    // The fetcher and the consumer each walk the (tile, round) pairs with their own counters: no divisions, 32-bit offsets
+    // from two row pointers that move once per tile.
+    int f_ti = 0, f_ri = 0;
+    const uint8_t* f_ca = nullptr; const uint8_t* f_cb = nullptr;
+    const uint16_t* f_sa = nullptr; const uint16_t* f_sb = nullptr;
+    auto fetch_rows = [&]() {
+        const int tile = blockIdx.x + f_ti * gridDim.x;
+        const int na = min(tile * 16 + g, N - 1), nb = min(tile * 16 + g + 8, N - 1);     // rows beyond N re-read the last row
+        f_ca = packed + na * row_codes + t * 16; f_cb = packed + nb * row_codes + t * 16;
+        f_sa = scales + na * row_scales + t * 2; f_sb = scales + nb * row_scales + t * 2;
+    };
+    auto fetch = [&](B2Loads& L) {
+        const int r = warp + f_ri * kB2Warps;
+        L.ca = __ldg(reinterpret_cast<const uint4*>(f_ca + r * 64));
+        L.cb = __ldg(reinterpret_cast<const uint4*>(f_cb + r * 64));
+        L.sa = __ldg(reinterpret_cast<const uint32_t*>(f_sa + r * 8));
+        L.sb = __ldg(reinterpret_cast<const uint32_t*>(f_sb + r * 8));
+        if (++f_ri == my_rounds) {
+            f_ri = 0;
+            ++f_ti;
+            if (f_ti < my_tiles) fetch_rows();
+        }
+    };
+    B2Loads ring[kB2Ahead];
+    if (total > 0) fetch_rows();
+#pragma unroll
+    for (int i = 0; i < kB2Ahead; ++i)
+        if (i < total) fetch(ring[i]);
 
     // ---- prologue: fixed-point digits of x in the operand layout, once per CTA ----
+    bool any_bad = false;                                                         // Inf or NaN seen by this warp
+#pragma unroll 2
     for (int mr = warp; mr < M * rounds; mr += kB2Warps) {
         const int xm = mr / rounds, r = mr - xm * rounds;                         // activation row, round
         const int64_t x0 = (int64_t)xm * K + (int64_t)r * 256 + lane * 8;
@@ -94,7 +129,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
             else amax = max(amax, mag);
             sum8 += v[i];
         }
-        if (__any_sync(0xFFFFFFFFu, bad) && lane == 0) *bad_flag = 1;
+        any_bad |= bad;
         amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
         amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));                 // the four lanes of a group
         sum8 += __shfl_xor_sync(0xFFFFFFFFu, sum8, 1);
@@ -134,11 +169,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
             f[3] = 0.f;
         }
     }
-    __syncthreads();
-
-    const int tiles = (N + 15) / 16;
-    const int64_t row_codes = K / 4, row_scales = K / 32;
-    if (*bad_flag != 0) {
+    if (__syncthreads_or(any_bad)) {
         // Inf / NaN in x: every product in fp32, one warp per weight row
         for (int n = blockIdx.x * kB2Warps + warp; n < N; n += gridDim.x * kB2Warps) {
             for (int m = 0; m < M; ++m) {
@@ -159,38 +190,6 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
         return;
     }
 
-    // ---- main loop: this warp's (tile, round) pairs in order, kB2Ahead of them in flight ----
-    const int my_rounds = (rounds - warp + kB2Warps - 1) / kB2Warps;              // rounds warp, warp + 8, ...
-    const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const int64_t total = (int64_t)my_tiles * my_rounds;
-    // The fetcher and the consumer each walk the (tile, round) pairs with their own counters: no divisions, 32-bit offsets
-    // from two row pointers that move once per tile.
-    int f_ti = 0, f_ri = 0;
-    const uint8_t* f_ca = nullptr; const uint8_t* f_cb = nullptr;
-    const uint16_t* f_sa = nullptr; const uint16_t* f_sb = nullptr;
-    auto fetch_rows = [&]() {
-        const int tile = blockIdx.x + f_ti * gridDim.x;
-        const int na = min(tile * 16 + g, N - 1), nb = min(tile * 16 + g + 8, N - 1);     // rows beyond N re-read the last row
-        f_ca = packed + na * row_codes + t * 16; f_cb = packed + nb * row_codes + t * 16;
-        f_sa = scales + na * row_scales + t * 2; f_sb = scales + nb * row_scales + t * 2;
-    };
-    auto fetch = [&](B2Loads& L) {
-        const int r = warp + f_ri * kB2Warps;
-        L.ca = __ldg(reinterpret_cast<const uint4*>(f_ca + r * 64));
-        L.cb = __ldg(reinterpret_cast<const uint4*>(f_cb + r * 64));
-        L.sa = __ldg(reinterpret_cast<const uint32_t*>(f_sa + r * 8));
-        L.sb = __ldg(reinterpret_cast<const uint32_t*>(f_sb + r * 8));
-        if (++f_ri == my_rounds) {
-            f_ri = 0;
-            ++f_ti;
-            if (f_ti < my_tiles) fetch_rows();
-        }
-    };
-    B2Loads ring[kB2Ahead];
-    if (total > 0) fetch_rows();
-#pragma unroll
-    for (int i = 0; i < kB2Ahead; ++i)
-        if (i < total) fetch(ring[i]);
 
     const bool owner = (g >> 1) == t;
     float og[kM], og8[kM];                          // this warp's partial sums of rows g and g + 8 of the current tile, per row of x

@@ -592,34 +592,37 @@ def test_low_bit_decode_linear_matches_dense_product(P, oracle, bits, m, k, n, g
                                       (1, 8192, 17, torch.float32), (2, 4096, 100, torch.bfloat16), (3, 2048, 33, torch.float16),
                                       (4, 8192, 64, torch.bfloat16), (5, 2048, 48, torch.float32), (8, 4096, 4096, torch.bfloat16),
                                       (7, 4096, 20, torch.float16)])
-def test_two_bit_tensor_core_kernel(P, oracle, m, k, n, dt):
-    """gemv_b2_kernel (one to eight rows, groups of 32, K % 2048 == 0) against the dense fp32 product: within 1e-5 of
+@pytest.mark.parametrize("bits", [2, 1])
+def test_low_bit_tensor_core_kernels(P, oracle, bits, m, k, n, dt):
+    """gemv_b2_kernel / gemv_b1_kernel (one to eight rows, groups of 32, K % 2048 == 0) against the dense fp32 product: within 1e-5 of
     sum |x||w| per output (row counts that are not multiples of 16 included), outliers do not hurt their neighbours,
     scaling x by a power of two scales y exactly, Inf / NaN give the dense product's pattern and leave the other rows
     of x within the same bound."""
     dev = torch.device(DEV)
     w = torch.from_numpy(oracle.gen_normal(950 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
-    pk, sc = P.ops.encode_2bit(w, 32)
-    wd = P.ops.decode_2bit(pk, sc, (n, k), torch.float32)
+    enc, dec, lin = ((P.ops.encode_2bit, P.ops.decode_2bit, P.ops.linear_2bit) if bits == 2
+                     else (P.ops.encode_1bit, P.ops.decode_1bit, P.ops.linear_1bit))
+    pk, sc = enc(w, 32)
+    wd = dec(pk, sc, (n, k), torch.float32)
     x = torch.from_numpy(oracle.gen_normal(951 + m, m * k, 1.0).reshape(m, k).copy()).to(dt).to(dev)
     for r in range(m):
         x[r, 7 + r::256] *= 1.0e3                                    # one outlier per 256-wide round
         x[r] *= 2.0 ** (r - 4 if dt == torch.float16 else 2 * r)     # every row on its own scale
     bias = torch.from_numpy(oracle.gen_normal(952, n, 0.1).copy()).to(dt).to(dev)
-    y = P.ops.linear_2bit(x, pk, sc, bias, n, k, 32, out_dtype=torch.float32)
+    y = lin(x, pk, sc, bias, n, k, 32, out_dtype=torch.float32)
     ref = x.float() @ wd.t() + bias.float()
     budget = x.float().abs() @ wd.abs().t() + bias.float().abs()
     assert float(((y - ref).abs() / budget).max()) < 1e-5
-    y0 = P.ops.linear_2bit(x, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+    y0 = lin(x, pk, sc, None, n, k, 32, out_dtype=torch.float32)
     for s in (-30, 20):
         if dt == torch.float16:
             continue                                                 # would leave fp16's range
-        ys = P.ops.linear_2bit(x * 2.0 ** s, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+        ys = lin(x * 2.0 ** s, pk, sc, None, n, k, 32, out_dtype=torch.float32)
         assert torch.equal(ys, y0 * 2.0 ** s), s
     xi = x.clone()
     xi[0, 5] = float("inf")
     xi[m - 1, k - 1] = float("-inf")
-    yi = P.ops.linear_2bit(xi, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+    yi = lin(xi, pk, sc, None, n, k, 32, out_dtype=torch.float32)
     ri = xi.float() @ wd.t()
     assert torch.equal(torch.isnan(yi), torch.isnan(ri)) and torch.equal(torch.isposinf(yi), torch.isposinf(ri))
     assert torch.equal(torch.isneginf(yi), torch.isneginf(ri))
@@ -628,5 +631,5 @@ def test_two_bit_tensor_core_kernel(P, oracle, m, k, n, dt):
         assert float((((yi - ri).abs() / (budget - bias.float().abs()))[fin]).max()) < 1e-5
     xn = x.clone()
     xn[m // 2, 100] = float("nan")
-    yn = P.ops.linear_2bit(xn, pk, sc, None, n, k, 32, out_dtype=torch.float32)
+    yn = lin(xn, pk, sc, None, n, k, 32, out_dtype=torch.float32)
     assert torch.isnan(yn[m // 2]).all() and int(torch.isnan(yn).sum()) == n
