@@ -14,9 +14,10 @@
 // access then read sixteen different bank pairs whatever their codes are (one copy measured 55 % of all shared-memory
 // wavefronts as bank conflicts).
 //
-// Work decomposition as in the 2.0-bit kernel: a CTA of 8 warps takes tiles of 16 weight rows; the 256-wide rounds of K
-// are dealt to the warps in turn.  A round's 32 code bytes and 8 scales per row (768 bytes for the 16 rows) travel by
-// 16-byte cp.async copies into a ring in shared memory that belongs to the warp alone (four rounds in flight, no
+// Work decomposition as in the 2.0-bit kernel: one CTA per SM, two groups of 8 warps that take tiles of 16 weight rows
+// independently and share the table and the operands of x; the 256-wide rounds of K are dealt to a group's warps in
+// turn.  A round's 32 code bytes and 8 scales per row (768 bytes for the 16 rows) travel by
+// 16-byte cp.async copies into a ring in shared memory that belongs to the warp alone (three rounds in flight, no
 // registers held by loads in flight, no CTA-wide synchronisation); the four lanes of a quad then read the same 32
 // bytes and each uses its own byte of every group.
 //
@@ -32,16 +33,17 @@
 
 namespace ojx {
 
-constexpr int kB1Warps = 8;
-constexpr int kB1Ahead = 4;                       // rounds in flight per warp
+constexpr int kB1Warps = 8;                       // warps of a tile group
+constexpr int kB1Groups = 2;                      // tile groups of a CTA
+constexpr int kB1Ahead = 3;                       // rounds in flight per warp
 constexpr int kB1RoundBytes = 16 * 32 + 16 * 16;  // one round of a 16-row tile: code bytes, then scales
 
 __host__ __device__ inline size_t b1_smem_bytes(int cbs, int copies, int K) {      // cbs: column blocks (pairs of activation rows)
     const int rounds = K / 256;
     // operands [cb][round][group pair][lane][32 B], group factors [2 cb][round][parity][group] x 4 B, table copies, the
-    // warps' rings, partial sums, flag
+    // warps' rings, partial sums
     return (size_t)cbs * rounds * 2048 + (size_t)2 * cbs * rounds * 64 + (size_t)2048 * copies +
-           (size_t)kB1Warps * kB1Ahead * kB1RoundBytes + (size_t)2 * kB1Warps * 2 * cbs * 16 * 4 + 16;
+           (size_t)kB1Groups * kB1Warps * kB1Ahead * kB1RoundBytes + (size_t)kB1Groups * 2 * kB1Warps * 2 * cbs * 16 * 4;
 }
 
 // D = A . B with a zero accumulator operand: no registers to clear before the instruction.
@@ -52,7 +54,7 @@ __device__ __forceinline__ void mma_s8_from_zero(int (&d)[4], uint32_t a0, uint3
 
 
 template <int kCB, int kB1Copies>                 // column blocks (pairs of activation rows); copies of the code table (16 or 8)
-__global__ void __launch_bounds__(kB1Warps * 32, kCB == 4 ? 1 : 2)
+__global__ void __launch_bounds__(kB1Groups * kB1Warps * 32, 1)
 gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
                const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype) {
     extern __shared__ __align__(16) uint8_t b1_smem[];
@@ -61,24 +63,27 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
     float* gf = reinterpret_cast<float*>(b1_smem + (size_t)kCB * rounds * 2048);       // [m < 2 kCB][round][parity][group]
     uint2* lut = reinterpret_cast<uint2*>(gf + (size_t)2 * kCB * rounds * 16);         // slot 16 code + copy -> coordinates 0-3, 4-7
     uint8_t* rings = reinterpret_cast<uint8_t*>(lut + 256 * kB1Copies);                // [warp][slot][768 B]
-    float* red = reinterpret_cast<float*>(rings + kB1Warps * kB1Ahead * kB1RoundBytes);   // [2][warp][m < 2 kCB][16 rows]
+    float* red_all = reinterpret_cast<float*>(rings + kB1Groups * kB1Warps * kB1Ahead * kB1RoundBytes);   // [group][2][warp][m < 2 kCB][16 rows]
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int cta_warp = tid >> 5, grp = cta_warp >> 3, warp = cta_warp & (kB1Warps - 1);   // warp: index inside its tile group
+    float* red = red_all + (size_t)grp * 2 * kB1Warps * 2 * kCB * 16;
+    const int first_tile = blockIdx.x * kB1Groups + grp, tile_step = gridDim.x * kB1Groups;   // this group's tiles
     const int g = lane >> 2, t = lane & 3;
     const int tiles = (N + 15) / 16;
     const int64_t row_codes = K / 8, row_scales = K / 32;
     // ---- this warp's (tile, round) pairs in order, kB1Ahead of them in flight: the first loads are issued before the
     // prologue, whose shared-memory work then hides their latency ----
     const int my_rounds = (rounds - warp + kB1Warps - 1) / kB1Warps;              // rounds warp, warp + 8, ...
-    const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int my_tiles = first_tile < tiles ? (tiles - first_tile + tile_step - 1) / tile_step : 0;
     const int64_t total = (int64_t)my_tiles * my_rounds;
     int f_ti = 0, f_ri = 0;                                                       // the fetcher's position
     // lane l copies half l & 1 of the code bytes of tile row l >> 1, and (lanes 0-15) the scales of tile row l
     const uint8_t* f_code = nullptr;
     const uint16_t* f_scale = nullptr;
-    const uint32_t ring0 = smem_u32(rings + warp * kB1Ahead * kB1RoundBytes);
+    const uint32_t ring0 = smem_u32(rings + cta_warp * kB1Ahead * kB1RoundBytes);
     auto fetch_rows = [&]() {
-        const int tile = blockIdx.x + f_ti * gridDim.x;
+        const int tile = first_tile + f_ti * tile_step;
         const int nc = min(tile * 16 + (lane >> 1), N - 1), ns = min(tile * 16 + (lane & 15), N - 1);   // rows beyond N re-read the last row
         f_code = packed + nc * row_codes + (lane & 1) * 16;
         f_scale = scales + ns * row_scales;
@@ -101,7 +106,7 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
 #pragma unroll
     for (int i = 0; i < kB1Ahead; ++i) fetch(i);
 
-    {   // thread `tid` writes all copies of code `tid`, starting at a copy that depends on the code: sixteen lanes, sixteen bank pairs
+    if (tid < 256) {   // thread `tid` writes all copies of code `tid`, starting at a copy that depends on the code: sixteen lanes, sixteen bank pairs
         const uint2 entry = make_uint2(g_root_coords[2 * tid], g_root_coords[2 * tid + 1]);
 #pragma unroll
         for (int c = 0; c < kB1Copies; ++c) lut[tid * kB1Copies + ((c + tid) & (kB1Copies - 1))] = entry;
@@ -111,7 +116,7 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
     // k = 8 l .. 8 l + 7 of the round: group l >> 2, quarter l & 3 - one 64-bit operand cell per digit. ----
     bool any_bad = false;                                                         // Inf or NaN seen by this warp
 #pragma unroll 2
-    for (int mr = warp; mr < 2 * kCB * rounds; mr += kB1Warps) {
+    for (int mr = cta_warp; mr < 2 * kCB * rounds; mr += kB1Groups * kB1Warps) {
         const int xm = mr / rounds, r = mr - xm * rounds;                         // activation row, round
         uint32_t dw[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};             // [digit][values 0-3, 4-7] as int8 x 4
         float f0 = 0.f;
@@ -152,16 +157,20 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
             const int sa = shift >> 1, sb = shift - sa;
             const float fa = __uint_as_float((uint32_t)(127 + sa) << 23), fb = __uint_as_float((uint32_t)(127 + sb) << 23);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int q0 = __float2int_rn(v[i] * fa * fb);
-                const int q1 = (q0 + 64) >> 7, d3 = q0 - (q1 << 7);
-                const int q2 = (q1 + 64) >> 7, d2 = q1 - (q2 << 7);
-                const int d0 = (q2 + 64) >> 7, d1 = q2 - (d0 << 7);
-                const int sh = 8 * (i & 3);
-                dw[0][i >> 2] |= (uint32_t)(d0 & 0xFF) << sh;
-                dw[1][i >> 2] |= (uint32_t)(d1 & 0xFF) << sh;
-                dw[2][i >> 2] |= (uint32_t)(d2 & 0xFF) << sh;
-                dw[3][i >> 2] |= (uint32_t)(d3 & 0xFF) << sh;
+            for (int h = 0; h < 2; ++h) {                                           // values 4h .. 4h + 3: one operand word per digit
+                int dg[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int q0 = __float2int_rn(v[4 * h + j] * fa * fb);
+                    const int q1 = (q0 + 64) >> 7, q2 = (q1 + 64) >> 7;
+                    dg[0][j] = (q2 + 64) >> 7;
+                    dg[1][j] = q2 - (dg[0][j] << 7);
+                    dg[2][j] = q1 - (q2 << 7);
+                    dg[3][j] = q0 - (q1 << 7);
+                }
+#pragma unroll
+                for (int d = 0; d < 4; ++d)                                            // low bytes of four integers into one word
+                    dw[d][h] = prmt(prmt((uint32_t)dg[d][0], (uint32_t)dg[d][1], 0x0040u), prmt((uint32_t)dg[d][2], (uint32_t)dg[d][3], 0x0040u), 0x5410u);
             }
             f0 = __uint_as_float(shift <= 126 ? (uint32_t)(127 - shift) << 23 : 1u << (149 - shift));   // 2^-shift, exact
         }
@@ -178,7 +187,7 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
     if (__syncthreads_or(any_bad)) {
         asm volatile("cp.async.wait_all;" ::: "memory");                           // nothing of this thread is still in flight into shared memory
         // Inf / NaN in x: every product in fp32, one warp per weight row
-        for (int n = blockIdx.x * kB1Warps + warp; n < N; n += gridDim.x * kB1Warps) {
+        for (int n = blockIdx.x * kB1Groups * kB1Warps + cta_warp; n < N; n += gridDim.x * kB1Groups * kB1Warps) {
             for (int m = 0; m < M; ++m) {
                 float acc = 0.f;
                 for (int k = lane; k < K; k += 32) {
@@ -213,7 +222,7 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
             // this round has landed when at most kB1Ahead - 1 newer groups are pending; the copies were made by other lanes
             asm volatile("cp.async.wait_group %0;" ::"n"(kB1Ahead - 1) : "memory");
             __syncwarp();
-            const uint8_t* rs = rings + (warp * kB1Ahead + slot) * kB1RoundBytes;
+            const uint8_t* rs = rings + (cta_warp * kB1Ahead + slot) * kB1RoundBytes;
             const uint4 ca0 = *reinterpret_cast<const uint4*>(rs + g * 32), ca1 = *reinterpret_cast<const uint4*>(rs + g * 32 + 16);
             const uint4 cb0 = *reinterpret_cast<const uint4*>(rs + (g + 8) * 32), cb1 = *reinterpret_cast<const uint4*>(rs + (g + 8) * 32 + 16);
             const uint4 sva = *reinterpret_cast<const uint4*>(rs + 512 + g * 16), svb = *reinterpret_cast<const uint4*>(rs + 512 + (g + 8) * 16);
@@ -268,9 +277,9 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
                     }
                     og[cb] = og8[cb] = 0.f;
                 }
-                asm volatile("bar.sync 1, %0;" ::"r"(kB1Warps * 32) : "memory");       // every warp reaches its tile ends in the same order
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(kB1Warps * 32) : "memory");   // the group's warps reach their tile ends in the same order
                 if (warp == 0) {
-                    const int tile = blockIdx.x + ti * gridDim.x;
+                    const int tile = first_tile + ti * tile_step;
                     for (int e = lane; e < M * 16; e += 32) {                           // element (m, row) of the tile
                         const int m = e >> 4, n = tile * 16 + (e & 15);
                         if (n < N) {

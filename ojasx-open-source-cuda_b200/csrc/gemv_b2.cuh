@@ -13,7 +13,9 @@
 // operations per sixteen weights, no table, no permute.  The order of k inside an MMA does not matter as long as the
 // activation operand uses the same order, and a word never crosses a scale group.
 //
-// Work decomposition: a CTA of 8 warps takes tiles of 16 weight rows; the 256-wide rounds of K are dealt to the warps
+// Work decomposition: a CTA is two groups of 8 warps, one CTA per SM; each group takes tiles of 16 weight rows on its
+// own (its own named barrier and partial-sum buffers), while the operands of x are built once by all sixteen warps and
+// shared.  Inside a group the 256-wide rounds of K are dealt to the warps
 // in turn (round r to warp r mod 8), so one tile's codes are read by all eight warps at once, 64 contiguous bytes per
 // row and round, straight from global memory into registers (three rounds in flight per warp; no shared-memory ring is
 // needed because nothing is shared between rows).  Lane (g, t) owns rows g and g + 8 and the 64 codes 64t..64t+63 of
@@ -32,12 +34,13 @@
 
 namespace ojx {
 
-constexpr int kB2Warps = 8;
+constexpr int kB2Warps = 8;                       // warps of a tile group
+constexpr int kB2Groups = 2;                      // tile groups of a CTA
 constexpr int kB2Ahead = 3;                       // rounds in flight per warp
 
 __host__ __device__ inline size_t b2_smem_bytes(int M, int K) {
     const int rounds = K / 256;
-    return (size_t)M * rounds * (8 * 32 * 4 + 8 * 4 * 4) + (size_t)M * kB2Warps * 16 * 4 * 2 + 16;   // operands, group factors, partial sums, flag
+    return (size_t)M * rounds * (8 * 32 * 4 + 8 * 4 * 4) + (size_t)kB2Groups * M * kB2Warps * 16 * 4 * 2;   // operands, group factors, partial sums
 }
 
 struct B2Loads {
@@ -46,16 +49,19 @@ struct B2Loads {
 };
 
 template <int kM>
-__global__ void __launch_bounds__(kB2Warps * 32, 2)
+__global__ void __launch_bounds__(kB2Groups * kB2Warps * 32, 1)
 gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
                const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype) {
     extern __shared__ __align__(16) uint8_t b2_smem[];
     const int rounds = K / 256;
     uint32_t* frag = reinterpret_cast<uint32_t*>(b2_smem);                             // [m][round][digit][word group 0..15][4 words]
     float* gf = reinterpret_cast<float*>(b2_smem + (size_t)M * rounds * 8 * 32 * 4);   // [m][round][group 0..7][ua, ub, -1.5 sum x, pad]
-    float* red = gf + (size_t)M * rounds * 8 * 4;                                      // [2][warp][m][16 rows]
+    float* red_all = gf + (size_t)M * rounds * 8 * 4;                                  // [group][2][warp][m][16 rows]
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int cta_warp = tid >> 5, grp = cta_warp >> 3, warp = cta_warp & (kB2Warps - 1);   // warp: index inside its tile group
+    float* red = red_all + (size_t)grp * 2 * kB2Warps * M * 16;
+    const int first_tile = blockIdx.x * kB2Groups + grp, tile_step = gridDim.x * kB2Groups;   // this group's tiles
     const int g = lane >> 2, t = lane & 3;
 
     const int tiles = (N + 15) / 16;
@@ -63,7 +69,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
     // ---- this warp's (tile, round) pairs in order, kB2Ahead of them in flight: the first loads are issued before the
     // prologue, whose shared-memory work then hides their latency ----
     const int my_rounds = (rounds - warp + kB2Warps - 1) / kB2Warps;              // rounds warp, warp + 8, ...
-    const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int my_tiles = first_tile < tiles ? (tiles - first_tile + tile_step - 1) / tile_step : 0;
     const int64_t total = (int64_t)my_tiles * my_rounds;
     // The fetcher and the consumer each walk the (tile, round) pairs with their own counters: no divisions, 32-bit offsets
     // from two row pointers that move once per tile.
@@ -71,7 +77,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
     const uint8_t* f_ca = nullptr; const uint8_t* f_cb = nullptr;
     const uint16_t* f_sa = nullptr; const uint16_t* f_sb = nullptr;
     auto fetch_rows = [&]() {
-        const int tile = blockIdx.x + f_ti * gridDim.x;
+        const int tile = first_tile + f_ti * tile_step;
         const int na = min(tile * 16 + g, N - 1), nb = min(tile * 16 + g + 8, N - 1);     // rows beyond N re-read the last row
         f_ca = packed + na * row_codes + t * 16; f_cb = packed + nb * row_codes + t * 16;
         f_sa = scales + na * row_scales + t * 2; f_sb = scales + nb * row_scales + t * 2;
@@ -97,7 +103,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
     // ---- prologue: fixed-point digits of x in the operand layout, once per CTA ----
     bool any_bad = false;                                                         // Inf or NaN seen by this warp
 #pragma unroll 2
-    for (int mr = warp; mr < M * rounds; mr += kB2Warps) {
+    for (int mr = cta_warp; mr < M * rounds; mr += kB2Groups * kB2Warps) {
         const int xm = mr / rounds, r = mr - xm * rounds;                         // activation row, round
         const int64_t x0 = (int64_t)xm * K + (int64_t)r * 256 + lane * 8;
         float v[8];                                                               // x is 16-byte aligned: one or two vector loads
@@ -140,16 +146,20 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
         const float fa = __uint_as_float((uint32_t)(127 + sa) << 23), fb = __uint_as_float((uint32_t)(127 + sb) << 23);
         uint32_t dw[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};             // [digit][values 0-3, 4-7] as int8 x 4
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int q0 = __float2int_rn(v[i] * fa * fb);
-            const int q1 = (q0 + 64) >> 7, d3 = q0 - (q1 << 7);
-            const int q2 = (q1 + 64) >> 7, d2 = q1 - (q2 << 7);
-            const int d0 = (q2 + 64) >> 7, d1 = q2 - (d0 << 7);
-            const int sh = 8 * (i & 3);
-            dw[0][i >> 2] |= (uint32_t)(d0 & 0xFF) << sh;
-            dw[1][i >> 2] |= (uint32_t)(d1 & 0xFF) << sh;
-            dw[2][i >> 2] |= (uint32_t)(d2 & 0xFF) << sh;
-            dw[3][i >> 2] |= (uint32_t)(d3 & 0xFF) << sh;
+        for (int h = 0; h < 2; ++h) {                                           // values 4h .. 4h + 3: one operand word per digit
+            int dg[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int q0 = __float2int_rn(v[4 * h + j] * fa * fb);
+                const int q1 = (q0 + 64) >> 7, q2 = (q1 + 64) >> 7;
+                dg[0][j] = (q2 + 64) >> 7;
+                dg[1][j] = q2 - (dg[0][j] << 7);
+                dg[2][j] = q1 - (q2 << 7);
+                dg[3][j] = q0 - (q1 << 7);
+            }
+#pragma unroll
+            for (int d = 0; d < 4; ++d)                                            // low bytes of four integers into one word
+                dw[d][h] = prmt(prmt((uint32_t)dg[d][0], (uint32_t)dg[d][1], 0x0040u), prmt((uint32_t)dg[d][2], (uint32_t)dg[d][3], 0x0040u), 0x5410u);
         }
         // Operand layout in shared memory: frag[round][digit][word group 0..15][c 0..3] - the 32-bit word (group, c) holds
         // the digit bytes of k = 16 group + c + {0, 4, 8, 12}, exactly the bytes that meet the code bytes of
@@ -171,7 +181,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
     }
     if (__syncthreads_or(any_bad)) {
         // Inf / NaN in x: every product in fp32, one warp per weight row
-        for (int n = blockIdx.x * kB2Warps + warp; n < N; n += gridDim.x * kB2Warps) {
+        for (int n = blockIdx.x * kB2Groups * kB2Warps + cta_warp; n < N; n += gridDim.x * kB2Groups * kB2Warps) {
             for (int m = 0; m < M; ++m) {
                 float acc = 0.f;
                 for (int k = lane; k < K; k += 32) {
@@ -260,9 +270,9 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
                     if (t == 0) { mybuf[m * 16 + g] = a; mybuf[m * 16 + g + 8] = b; }
                     og[m] = og8[m] = 0.f;
                 }
-                asm volatile("bar.sync 1, %0;" ::"r"(kB2Warps * 32) : "memory");       // every warp reaches its tile ends in the same order
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(kB2Warps * 32) : "memory");   // the group's warps reach their tile ends in the same order
                 if (warp == 0) {
-                    const int tile = blockIdx.x + ti * gridDim.x;
+                    const int tile = first_tile + ti * tile_step;
                     for (int e = lane; e < M * 16; e += 32) {                           // element (m, row) of the tile
                         const int m = e >> 4, n = tile * 16 + (e & 15);
                         if (n < N) {

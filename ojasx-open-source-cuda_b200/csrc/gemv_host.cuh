@@ -241,13 +241,12 @@ int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, cons
         ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(scales) & 3) == 0) {
         const size_t smem = b2_smem_bytes((int)M, (int)K);
-        const int tiles = (int)((N + 15) / 16);
-        const int ctas = (smem <= 112 * 1024 ? 2 : 1) * num_sms();          // two CTAs per SM while the operands of x leave room
-        const int grid = tiles < ctas ? tiles : ctas;
+        const int tile_pairs = (int)((N + 31) / 32);                         // one CTA per SM, two tile groups each
+        const int grid = tile_pairs < num_sms() ? tile_pairs : num_sms();
         auto run = [&](auto kernel, std::atomic<uint64_t>& done) -> int32_t {
             const int32_t sc = ensure_dynamic_smem(kernel, 227 * 1024, done);
             OJX_RETURN_IF(sc != OJX_OK, sc);
-            kernel<<<grid, kB2Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
+            kernel<<<grid, kB2Groups * kB2Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
             return launch_status();
         };
         static std::atomic<uint64_t> d1{0}, d2{0}, d4{0}, d8{0};
@@ -258,26 +257,23 @@ int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, cons
     }
     // the same shapes of the 1.0-bit format: int8 tensor cores, one table read per code byte
     if (bits == 1 && M >= 1 && M <= 8 && group == 32 && K % 2048 == 0 && K <= (1 << 20) && N < (1 << 30) &&
-        b1_smem_bytes(M <= 2 ? 1 : (M <= 4 ? 2 : 4), 16, (int)K) <= 227 * 1024 &&
+        b1_smem_bytes(M <= 2 ? 1 : (M <= 4 ? 2 : 4), 8, (int)K) <= 227 * 1024 &&
         ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(scales)) & 15) == 0) {
         const int cbs = M <= 2 ? 1 : (M <= 4 ? 2 : 4);
-        // sixteen copies of the table, eight when that is what lets two CTAs share an SM
-        const bool narrow = cbs == 1 && b1_smem_bytes(1, 16, (int)K) > 112 * 1024 && b1_smem_bytes(1, 8, (int)K) <= 112 * 1024;
+        const bool narrow = b1_smem_bytes(cbs, 16, (int)K) > 227 * 1024;      // sixteen copies of the table, eight where sixteen do not fit
         const size_t smem = b1_smem_bytes(cbs, narrow ? 8 : 16, (int)K);
-        const int tiles = (int)((N + 15) / 16);
-        const int ctas = (smem <= 112 * 1024 && cbs < 4 ? 2 : 1) * num_sms();     // the four-block variant needs the registers of a whole SM half
-        const int grid = tiles < ctas ? tiles : ctas;
+        const int tile_pairs = (int)((N + 31) / 32);                         // one CTA per SM, two tile groups each
+        const int grid = tile_pairs < num_sms() ? tile_pairs : num_sms();
         auto run = [&](auto kernel, std::atomic<uint64_t>& done) -> int32_t {
             const int32_t sc = ensure_dynamic_smem(kernel, 227 * 1024, done);
             OJX_RETURN_IF(sc != OJX_OK, sc);
-            kernel<<<grid, kB1Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
+            kernel<<<grid, kB1Groups * kB1Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
             return launch_status();
         };
-        static std::atomic<uint64_t> d1{0}, d1n{0}, d2{0}, d4{0};
-        if (narrow) return run(gemv_b1_kernel<1, 8>, d1n);
-        if (cbs == 1) return run(gemv_b1_kernel<1, 16>, d1);
-        if (cbs == 2) return run(gemv_b1_kernel<2, 16>, d2);
-        return run(gemv_b1_kernel<4, 16>, d4);
+        static std::atomic<uint64_t> d1{0}, d2{0}, d4{0}, d1n{0}, d2n{0}, d4n{0};
+        if (cbs == 1) return narrow ? run(gemv_b1_kernel<1, 8>, d1n) : run(gemv_b1_kernel<1, 16>, d1);
+        if (cbs == 2) return narrow ? run(gemv_b1_kernel<2, 8>, d2n) : run(gemv_b1_kernel<2, 16>, d2);
+        return narrow ? run(gemv_b1_kernel<4, 8>, d4n) : run(gemv_b1_kernel<4, 16>, d4);
     }
     int32_t st = OJX_OK;                                      // small batches: the shared-memory kernel when x fits
     if (bits == 2 ? launch_lowbit_gemv<2>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, s, &st)
