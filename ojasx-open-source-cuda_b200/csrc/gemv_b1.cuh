@@ -34,16 +34,15 @@
 namespace ojx {
 
 constexpr int kB1Warps = 8;                       // warps of a tile group
-constexpr int kB1Groups = 2;                      // tile groups of a CTA
 constexpr int kB1Ahead = 3;                       // rounds in flight per warp
 constexpr int kB1RoundBytes = 16 * 32 + 16 * 16;  // one round of a 16-row tile: code bytes, then scales
 
-__host__ __device__ inline size_t b1_smem_bytes(int cbs, int copies, int K) {      // cbs: column blocks (pairs of activation rows)
+__host__ __device__ inline size_t b1_smem_bytes(int cbs, int copies, int groups, int K) {      // cbs: column blocks (pairs of activation rows)
     const int rounds = K / 256;
     // operands [cb][round][group pair][lane][32 B], group factors [2 cb][round][parity][group] x 4 B, table copies, the
     // warps' rings, partial sums
     return (size_t)cbs * rounds * 2048 + (size_t)2 * cbs * rounds * 64 + (size_t)2048 * copies +
-           (size_t)kB1Groups * kB1Warps * kB1Ahead * kB1RoundBytes + (size_t)kB1Groups * 2 * kB1Warps * 2 * cbs * 16 * 4;
+           (size_t)groups * kB1Warps * kB1Ahead * kB1RoundBytes + (size_t)groups * 2 * kB1Warps * 2 * cbs * 16 * 4;
 }
 
 // D = A . B with a zero accumulator operand: no registers to clear before the instruction.
@@ -53,7 +52,7 @@ __device__ __forceinline__ void mma_s8_from_zero(int (&d)[4], uint32_t a0, uint3
 }
 
 
-template <int kCB, int kB1Copies>                 // column blocks (pairs of activation rows); copies of the code table (16 or 8)
+template <int kCB, int kB1Copies, int kB1Groups>  // column blocks (pairs of activation rows); copies of the code table (16 or 8); tile groups of 8 warps
 __global__ void __launch_bounds__(kB1Groups * kB1Warps * 32, 1)
 gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
                const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype) {

@@ -35,12 +35,11 @@
 namespace ojx {
 
 constexpr int kB2Warps = 8;                       // warps of a tile group
-constexpr int kB2Groups = 2;                      // tile groups of a CTA
 constexpr int kB2Ahead = 3;                       // rounds in flight per warp
 
-__host__ __device__ inline size_t b2_smem_bytes(int M, int K) {
+__host__ __device__ inline size_t b2_smem_bytes(int M, int groups, int K) {
     const int rounds = K / 256;
-    return (size_t)M * rounds * (8 * 32 * 4 + 8 * 4 * 4) + (size_t)kB2Groups * M * kB2Warps * 16 * 4 * 2;   // operands, group factors, partial sums
+    return (size_t)M * rounds * (8 * 32 * 4 + 8 * 4 * 4) + (size_t)groups * M * kB2Warps * 16 * 4 * 2;   // operands, group factors, partial sums
 }
 
 struct B2Loads {
@@ -48,7 +47,7 @@ struct B2Loads {
     uint32_t sa, sb;                              // their two fp16 scales each
 };
 
-template <int kM>
+template <int kM, int kB2Groups>                  // rows of x handled by the unrolled loops; tile groups of 8 warps
 __global__ void __launch_bounds__(kB2Groups * kB2Warps * 32, 1)
 gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
                const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype) {

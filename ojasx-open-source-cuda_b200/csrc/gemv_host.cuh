@@ -237,43 +237,47 @@ int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, cons
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
     // up to eight rows of the 2.0-bit format with groups of 32 and K a multiple of 2048: int8 tensor cores, no table
     if (bits == 2 && M >= 1 && M <= 8 && group == 32 && K % 2048 == 0 && K <= (1 << 20) && N < (1 << 30) &&
-        b2_smem_bytes((int)M, (int)K) <= 227 * 1024 &&
+        b2_smem_bytes((int)M, 2, (int)K) <= 227 * 1024 &&
         ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(scales) & 3) == 0) {
-        const size_t smem = b2_smem_bytes((int)M, (int)K);
-        const int tile_pairs = (int)((N + 31) / 32);                         // one CTA per SM, two tile groups each
-        const int grid = tile_pairs < num_sms() ? tile_pairs : num_sms();
+        // one CTA per SM, two groups of eight warps (three and four groups were measured: coarser tile sets and fewer
+        // registers per thread cost more than the extra warps hide)
+        const int groups = 2;
+        const size_t smem = b2_smem_bytes((int)M, groups, (int)K);
+        const int tile_sets = (int)((N + 16 * groups - 1) / (16 * groups));
+        const int grid = tile_sets < num_sms() ? tile_sets : num_sms();
         auto run = [&](auto kernel, std::atomic<uint64_t>& done) -> int32_t {
             const int32_t sc = ensure_dynamic_smem(kernel, 227 * 1024, done);
             OJX_RETURN_IF(sc != OJX_OK, sc);
-            kernel<<<grid, kB2Groups * kB2Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
+            kernel<<<grid, groups * kB2Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
             return launch_status();
         };
         static std::atomic<uint64_t> d1{0}, d2{0}, d4{0}, d8{0};
-        if (M == 1) return run(gemv_b2_kernel<1>, d1);
-        if (M == 2) return run(gemv_b2_kernel<2>, d2);
-        if (M <= 4) return run(gemv_b2_kernel<4>, d4);
-        return run(gemv_b2_kernel<8>, d8);
+        if (M == 1) return run(gemv_b2_kernel<1, 2>, d1);
+        if (M == 2) return run(gemv_b2_kernel<2, 2>, d2);
+        if (M <= 4) return run(gemv_b2_kernel<4, 2>, d4);
+        return run(gemv_b2_kernel<8, 2>, d8);
     }
     // the same shapes of the 1.0-bit format: int8 tensor cores, one table read per code byte
     if (bits == 1 && M >= 1 && M <= 8 && group == 32 && K % 2048 == 0 && K <= (1 << 20) && N < (1 << 30) &&
-        b1_smem_bytes(M <= 2 ? 1 : (M <= 4 ? 2 : 4), 8, (int)K) <= 227 * 1024 &&
+        b1_smem_bytes(M <= 2 ? 1 : (M <= 4 ? 2 : 4), 8, 2, (int)K) <= 227 * 1024 &&
         ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(scales)) & 15) == 0) {
         const int cbs = M <= 2 ? 1 : (M <= 4 ? 2 : 4);
-        const bool narrow = b1_smem_bytes(cbs, 16, (int)K) > 227 * 1024;      // sixteen copies of the table, eight where sixteen do not fit
-        const size_t smem = b1_smem_bytes(cbs, narrow ? 8 : 16, (int)K);
-        const int tile_pairs = (int)((N + 31) / 32);                         // one CTA per SM, two tile groups each
-        const int grid = tile_pairs < num_sms() ? tile_pairs : num_sms();
+        const int groups = 2;                                                // one CTA per SM, two groups of eight warps
+        const bool narrow = b1_smem_bytes(cbs, 16, groups, (int)K) > 227 * 1024;      // sixteen copies of the table, eight where sixteen do not fit
+        const size_t smem = b1_smem_bytes(cbs, narrow ? 8 : 16, groups, (int)K);
+        const int tile_sets = (int)((N + 16 * groups - 1) / (16 * groups));
+        const int grid = tile_sets < num_sms() ? tile_sets : num_sms();
         auto run = [&](auto kernel, std::atomic<uint64_t>& done) -> int32_t {
             const int32_t sc = ensure_dynamic_smem(kernel, 227 * 1024, done);
             OJX_RETURN_IF(sc != OJX_OK, sc);
-            kernel<<<grid, kB1Groups * kB1Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
+            kernel<<<grid, groups * kB1Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
             return launch_status();
         };
         static std::atomic<uint64_t> d1{0}, d2{0}, d4{0}, d1n{0}, d2n{0}, d4n{0};
-        if (cbs == 1) return narrow ? run(gemv_b1_kernel<1, 8>, d1n) : run(gemv_b1_kernel<1, 16>, d1);
-        if (cbs == 2) return narrow ? run(gemv_b1_kernel<2, 8>, d2n) : run(gemv_b1_kernel<2, 16>, d2);
-        return narrow ? run(gemv_b1_kernel<4, 8>, d4n) : run(gemv_b1_kernel<4, 16>, d4);
+        if (cbs == 1) return narrow ? run(gemv_b1_kernel<1, 8, 2>, d1n) : run(gemv_b1_kernel<1, 16, 2>, d1);
+        if (cbs == 2) return narrow ? run(gemv_b1_kernel<2, 8, 2>, d2n) : run(gemv_b1_kernel<2, 16, 2>, d2);
+        return narrow ? run(gemv_b1_kernel<4, 8, 2>, d4n) : run(gemv_b1_kernel<4, 16, 2>, d4);
     }
     int32_t st = OJX_OK;                                      // small batches: the shared-memory kernel when x fits
     if (bits == 2 ? launch_lowbit_gemv<2>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, s, &st)
