@@ -863,6 +863,13 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
             del graph
             gbs = per * (0.25 + 2.0 / 32) / (ms * 1e-3) / 1e9
             two[f"linear_14336x4096_{rows_x}row"] = {"ms": ms, "packed_GBps": gbs, "frac_hbm": gbs / hbm_peak}
+        # a batch of 2048 tokens on one 14336 x 4096 matrix: the tcgen05 prefill kernel with the 2-bit decoder
+        xp = ops.generate(2048 * 4096, 10, 1.0, torch.bfloat16, dev).view(2048, 4096)
+        per = 14336 * 4096
+        ms = timed(lambda: ops.linear_2bit(xp, p2[: per // 4], s2[: per // 32], None, 14336, 4096, 32), 5)
+        ops.gemm_status(dev)
+        tf = 2.0 * 2048 * per / (ms * 1e-3) / 1e12
+        two["prefill_14336x4096_2048tokens"] = {"ms": ms, "TFLOPs": tf, "frac_bf16_peak": tf / tf_peak}
         out["two_bit"] = two
         del p2, s2
         # the 1.0-bit root format: packer (argmax over 256 candidate vectors per 8 weights) and unpacker, groups of 32
@@ -890,8 +897,12 @@ def run_extras(torch, ops, sharding, dist, dev, world, rank, groups, packed_stor
             del graph
             gbs = per * (0.125 + 2.0 / 32) / (ms * 1e-3) / 1e9
             one[f"linear_14336x4096_{rows_x}row"] = {"ms": ms, "packed_GBps": gbs, "frac_hbm": gbs / hbm_peak}
+        ms = timed(lambda: ops.linear_1bit(xp, p1[: per // 8], s1[: per // 32], None, 14336, 4096, 32), 5)
+        ops.gemm_status(dev)
+        tf = 2.0 * 2048 * per / (ms * 1e-3) / 1e12
+        one["prefill_14336x4096_2048tokens"] = {"ms": ms, "TFLOPs": tf, "frac_bf16_peak": tf / tf_peak}
         out["one_bit"] = one
-        del p1, s1
+        del p1, s1, xp
         ops.encode(w, 32, out=(pk, sc))
         # decoder (unpack): packed codes + scales -> dense fp16 weights, 0.25 B read + 2 B written per weight
         ms = timed(lambda: ops.decode(pk, sc, (n, k), torch.float16, out=w), 3)

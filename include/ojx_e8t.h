@@ -390,6 +390,20 @@ int32_t ojx_e8t_gemm(const void* x, int32_t x_dtype, int64_t M,
 int32_t ojx_e8t_gemm_status(const void* workspace, void* stream);
 
 /*
+ * The same prefill kernel for the two sibling formats (`bits` 2 or 1; group 32, K % 256 == 0, 16-bit activations,
+ * workspace and status exactly as for ojx_e8t_gemm): the decoder warps read the 2-bit / 1-bit codes instead of the
+ * ternary ranks.  Replaces the 2.0-bit / 1.0-bit branches of _FusedE8GEMMFunction.forward
+ * (ojasx2/math/lattice.py:596-624) for batches of tokens.  The weights enter the tensor cores as fp16: for 1 bit
+ * coordinate * scale is exact; for 2 bits (code - 1.5) * scale is rounded to fp16 once, i.e. the product equals
+ * x . decode_2bit(fp16)^T with fp32 accumulation.
+ */
+int32_t ojx_e8t_gemm_lowbit(int32_t bits, const void* x, int32_t x_dtype, int64_t M,
+                            const uint8_t* packed, const uint16_t* scales, const void* bias,
+                            int64_t N, int64_t K, int32_t group,
+                            void* y, int32_t y_dtype,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Backward of the packed linear with respect to its input: dX[M, K] = dY[M, N] . W[N, K], W given packed, on the
  * same tcgen05 pipeline (the contraction runs over the weight rows; the decoded weights enter the MMAs as an
  * MN-major operand, so no dense or transposed copy of W ever exists).  Replaces the decode-then-matmul of

@@ -285,7 +285,7 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 //              the number of weight COLUMNS (the output's feature dimension, tiled like N above) and p.K the number
 //              of weight rows (the contraction length, any positive value: the last block is zero-filled).  The
 //              decoded weights enter the MMA as an MN-major operand, so a decoded rank is still one 16-byte store.
-template <bool kDX>
+template <bool kDX, int kFmt = 0>              // kFmt: 0 ternary codes, 2 the 2.0-bit format, 1 the 1.0-bit format (forward only)
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -311,12 +311,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     // interleaved copies (one per lane of a half warp, so the 64-bit lookups never meet in a bank).  A rank r is
     // the base-3 number 2r (even coordinate sums are exactly the even numbers), so its eight coordinates are the
     // digits of (2r) mod 81 followed by those of (2r) div 81.
-    for (int i = tid; i < 81 * kGemmDigitCopies; i += kGemmThreads) {
-        int e = i / kGemmDigitCopies;
-        uint32_t h[4];
+    if constexpr (kFmt == 0) {
+        for (int i = tid; i < 81 * kGemmDigitCopies; i += kGemmThreads) {
+            int e = i / kGemmDigitCopies;
+            uint32_t h[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) { const int d = e % 3; e /= 3; h[k] = d == 0 ? 0xBC00u : (d == 1 ? 0u : 0x3C00u); }
-        reinterpret_cast<uint2*>(lut)[i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+            for (int k = 0; k < 4; ++k) { const int d = e % 3; e /= 3; h[k] = d == 0 ? 0xBC00u : (d == 1 ? 0u : 0x3C00u); }
+            reinterpret_cast<uint2*>(lut)[i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+        }
+    } else if constexpr (kFmt == 2) {
+        // 2.0-bit format: a code byte (four codes, code j in bits 2j) -> four fp16 values code - 1.5, eight interleaved copies
+        for (int i = tid; i < 256 * 8; i += kGemmThreads) {
+            const int e = i >> 3;
+            uint32_t h[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const int c = (e >> (2 * k)) & 3; h[k] = c == 0 ? 0xBE00u : (c == 1 ? 0xB800u : (c == 2 ? 0x3800u : 0x3E00u)); }
+            reinterpret_cast<uint2*>(lut)[i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+        }
+    } else {
+        // 1.0-bit format: a code -> its eight coordinates (0, +-1, +-2) as fp16, four interleaved copies
+        for (int i = tid; i < 256 * 4; i += kGemmThreads) {
+            const int e = i >> 2;
+            const uint32_t cw[2] = {g_root_coords[2 * e], g_root_coords[2 * e + 1]};
+            uint32_t h[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int c = (int)(int8_t)((cw[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+                h[k] = c == 0 ? 0u : (c == 1 ? 0x3C00u : (c == -1 ? 0xBC00u : (c == 2 ? 0x4000u : 0xC000u)));
+            }
+            reinterpret_cast<uint4*>(lut)[i] = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+        }
     }
     if (tid == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
@@ -474,6 +498,73 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
                     if (lane == 0) mbar_arrive(full_bar(s));
                 }
             }
+        } else if constexpr (kFmt != 0) {
+        // The sibling formats: thread r owns weight row r of the tile; 256 k are 64 (2.0-bit) or 32 (1.0-bit) bytes of
+        // codes and eight scales; every 8 weights are one table read (two for 2 bits) and four packed multiplies.
+        const int r = (warp - 4) * 32 + lane;
+        constexpr int kVec = kFmt == 2 ? 4 : 2;          // 16-byte vectors of codes per 256 k
+        const uint8_t* tab_lane = reinterpret_cast<const uint8_t*>(lut) + (kFmt == 2 ? (lane & 7) * 8 : (lane & 3) * 16);   // entry stride 64 B
+        uint32_t it = 0;
+        bool ok = true;
+        const int64_t row_bytes = kFmt == 2 ? p.K / 4 : p.K / 8, row_scales = p.K / 32;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const int n_blk = tile % n_blocks;
+            const int row = min(n_blk * p.rows + r, p.N - 1);
+            const uint4* cptr = reinterpret_cast<const uint4*>(p.packed + row * row_bytes);
+            const uint4* sptr = reinterpret_cast<const uint4*>(p.scales + row * row_scales);
+            const int chunks = p.K / 256;
+            uint4 cv[kVec];
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) cv[i] = __ldg(cptr + i);
+            uint4 sc = __ldg(sptr);
+            for (int ch = 0; ch < chunks && ok; ++ch) {
+                uint32_t cw[4 * kVec];
+#pragma unroll
+                for (int i = 0; i < kVec; ++i) { cw[4 * i] = cv[i].x; cw[4 * i + 1] = cv[i].y; cw[4 * i + 2] = cv[i].z; cw[4 * i + 3] = cv[i].w; }
+                const uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
+                if (ch + 1 < chunks) {                   // prefetch the next 256 k of this row
+#pragma unroll
+                    for (int i = 0; i < kVec; ++i) cv[i] = __ldg(cptr + kVec * (ch + 1) + i);
+                    sc = __ldg(sptr + ch + 1);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q, ++it) {
+                    const int s = it % kGemmStages;
+                    const uint32_t ph = (it / kGemmStages) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 4)) { ok = false; break; }
+                    uint8_t* arow = smem + kGemmStages * kXStageBytes + s * kAStageBytes + r * 128;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {                         // one scale group (32 k) = four 8-weight chunks
+                        uint2 lo8[4], hi8[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int jj = half * 4 + j;                           // chunk of the stage: k = 64 q + 8 jj ..
+                            if constexpr (kFmt == 2) {                             // two code bytes
+                                const uint32_t word = cw[4 * q + (jj >> 1)];
+                                lo8[j] = *reinterpret_cast<const uint2*>(tab_lane + prmt(word, 0u, 0x4440u | (uint32_t)(2 * (jj & 1))) * 64u);
+                                hi8[j] = *reinterpret_cast<const uint2*>(tab_lane + prmt(word, 0u, 0x4440u | (uint32_t)(2 * (jj & 1) + 1)) * 64u);
+                            } else {                                               // one code byte
+                                const uint32_t word = cw[2 * q + (jj >> 2)];
+                                const uint4 e = *reinterpret_cast<const uint4*>(tab_lane + prmt(word, 0u, 0x4440u | (uint32_t)(jj & 3)) * 64u);
+                                lo8[j] = make_uint2(e.x, e.y);
+                                hi8[j] = make_uint2(e.z, e.w);
+                            }
+                        }
+                        const uint32_t sc2 = prmt(sw[q], 0u, half == 0 ? 0x1010u : 0x3232u);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int jj = half * 4 + j;
+                            const uint4 v = make_uint4(hmul2_u32(lo8[j].x, sc2), hmul2_u32(lo8[j].y, sc2),
+                                                       hmul2_u32(hi8[j].x, sc2), hmul2_u32(hi8[j].y, sc2));
+                            *reinterpret_cast<uint4*>(arow + ((jj ^ (r & 7)) << 4)) = v;
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> async proxy (UMMA)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_bar(s));
+                }
+            }
+        }
         } else {
         const int r = (warp - 4) * 32 + lane;           // row of the 256-row tile
         const uint8_t* digit_lane = reinterpret_cast<const uint8_t*>(lut) + (lane & (kGemmDigitCopies - 1)) * 8;
@@ -593,14 +684,18 @@ size_t gemm_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
     return 256 + gemm_up_bytes(M) + (size_t)M * (size_t)K * 2;
 }
 
-int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
-                  const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
-                  void* workspace, size_t workspace_bytes, cudaStream_t s) {
+// fmt: 0 ternary codes (3 bytes per 16 weights), 2 the 2.0-bit format (one byte per 4 weights, weight =
+// (code - 1.5) * scale rounded to fp16 once, exactly the fp16 output of its decoder), 1 the 1.0-bit format (one byte
+// per 8 weights, coordinate * scale exact in fp16).
+int32_t gemm_fmt_impl(int fmt, const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                      const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
+                      void* workspace, size_t workspace_bytes, cudaStream_t s) {
     OJX_RETURN_IF(!x || !packed || !scales || !y, OJX_ERR_NULL);
+    OJX_RETURN_IF(fmt != 0 && fmt != 1 && fmt != 2, OJX_ERR_UNSUPPORTED);
     OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0, OJX_ERR_SHAPE);
     OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
-    group = effective_group(group);
+    if (fmt == 0) group = effective_group(group);
     OJX_RETURN_IF(!gemm_fast_ok(M, N, K, group, x_dtype), OJX_ERR_UNSUPPORTED);
     OJX_RETURN_IF(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) |
                     reinterpret_cast<uintptr_t>(scales)) & 15) != 0, OJX_ERR_ALIGN);
@@ -630,8 +725,11 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
             }
     }
 
-    static std::atomic<uint64_t> configured{0};                  // one bit per device: the opt-in is per context
-    OJX_RETURN_IF(ensure_dynamic_smem(gemm_tcgen05_kernel<false>, kGemmSmemBytes, configured) != OJX_OK, OJX_ERR_LAUNCH);
+    static std::atomic<uint64_t> configured[3];                  // per format; one bit per device: the opt-in is per context
+    OJX_RETURN_IF((fmt == 0 ? ensure_dynamic_smem(gemm_tcgen05_kernel<false, 0>, kGemmSmemBytes, configured[0])
+                   : fmt == 2 ? ensure_dynamic_smem(gemm_tcgen05_kernel<false, 2>, kGemmSmemBytes, configured[2])
+                              : ensure_dynamic_smem(gemm_tcgen05_kernel<false, 1>, kGemmSmemBytes, configured[1])) != OJX_OK,
+                  OJX_ERR_LAUNCH);
     if (convert) {
         if (K <= 4096)
             normalize_rows_bf16_to_f16_kernel<32, 16><<<(unsigned)((M + 7) / 8), 256, 0, s>>>(
@@ -659,7 +757,7 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return OJX_ERR_LAUNCH;
         GemmParams prm;
-        prm.packed = packed + (size_t)n0 * (size_t)K * 3 / 16;
+        prm.packed = packed + (fmt == 0 ? (size_t)n0 * (size_t)K * 3 / 16 : (size_t)n0 * (size_t)K / (fmt == 2 ? 4 : 8));
         prm.scales = scales + (size_t)n0 * (size_t)K / 32;
         prm.bias = bias ? static_cast<const uint8_t*>(bias) + (size_t)n0 * dtype_size(x_dtype) : nullptr;
         prm.y = static_cast<uint8_t*>(y) + ((size_t)m0 * (size_t)N + (size_t)n0) * dtype_size(y_dtype);
@@ -675,7 +773,9 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         const int64_t all = ((Ns + rows - 1) / rows) * ((Ms + bn - 1) / bn);
         prm.tile_limit = (int)(all < tile_limit ? all : tile_limit);
         const int grid = prm.tile_limit < num_sms() ? prm.tile_limit : num_sms();
-        gemm_tcgen05_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+        if (fmt == 0) gemm_tcgen05_kernel<false, 0><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+        else if (fmt == 2) gemm_tcgen05_kernel<false, 2><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+        else gemm_tcgen05_kernel<false, 1><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
         return launch_status();
     };
 
@@ -691,6 +791,12 @@ int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         return launch_region((n_blocks - leftover) * rows, (m_blocks - 1) * bn, kGemmHalf, 128, 1 << 30);
     }
     return launch_region(0, 0, rows, bn, 1 << 30);
+}
+
+int32_t gemm_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                  const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype,
+                  void* workspace, size_t workspace_bytes, cudaStream_t s) {
+    return gemm_fmt_impl(0, x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, workspace, workspace_bytes, s);
 }
 
 // dX[M, K] = dY[M, N] . W[N, K] without ever materialising W (the backward of the linear with respect to its

@@ -231,6 +231,14 @@ int32_t ojx_e8t_gemm(const void* x, int32_t x_dtype, int64_t M, const uint8_t* p
                           (cudaStream_t)stream);
 }
 
+int32_t ojx_e8t_gemm_lowbit(int32_t bits, const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                            const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+    if (bits != 1 && bits != 2) return OJX_ERR_UNSUPPORTED;
+    return ojx::gemm_fmt_impl(bits, x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, workspace, workspace_bytes,
+                              (cudaStream_t)stream);
+}
+
 size_t ojx_e8t_gemm_dx_workspace_bytes(int64_t M, int64_t N, int64_t K) { return ojx::gemm_dx_workspace_bytes_impl(M, N, K); }
 
 int32_t ojx_e8t_gemm_dx(const void* grad_y, int32_t gy_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,

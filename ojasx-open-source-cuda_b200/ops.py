@@ -154,6 +154,9 @@ def _decode_lowbit(bits: int, packed: torch.Tensor, scales: torch.Tensor, shape:
     return out
 
 
+LOWBIT_GEMV_MAX_M = 8      # rows of x the decode kernels of the 2.0-bit / 1.0-bit formats take
+
+
 def _linear_lowbit(bits: int, x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
                    n: int, k: int, group_size: int, out_dtype: Optional[torch.dtype]) -> torch.Tensor:
     dev = _require_cuda(x, packed, scales)
@@ -163,6 +166,18 @@ def _linear_lowbit(bits: int, x: torch.Tensor, packed: torch.Tensor, scales: tor
     if m == 0:
         return y
     b = None if bias is None else bias.detach().to(x2.dtype).contiguous()
+    lib = _cabi.lib()
+    if (m > LOWBIT_GEMV_MAX_M and int(group_size) == 32 and k % 256 == 0 and x2.dtype in (torch.bfloat16, torch.float16)
+            and packed.numel() * (4 if bits == 2 else 8) == n * k
+            and (x2.data_ptr() | packed.data_ptr() | scales.data_ptr()) % 16 == 0):
+        # batches of tokens: the tcgen05 prefill kernel with this format's decoder
+        with torch.cuda.device(dev):
+            ws = _gemm_scratch(dev, lib.ojx_e8t_gemm_workspace_bytes(m, n, k))
+            st = lib.ojx_e8t_gemm_lowbit(bits, x2.data_ptr(), _dtype_code(x2.dtype), m, packed.data_ptr(), scales.data_ptr(),
+                                         None if b is None else b.data_ptr(), n, k, 32, y.data_ptr(), _dtype_code(y.dtype),
+                                         ws.data_ptr(), ws.numel(), _stream_ptr(dev))
+        _cabi.check(st, "ojx_e8t_gemm_lowbit")
+        return y
     name = "ojx_e8t_linear_2bit" if bits == 2 else "ojx_e8t_linear_1bit"
     with torch.cuda.device(dev):
         st = getattr(_cabi.lib(), name)(x2.data_ptr(), _dtype_code(x2.dtype), m, packed.data_ptr(), scales.data_ptr(),
@@ -188,7 +203,10 @@ def decode_2bit(packed: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, in
 
 def linear_2bit(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor], n: int, k: int,
                 group_size: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``y = x . W^T (+ bias)`` from 2-bit codes in one fused fp32 kernel."""
+    """``y = x . W^T (+ bias)`` from 2-bit codes: up to eight rows of x run the decode kernels (int8 tensor cores for
+    groups of 32 and K % 2048 == 0), more rows with 16-bit activations, groups of 32 and K % 256 == 0 the tcgen05
+    prefill kernel (weights rounded to fp16 once, as ``decode_2bit(..., torch.float16)`` gives them), anything else
+    a scalar fp32 kernel."""
     return _linear_lowbit(2, x, packed, scales, bias, n, k, group_size, out_dtype)
 
 
@@ -207,7 +225,8 @@ def decode_1bit(packed: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, in
 
 def linear_1bit(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor], n: int, k: int,
                 group_size: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``y = x . W^T (+ bias)`` from root codes in one fused fp32 kernel."""
+    """``y = x . W^T (+ bias)`` from root codes; routed as :func:`linear_2bit` (here the fp16 weights of the
+    prefill kernel are exact)."""
     return _linear_lowbit(1, x, packed, scales, bias, n, k, group_size, out_dtype)
 
 

@@ -567,17 +567,20 @@ def test_one_bit_golden_ties_and_layer(P, golden, oracle):
 @pytest.mark.parametrize("bits", [2, 1])
 @pytest.mark.parametrize("m,k,n,group,dt", [(1, 4096, 4096, 32, torch.bfloat16), (3, 256, 40, 8, torch.float16),
                                              (8, 4096, 96, 64, torch.bfloat16), (1, 14336, 64, 32, torch.float32),
-                                             (2, 1024, 33, 16, torch.bfloat16), (9, 512, 24, 32, torch.bfloat16)])
+                                             (2, 1024, 33, 16, torch.bfloat16), (9, 512, 24, 32, torch.bfloat16), (9, 512, 24, 32, torch.float32), (12, 320, 24, 32, torch.bfloat16)])
 def test_low_bit_decode_linear_matches_dense_product(P, oracle, bits, m, k, n, group, dt):
-    """ojx_e8t_linear_2bit / _1bit at decode shapes (the shared-memory kernel for up to eight rows, the generic kernel
-    beyond) against the fp32 product with the decoded weights: fp32 accumulation of exact products, so the error stays
-    within 1e-5 of sum |x||w| per output."""
+    """ojx_e8t_linear_2bit / _1bit at decode shapes (the tensor-core or the shared-memory kernel for up to eight rows;
+    beyond, the prefill kernel or the scalar kernel) against the fp32 product with the decoded weights: fp32
+    accumulation of exact products, so the error stays within 1e-5 of sum |x||w| per output."""
     dev = torch.device(DEV)
     w = torch.from_numpy(oracle.gen_normal(900 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
     enc, dec, lin = ((P.ops.encode_2bit, P.ops.decode_2bit, P.ops.linear_2bit) if bits == 2
                      else (P.ops.encode_1bit, P.ops.decode_1bit, P.ops.linear_1bit))
     pk, sc = enc(w, group)
-    wd = dec(pk, sc, (n, k), torch.float32)
+    # more than eight rows of 16-bit activations with groups of 32 and K % 256 == 0 run the prefill kernel, whose
+    # operand is the weight rounded to fp16
+    prefill = m > 8 and group == 32 and k % 256 == 0 and dt != torch.float32
+    wd = dec(pk, sc, (n, k), torch.float16).float() if prefill else dec(pk, sc, (n, k), torch.float32)
     x = torch.from_numpy(oracle.gen_normal(901 + m, m * k, 1.0).reshape(m, k).copy()).to(dt).to(dev)
     bias = torch.from_numpy(oracle.gen_normal(902, n, 0.1).copy()).to(dt).to(dev)
     y = lin(x, pk, sc, bias, n, k, group, out_dtype=torch.float32)
@@ -633,3 +636,50 @@ def test_low_bit_tensor_core_kernels(P, oracle, bits, m, k, n, dt):
     xn[m // 2, 100] = float("nan")
     yn = lin(xn, pk, sc, None, n, k, 32, out_dtype=torch.float32)
     assert torch.isnan(yn[m // 2]).all() and int(torch.isnan(yn).sum()) == n
+
+
+@pytest.mark.parametrize("bits", [2, 1])
+@pytest.mark.parametrize("m,k,n,dt,with_bias", [(64, 256, 40, torch.float16, False), (17, 512, 256, torch.float16, True),
+                                                (300, 1024, 500, torch.bfloat16, True), (2048, 4096, 4096, torch.bfloat16, False),
+                                                (129, 2048, 8, torch.bfloat16, False)])
+def test_low_bit_prefill_gemm_matches_dense_product(P, oracle, bits, m, k, n, dt, with_bias):
+    """ojx_e8t_gemm_lowbit (the tcgen05 prefill kernel with the 2.0-bit / 1.0-bit decoders) against the fp32 product
+    with the weights decoded to fp16 - the operand the tensor cores see: fp32 accumulation of exact products, so the
+    error stays within 2e-5 of sum |x||w| per output; tile edges in both directions included."""
+    dev = torch.device(DEV)
+    w = torch.from_numpy(oracle.gen_normal(970 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
+    enc, dec, lin = ((P.ops.encode_2bit, P.ops.decode_2bit, P.ops.linear_2bit) if bits == 2
+                     else (P.ops.encode_1bit, P.ops.decode_1bit, P.ops.linear_1bit))
+    pk, sc = enc(w, 32)
+    wd = dec(pk, sc, (n, k), torch.float16).float()
+    x = torch.from_numpy(oracle.gen_normal(971 + m, m * k, 1.0).reshape(m, k).copy()).to(dt).to(dev)
+    x[m // 2] *= 64.0                                                    # rows on different scales
+    bias = torch.from_numpy(oracle.gen_normal(972, n, 0.1).copy()).to(dt).to(dev) if with_bias else None
+    y = lin(x, pk, sc, bias, n, k, 32, out_dtype=torch.float32)
+    P.ops.gemm_status(dev)
+    ref = x.float() @ wd.t() + (bias.float() if with_bias else 0.0)
+    budget = x.float().abs() @ wd.abs().t() + (bias.float().abs() if with_bias else 0.0)
+    assert float(((y - ref).abs() / budget.clamp_min(1e-30)).max()) < 2e-5
+    y16 = lin(x, pk, sc, bias, n, k, 32)
+    assert y16.dtype == dt and float((y16.float() - ref).abs().max()) <= 2.0 ** -7 * float(ref.abs().max()) + 1e-3
+    if bits == 2:                                                        # the fp16 rounding of (code - 1.5) * scale is within the tolerance of the path
+        exact = x.float() @ dec(pk, sc, (n, k), torch.float32).t() + (bias.float() if with_bias else 0.0)
+        assert float((y - exact).norm() / exact.norm()) <= 2e-3
+
+
+def test_low_bit_layer_prefill_runs_on_the_tensor_core_kernel(P):
+    """E8LatticeLinear with the reference's default bit-rate (2.0) and with 1.0 on a batch of tokens: forward through the
+    prefill kernel equals the product with the unpacked fp16 weights; backward still gives dY . W."""
+    dev = torch.device(DEV)
+    torch.manual_seed(11)
+    for bitrate in (2.0, 1.0):
+        lin = torch.nn.Linear(512, 96, bias=True).to(dev).to(torch.bfloat16)
+        layer = P.E8LatticeLinear.from_linear(lin, rank=0, bitrate=bitrate, group_size=32)
+        wd = layer.unpack_weights(torch.float16).float()
+        x = torch.randn(3, 40, 512, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        y = layer(x)
+        ref = x.detach().float() @ wd.t() + layer.bias.float()
+        assert y.shape == (3, 40, 96) and float((y.float() - ref).abs().max()) <= 2.0 ** -7 * float(ref.abs().max()) + 1e-3
+        y.float().sum().backward()
+        gref = torch.ones(120, 96, device=dev) @ layer.unpack_weights(torch.float32)
+        assert float((x.grad.float().reshape(120, 512) - gref).abs().max()) <= 2.0 ** -6 * float(gref.abs().max()) + 1e-3
