@@ -418,6 +418,13 @@ int32_t ojx_e8t_gemm_dx(const void* grad_y, int32_t gy_dtype, int64_t M,
                         int64_t N, int64_t K, int32_t group,
                         void* dx, int32_t dx_dtype,
                         void* workspace, size_t workspace_bytes, void* stream);
+/* The same for the 2.0-bit and 1.0-bit formats (`bits` 2 or 1; the weights enter as fp16 exactly as in
+ * ojx_e8t_gemm_lowbit): dX = dY . decode(fp16 W). */
+int32_t ojx_e8t_gemm_dx_lowbit(int32_t bits, const void* grad_y, int32_t gy_dtype, int64_t M,
+                               const uint8_t* packed, const uint16_t* scales,
+                               int64_t N, int64_t K, int32_t group,
+                               void* dx, int32_t dx_dtype,
+                               void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Seeded synthetic data, generated on the device: element i of stream `seed` is a sum of twelve

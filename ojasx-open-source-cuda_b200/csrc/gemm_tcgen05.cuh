@@ -285,7 +285,7 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 //              the number of weight COLUMNS (the output's feature dimension, tiled like N above) and p.K the number
 //              of weight rows (the contraction length, any positive value: the last block is zero-filled).  The
 //              decoded weights enter the MMA as an MN-major operand, so a decoded rank is still one 16-byte store.
-template <bool kDX, int kFmt = 0>              // kFmt: 0 ternary codes, 2 the 2.0-bit format, 1 the 1.0-bit format (forward only)
+template <bool kDX, int kFmt = 0>              // kFmt: 0 ternary codes, 2 the 2.0-bit format, 1 the 1.0-bit format
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -439,29 +439,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
             // eight ranks = 12 bytes of codes and two scales, each rank one 16-byte chunk of the MN-major tile.
             const int r = (warp - 4) * 32 + lane;
             const int j = r & 63, kq = r >> 6;
-            const uint8_t* digit_lane = reinterpret_cast<const uint8_t*>(lut) + (lane & (kGemmDigitCopies - 1)) * 8;
-            const int64_t row_bytes = (int64_t)p.N * 3 / 16, row_scales = p.N / 32;
+            // (the sibling formats: 16 or 8 bytes of codes; one or two reads of their table per 8 weights)
+            const uint8_t* digit_lane = reinterpret_cast<const uint8_t*>(lut) +
+                                        (kFmt == 0 ? (lane & (kGemmDigitCopies - 1)) * 8 : (kFmt == 2 ? (lane & 7) * 8 : (lane & 3) * 16));
+            constexpr int kWords = kFmt == 0 ? 3 : (kFmt == 2 ? 4 : 2);            // 32-bit words of codes per 64 columns
+            const int64_t row_bytes = kFmt == 0 ? (int64_t)p.N * 3 / 16 : (kFmt == 2 ? p.N / 4 : p.N / 8), row_scales = p.N / 32;
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
                 const int n_blk = tile % n_blocks;
                 const int col0 = n_blk * p.rows + kq * 64;                       // first weight column of this thread
-                const uint8_t* cbase = p.packed + (int64_t)col0 * 3 / 16;
+                const uint8_t* cbase = p.packed + (kFmt == 0 ? (int64_t)col0 * 3 / 16 : (kFmt == 2 ? col0 / 4 : col0 / 8));
                 const uint16_t* sbase = p.scales + col0 / 32;
-                auto fetch = [&](int kb, uint32_t (&cw)[3], uint32_t& sw) {
+                auto fetch = [&](int kb, uint32_t (&cw)[4], uint32_t& sw) {
                     const int row = kb * kGemmBK + j;
                     if (row < p.K && col0 < p.N) {
                         const uint32_t* cp = reinterpret_cast<const uint32_t*>(cbase + (int64_t)row * row_bytes);
-                        cw[0] = __ldg(cp); cw[1] = __ldg(cp + 1); cw[2] = __ldg(cp + 2);
+#pragma unroll
+                        for (int i = 0; i < kWords; ++i) cw[i] = __ldg(cp + i);
                         sw = __ldg(reinterpret_cast<const uint32_t*>(sbase + (int64_t)row * row_scales));
-                    } else {                                                     // beyond the matrix: rank of the zero vector, scale 0
+                    } else if (kFmt == 0) {                                      // beyond the matrix: rank of the zero vector, scale 0
                         cw[0] = 0x68668668u; cw[1] = 0x86686686u; cw[2] = 0x66866866u; sw = 0u;   // rank 1640 eight times
+                    } else {                                                     // any code, scale 0
+                        cw[0] = cw[1] = cw[2] = cw[3] = 0u; sw = 0u;
                     }
                 };
-                uint32_t nw[3], ns;
+                uint32_t nw[4] = {0u, 0u, 0u, 0u}, ns;
                 fetch(0, nw, ns);
                 for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
-                    uint32_t cw[4] = {nw[0], nw[1], nw[2], 0u};
+                    uint32_t cw[4] = {nw[0], nw[1], nw[2], kWords == 4 ? nw[3] : 0u};
                     const uint32_t sw = ns;
                     if (kb + 1 < k_blocks) fetch(kb + 1, nw, ns);                // the next stage's words travel during this one's decode
                     const int s = it % kGemmStages;
@@ -474,15 +480,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             const int c = half * 4 + q;
-                            const int bit = 12 * c, w = bit >> 5, sh = bit & 31;
-                            uint32_t R;                              // 2 * rank
-                            if (sh + 12 <= 32) R = sh >= 1 ? (cw[w] >> (sh - 1)) : (cw[w] << 1);
-                            else R = __funnelshift_r(cw[w], cw[w + 1], sh - 1);
-                            R &= 0x1FFEu;
-                            const uint32_t v = (R * 6473u) >> 19;    // R div 81 (exact for R < 6562)
-                            const uint32_t u = R - 81u * v;
-                            lo8[q] = *reinterpret_cast<const uint2*>(digit_lane + u * (kGemmDigitCopies * 8));
-                            hi8[q] = *reinterpret_cast<const uint2*>(digit_lane + v * (kGemmDigitCopies * 8));
+                            if constexpr (kFmt == 0) {
+                                const int bit = 12 * c, w = bit >> 5, sh = bit & 31;
+                                uint32_t R;                              // 2 * rank
+                                if (sh + 12 <= 32) R = sh >= 1 ? (cw[w] >> (sh - 1)) : (cw[w] << 1);
+                                else R = __funnelshift_r(cw[w], cw[w + 1], sh - 1);
+                                R &= 0x1FFEu;
+                                const uint32_t v = (R * 6473u) >> 19;    // R div 81 (exact for R < 6562)
+                                const uint32_t u = R - 81u * v;
+                                lo8[q] = *reinterpret_cast<const uint2*>(digit_lane + u * (kGemmDigitCopies * 8));
+                                hi8[q] = *reinterpret_cast<const uint2*>(digit_lane + v * (kGemmDigitCopies * 8));
+                            } else if constexpr (kFmt == 2) {            // two code bytes: codes 0-3 and 4-7 of the chunk
+                                const uint32_t word = cw[c >> 1];
+                                lo8[q] = *reinterpret_cast<const uint2*>(digit_lane + prmt(word, 0u, 0x4440u | (uint32_t)(2 * (c & 1))) * 64u);
+                                hi8[q] = *reinterpret_cast<const uint2*>(digit_lane + prmt(word, 0u, 0x4440u | (uint32_t)(2 * (c & 1) + 1)) * 64u);
+                            } else {                                     // one code byte
+                                const uint4 e = *reinterpret_cast<const uint4*>(digit_lane + prmt(cw[c >> 2], 0u, 0x4440u | (uint32_t)(c & 3)) * 64u);
+                                lo8[q] = make_uint2(e.x, e.y);
+                                hi8[q] = make_uint2(e.z, e.w);
+                            }
                         }
                         const uint32_t sc2 = prmt(sw, 0u, half == 0 ? 0x1010u : 0x3232u);
 #pragma unroll
@@ -812,14 +828,15 @@ size_t gemm_dx_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
     return 256 + gemm_up_bytes(M) + (size_t)M * (size_t)N * 2;
 }
 
-int32_t gemm_dx_impl(const void* gy, int gy_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
-                     int64_t N, int64_t K, int group, void* dx, int dx_dtype,
-                     void* workspace, size_t workspace_bytes, cudaStream_t s) {
+int32_t gemm_dx_fmt_impl(int fmt, const void* gy, int gy_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                         int64_t N, int64_t K, int group, void* dx, int dx_dtype,
+                         void* workspace, size_t workspace_bytes, cudaStream_t s) {
     OJX_RETURN_IF(!gy || !packed || !scales || !dx, OJX_ERR_NULL);
+    OJX_RETURN_IF(fmt != 0 && fmt != 1 && fmt != 2, OJX_ERR_UNSUPPORTED);
     OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0, OJX_ERR_SHAPE);
     OJX_RETURN_IF(dtype_size(gy_dtype) == 0 || dtype_size(dx_dtype) == 0, OJX_ERR_DTYPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
-    group = effective_group(group);
+    if (fmt == 0) group = effective_group(group);
     OJX_RETURN_IF(!gemm_dx_ok(M, N, K, group, gy_dtype), OJX_ERR_UNSUPPORTED);
     OJX_RETURN_IF(((reinterpret_cast<uintptr_t>(gy) | reinterpret_cast<uintptr_t>(packed) |
                     reinterpret_cast<uintptr_t>(scales)) & 15) != 0, OJX_ERR_ALIGN);
@@ -847,8 +864,11 @@ int32_t gemm_dx_impl(const void* gy, int gy_dtype, int64_t M, const uint8_t* pac
                 if (cost < best) { best = cost; rows = cand_rows[ri]; bn = cand_bn[bi]; }
             }
     }
-    static std::atomic<uint64_t> configured{0};
-    OJX_RETURN_IF(ensure_dynamic_smem(gemm_tcgen05_kernel<true>, kGemmSmemBytes, configured) != OJX_OK, OJX_ERR_LAUNCH);
+    static std::atomic<uint64_t> configured[3];
+    OJX_RETURN_IF((fmt == 0 ? ensure_dynamic_smem(gemm_tcgen05_kernel<true, 0>, kGemmSmemBytes, configured[0])
+                   : fmt == 2 ? ensure_dynamic_smem(gemm_tcgen05_kernel<true, 2>, kGemmSmemBytes, configured[2])
+                              : ensure_dynamic_smem(gemm_tcgen05_kernel<true, 1>, kGemmSmemBytes, configured[1])) != OJX_OK,
+                  OJX_ERR_LAUNCH);
     if (convert) {
         // per-token power-of-two factors exactly as in the forward launch; rows here are N long (any multiple of 8)
         if (N <= 4096)
@@ -885,8 +905,16 @@ int32_t gemm_dx_impl(const void* gy, int gy_dtype, int64_t M, const uint8_t* pac
     const int64_t all = ((K + rows - 1) / rows) * ((M + bn - 1) / bn);
     prm.tile_limit = (int)(all < (1 << 30) ? all : (1 << 30));
     const int grid = prm.tile_limit < num_sms() ? prm.tile_limit : num_sms();
-    gemm_tcgen05_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+    if (fmt == 0) gemm_tcgen05_kernel<true, 0><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+    else if (fmt == 2) gemm_tcgen05_kernel<true, 2><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+    else gemm_tcgen05_kernel<true, 1><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
     return launch_status();
+}
+
+int32_t gemm_dx_impl(const void* gy, int gy_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
+                     int64_t N, int64_t K, int group, void* dx, int dx_dtype,
+                     void* workspace, size_t workspace_bytes, cudaStream_t s) {
+    return gemm_dx_fmt_impl(0, gy, gy_dtype, M, packed, scales, N, K, group, dx, dx_dtype, workspace, workspace_bytes, s);
 }
 
 int32_t gemm_status_impl(const void* workspace, cudaStream_t s) {

@@ -248,6 +248,14 @@ int32_t ojx_e8t_gemm_dx(const void* grad_y, int32_t gy_dtype, int64_t M, const u
                              (cudaStream_t)stream);
 }
 
+int32_t ojx_e8t_gemm_dx_lowbit(int32_t bits, const void* grad_y, int32_t gy_dtype, int64_t M, const uint8_t* packed,
+                               const uint16_t* scales, int64_t N, int64_t K, int32_t group, void* dx, int32_t dx_dtype,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    if (bits != 1 && bits != 2) return OJX_ERR_UNSUPPORTED;
+    return ojx::gemm_dx_fmt_impl(bits, grad_y, gy_dtype, M, packed, scales, N, K, group, dx, dx_dtype, workspace, workspace_bytes,
+                                 (cudaStream_t)stream);
+}
+
 int32_t ojx_e8t_gemm_status(const void* workspace, void* stream) {
     return ojx::gemm_status_impl(workspace, (cudaStream_t)stream);
 }

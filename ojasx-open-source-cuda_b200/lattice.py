@@ -265,16 +265,16 @@ class _FusedE8GEMMFunction(torch.autograd.Function):
         gy_2d = grad_y.reshape(-1, ctx.out_features).contiguous()
         eff = ops.effective_group(ctx.group_size)
         if ctx.bitrate == 1.0:
-            w = ops.decode_1bit(packed_weight, block_scales, (ctx.out_features, ctx.in_features), ctx.x_dtype)
-            grad_x = gy_2d.to(ctx.x_dtype).matmul(w).reshape(ctx.x_shape)
+            grad_x = ops.linear_dx_lowbit(1, gy_2d.to(ctx.x_dtype), packed_weight, block_scales, ctx.out_features,
+                                          ctx.in_features, ctx.group_size).reshape(ctx.x_shape)
         elif ctx.bitrate == 2.0:
             if torch.compiler.is_compiling() and ctx.in_features % ctx.group_size == 0:
                 grad_x = torch.ops.ojasx_math_native.fused_e8_gemm_bwd_dx(
                     gy_2d.to(ctx.x_dtype), packed_weight.view(ctx.out_features, -1), block_scales.view(ctx.out_features, -1),
                     ctx.in_features, ctx.group_size).reshape(ctx.x_shape)
             else:
-                w = ops.decode_2bit(packed_weight, block_scales, (ctx.out_features, ctx.in_features), ctx.x_dtype)
-                grad_x = gy_2d.to(ctx.x_dtype).matmul(w).reshape(ctx.x_shape)
+                grad_x = ops.linear_dx_lowbit(2, gy_2d.to(ctx.x_dtype), packed_weight, block_scales, ctx.out_features,
+                                              ctx.in_features, ctx.group_size).reshape(ctx.x_shape)
         elif torch.compiler.is_compiling() and ctx.in_features % eff == 0:
             grad_x = torch.ops.ojasx_math_native.fused_ternary_e8_gemm_bwd_dx(
                 gy_2d.to(ctx.x_dtype), packed_weight.view(ctx.out_features, -1), block_scales.view(ctx.out_features, -1),

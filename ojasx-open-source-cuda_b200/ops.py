@@ -462,6 +462,37 @@ def linear_dx(grad_y2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor
     return dx
 
 
+def linear_dx_lowbit(bits: int, grad_y2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, out_features: int,
+                     in_features: int, group_size: int = 32, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """dX[M, K] = dY[M, N] . W[N, K] for the 2.0-bit (``bits`` 2) or 1.0-bit (``bits`` 1) format straight from the
+    packed codes (``ojx_e8t_gemm_dx_lowbit``; the weights enter the tensor cores as fp16).  Shapes the kernel does not
+    take (fp32 gradients, K % 256 != 0, N % 8 != 0, groups other than 32) decode W and multiply."""
+    n, k = int(out_features), int(in_features)
+    dev = _require_cuda(grad_y2d, packed, scales)
+    if grad_y2d.dim() != 2 or grad_y2d.shape[1] != n:
+        raise ValueError(f"grad_y must be [M, {n}], got {tuple(grad_y2d.shape)}")
+    gy = grad_y2d.contiguous()
+    m = int(gy.shape[0])
+    ydt = out_dtype or gy.dtype
+    if m == 0:
+        return torch.empty((0, k), dtype=ydt, device=dev)
+    fast = (gy.dtype in (torch.bfloat16, torch.float16) and k % 256 == 0 and n % 8 == 0 and int(group_size) == 32
+            and packed.numel() * (4 if bits == 2 else 8) == n * k
+            and (gy.data_ptr() | packed.data_ptr() | scales.data_ptr()) % 16 == 0)
+    if not fast:
+        w = _decode_lowbit(bits, packed, scales, (n, k), gy.dtype if gy.dtype.is_floating_point else torch.float32)
+        return gy.matmul(w).to(ydt)
+    _cabi.raise_pending()
+    dx = torch.empty((m, k), dtype=ydt, device=dev)
+    lib = _cabi.lib()
+    with torch.cuda.device(dev):
+        ws = _gemm_scratch(dev, lib.ojx_e8t_gemm_dx_workspace_bytes(m, n, k))
+        st = lib.ojx_e8t_gemm_dx_lowbit(bits, gy.data_ptr(), _dtype_code(gy.dtype), m, packed.data_ptr(), scales.data_ptr(), n, k,
+                                        32, dx.data_ptr(), _dtype_code(ydt), ws.data_ptr(), ws.numel(), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_gemm_dx_lowbit")
+    return dx
+
+
 def _gemm_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     """256-byte aligned scratch for the prefill kernel (status block + fp16 copy of bf16 activations)."""
     buf = scratch(device, nbytes + 256, "gemm")

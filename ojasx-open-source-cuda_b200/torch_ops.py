@@ -38,8 +38,7 @@ def _fwd2_cuda(x, packed_weight, block_scales, bias=None, group_size=32):
 
 def _bwd2_cuda(grad_y, packed_weight, block_scales, in_features, group_size=32):
     n = int(packed_weight.shape[0])
-    w = ops.decode_2bit(packed_weight.reshape(-1), block_scales.reshape(-1), (n, int(in_features)), grad_y.dtype)
-    return grad_y.matmul(w)
+    return ops.linear_dx_lowbit(2, grad_y, packed_weight.reshape(-1), block_scales.reshape(-1), n, int(in_features), group_size)
 
 
 def _proj_cuda(x):

@@ -683,3 +683,27 @@ def test_low_bit_layer_prefill_runs_on_the_tensor_core_kernel(P):
         y.float().sum().backward()
         gref = torch.ones(120, 96, device=dev) @ layer.unpack_weights(torch.float32)
         assert float((x.grad.float().reshape(120, 512) - gref).abs().max()) <= 2.0 ** -6 * float(gref.abs().max()) + 1e-3
+
+
+@pytest.mark.parametrize("bits", [2, 1])
+@pytest.mark.parametrize("m,k,n,dt", [(64, 256, 40, torch.float16), (300, 1024, 504, torch.bfloat16), (2048, 4096, 4096, torch.bfloat16),
+                                      (33, 512, 8, torch.bfloat16)])
+def test_low_bit_backward_dx_matches_dense_product(P, oracle, bits, m, k, n, dt):
+    """ojx_e8t_gemm_dx_lowbit: dX = dY . W for the 2.0-bit / 1.0-bit formats against the fp32 product with the weights
+    decoded to fp16 (the tensor cores' operand), within 2e-5 of sum |dy||w| per output; a weight-row count that is not a
+    multiple of the 64-row contraction block included."""
+    dev = torch.device(DEV)
+    w = torch.from_numpy(oracle.gen_normal(980 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
+    enc, dec = (P.ops.encode_2bit, P.ops.decode_2bit) if bits == 2 else (P.ops.encode_1bit, P.ops.decode_1bit)
+    pk, sc = enc(w, 32)
+    wd = dec(pk, sc, (n, k), torch.float16).float()
+    gy = torch.from_numpy(oracle.gen_normal(981 + m, m * n, 1.0).reshape(m, n).copy()).to(dt).to(dev)
+    gy[m // 3] *= 32.0
+    dx = P.ops.linear_dx_lowbit(bits, gy, pk, sc, n, k, 32, out_dtype=torch.float32)
+    P.ops.gemm_status(dev)
+    ref = gy.float() @ wd
+    budget = gy.float().abs() @ wd.abs()
+    assert float(((dx - ref).abs() / budget.clamp_min(1e-30)).max()) < 2e-5
+    # fp32 gradients take the decode-and-multiply route
+    dx32 = P.ops.linear_dx_lowbit(bits, gy.float(), pk, sc, n, k, 32)
+    assert dx32.dtype == torch.float32 and float((dx32 - gy.float() @ dec(pk, sc, (n, k), torch.float32)).abs().max()) <= 1e-3 * float(ref.abs().max())
