@@ -390,7 +390,7 @@ int32_t ojx_e8t_gemm(const void* x, int32_t x_dtype, int64_t M,
 int32_t ojx_e8t_gemm_status(const void* workspace, void* stream);
 
 /*
- * The same prefill kernel for the two sibling formats (`bits` 2 or 1; group 32, K % 256 == 0, 16-bit activations,
+ * The same prefill kernel for the two sibling formats (`bits` 2 or 1; group 8, 16 or 32, K % 256 == 0, 16-bit activations,
  * workspace and status exactly as for ojx_e8t_gemm): the decoder warps read the 2-bit / 1-bit codes instead of the
  * ternary ranks.  Replaces the 2.0-bit / 1.0-bit branches of _FusedE8GEMMFunction.forward
  * (ojasx2/math/lattice.py:596-624) for batches of tokens.  The weights enter the tensor cores as fp16: for 1 bit

@@ -285,7 +285,7 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 //              the number of weight COLUMNS (the output's feature dimension, tiled like N above) and p.K the number
 //              of weight rows (the contraction length, any positive value: the last block is zero-filled).  The
 //              decoded weights enter the MMA as an MN-major operand, so a decoded rank is still one 16-byte store.
-template <bool kDX, int kFmt = 0>              // kFmt: 0 ternary codes, 2 the 2.0-bit format, 1 the 1.0-bit format
+template <bool kDX, int kFmt = 0, int kG = 32> // kFmt: 0 ternary codes, 2 the 2.0-bit format, 1 the 1.0-bit format; kG: weights per scale (8 and 16 only for the sibling formats)
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -443,32 +443,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
             const uint8_t* digit_lane = reinterpret_cast<const uint8_t*>(lut) +
                                         (kFmt == 0 ? (lane & (kGemmDigitCopies - 1)) * 8 : (kFmt == 2 ? (lane & 7) * 8 : (lane & 3) * 16));
             constexpr int kWords = kFmt == 0 ? 3 : (kFmt == 2 ? 4 : 2);            // 32-bit words of codes per 64 columns
-            const int64_t row_bytes = kFmt == 0 ? (int64_t)p.N * 3 / 16 : (kFmt == 2 ? p.N / 4 : p.N / 8), row_scales = p.N / 32;
+            constexpr int kSW = 32 / kG;                                           // 32-bit words of scales per 64 columns
+            const int64_t row_bytes = kFmt == 0 ? (int64_t)p.N * 3 / 16 : (kFmt == 2 ? p.N / 4 : p.N / 8), row_scales = p.N / kG;
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
                 const int n_blk = tile % n_blocks;
                 const int col0 = n_blk * p.rows + kq * 64;                       // first weight column of this thread
                 const uint8_t* cbase = p.packed + (kFmt == 0 ? (int64_t)col0 * 3 / 16 : (kFmt == 2 ? col0 / 4 : col0 / 8));
-                const uint16_t* sbase = p.scales + col0 / 32;
-                auto fetch = [&](int kb, uint32_t (&cw)[4], uint32_t& sw) {
+                const uint16_t* sbase = p.scales + col0 / kG;
+                auto fetch = [&](int kb, uint32_t (&cw)[4], uint32_t (&sw)[kSW]) {
                     const int row = kb * kGemmBK + j;
                     if (row < p.K && col0 < p.N) {
                         const uint32_t* cp = reinterpret_cast<const uint32_t*>(cbase + (int64_t)row * row_bytes);
 #pragma unroll
                         for (int i = 0; i < kWords; ++i) cw[i] = __ldg(cp + i);
-                        sw = __ldg(reinterpret_cast<const uint32_t*>(sbase + (int64_t)row * row_scales));
+#pragma unroll
+                        for (int i = 0; i < kSW; ++i) sw[i] = __ldg(reinterpret_cast<const uint32_t*>(sbase + (int64_t)row * row_scales) + i);
                     } else if (kFmt == 0) {                                      // beyond the matrix: rank of the zero vector, scale 0
-                        cw[0] = 0x68668668u; cw[1] = 0x86686686u; cw[2] = 0x66866866u; sw = 0u;   // rank 1640 eight times
+                        cw[0] = 0x68668668u; cw[1] = 0x86686686u; cw[2] = 0x66866866u; sw[0] = 0u;   // rank 1640 eight times
                     } else {                                                     // any code, scale 0
-                        cw[0] = cw[1] = cw[2] = cw[3] = 0u; sw = 0u;
+                        cw[0] = cw[1] = cw[2] = cw[3] = 0u;
+#pragma unroll
+                        for (int i = 0; i < kSW; ++i) sw[i] = 0u;
                     }
                 };
-                uint32_t nw[4] = {0u, 0u, 0u, 0u}, ns;
+                uint32_t nw[4] = {0u, 0u, 0u, 0u}, ns[kSW];
                 fetch(0, nw, ns);
                 for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
                     uint32_t cw[4] = {nw[0], nw[1], nw[2], kWords == 4 ? nw[3] : 0u};
-                    const uint32_t sw = ns;
+                    uint32_t sw[kSW];
+#pragma unroll
+                    for (int i = 0; i < kSW; ++i) sw[i] = ns[i];
                     if (kb + 1 < k_blocks) fetch(kb + 1, nw, ns);                // the next stage's words travel during this one's decode
                     const int s = it % kGemmStages;
                     const uint32_t ph = (it / kGemmStages) & 1u;
@@ -500,10 +506,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
                                 hi8[q] = make_uint2(e.z, e.w);
                             }
                         }
-                        const uint32_t sc2 = prmt(sw, 0u, half == 0 ? 0x1010u : 0x3232u);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             const int c = half * 4 + q;
+                            const int si = 8 * c / kG;                              // scale of this 8-weight chunk
+                            const uint32_t sc2 = prmt(sw[si >> 1], 0u, (si & 1) == 0 ? 0x1010u : 0x3232u);
                             const uint4 v = make_uint4(hmul2_u32(lo8[q].x, sc2), hmul2_u32(lo8[q].y, sc2),
                                                        hmul2_u32(hi8[q].x, sc2), hmul2_u32(hi8[q].y, sc2));
                             *reinterpret_cast<uint4*>(arow + ((c ^ (j & 7)) << 4)) = v;
@@ -522,26 +529,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         const uint8_t* tab_lane = reinterpret_cast<const uint8_t*>(lut) + (kFmt == 2 ? (lane & 7) * 8 : (lane & 3) * 16);   // entry stride 64 B
         uint32_t it = 0;
         bool ok = true;
-        const int64_t row_bytes = kFmt == 2 ? p.K / 4 : p.K / 8, row_scales = p.K / 32;
+        constexpr int kSV = 32 / kG;                     // 16-byte vectors of scales per 256 k
+        const int64_t row_bytes = kFmt == 2 ? p.K / 4 : p.K / 8, row_scales = p.K / kG;
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             const int n_blk = tile % n_blocks;
             const int row = min(n_blk * p.rows + r, p.N - 1);
             const uint4* cptr = reinterpret_cast<const uint4*>(p.packed + row * row_bytes);
             const uint4* sptr = reinterpret_cast<const uint4*>(p.scales + row * row_scales);
             const int chunks = p.K / 256;
-            uint4 cv[kVec];
+            uint4 cv[kVec], sv[kSV];
 #pragma unroll
             for (int i = 0; i < kVec; ++i) cv[i] = __ldg(cptr + i);
-            uint4 sc = __ldg(sptr);
+#pragma unroll
+            for (int i = 0; i < kSV; ++i) sv[i] = __ldg(sptr + i);
             for (int ch = 0; ch < chunks && ok; ++ch) {
-                uint32_t cw[4 * kVec];
+                uint32_t cw[4 * kVec], sw[4 * kSV];
 #pragma unroll
                 for (int i = 0; i < kVec; ++i) { cw[4 * i] = cv[i].x; cw[4 * i + 1] = cv[i].y; cw[4 * i + 2] = cv[i].z; cw[4 * i + 3] = cv[i].w; }
-                const uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+                for (int i = 0; i < kSV; ++i) { sw[4 * i] = sv[i].x; sw[4 * i + 1] = sv[i].y; sw[4 * i + 2] = sv[i].z; sw[4 * i + 3] = sv[i].w; }
                 if (ch + 1 < chunks) {                   // prefetch the next 256 k of this row
 #pragma unroll
                     for (int i = 0; i < kVec; ++i) cv[i] = __ldg(cptr + kVec * (ch + 1) + i);
-                    sc = __ldg(sptr + ch + 1);
+#pragma unroll
+                    for (int i = 0; i < kSV; ++i) sv[i] = __ldg(sptr + kSV * (ch + 1) + i);
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q, ++it) {
@@ -566,10 +577,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
                                 hi8[j] = make_uint2(e.z, e.w);
                             }
                         }
-                        const uint32_t sc2 = prmt(sw[q], 0u, half == 0 ? 0x1010u : 0x3232u);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const int jj = half * 4 + j;
+                            const int si = (64 * q + 8 * jj) / kG;                 // scale of this 8-weight chunk inside the 256 k
+                            const uint32_t sc2 = prmt(sw[si >> 1], 0u, (si & 1) == 0 ? 0x1010u : 0x3232u);
                             const uint4 v = make_uint4(hmul2_u32(lo8[j].x, sc2), hmul2_u32(lo8[j].y, sc2),
                                                        hmul2_u32(hi8[j].x, sc2), hmul2_u32(hi8[j].y, sc2));
                             *reinterpret_cast<uint4*>(arow + ((jj ^ (r & 7)) << 4)) = v;
@@ -686,6 +698,20 @@ static PFN_encodeTiled get_encode_tiled() {
     return fn;
 }
 
+// The kernel instance for a format and a scale-group size (null: not built), and its slot in the per-kernel tables.
+using GemmKernelFn = void (*)(const CUtensorMap, const GemmParams);
+template <bool kDX>
+inline GemmKernelFn gemm_kernel_for(int fmt, int group, int* slot) {
+    if (fmt == 0 && group == 32) { *slot = 0; return gemm_tcgen05_kernel<kDX, 0, 32>; }
+    if (fmt == 2 && group == 32) { *slot = 1; return gemm_tcgen05_kernel<kDX, 2, 32>; }
+    if (fmt == 2 && group == 16) { *slot = 2; return gemm_tcgen05_kernel<kDX, 2, 16>; }
+    if (fmt == 2 && group == 8) { *slot = 3; return gemm_tcgen05_kernel<kDX, 2, 8>; }
+    if (fmt == 1 && group == 32) { *slot = 4; return gemm_tcgen05_kernel<kDX, 1, 32>; }
+    if (fmt == 1 && group == 16) { *slot = 5; return gemm_tcgen05_kernel<kDX, 1, 16>; }
+    if (fmt == 1 && group == 8) { *slot = 6; return gemm_tcgen05_kernel<kDX, 1, 8>; }
+    return nullptr;
+}
+
 inline bool gemm_fast_ok(int64_t M, int64_t N, int64_t K, int group, int x_dtype) {
     return M >= 1 && N >= 1 && K >= 256 && K % 256 == 0 && group == 32 &&
            (x_dtype == OJX_BF16 || x_dtype == OJX_F16) && M < (1 << 30) && N < (1 << 30) && K < (1 << 30);
@@ -712,7 +738,9 @@ int32_t gemm_fmt_impl(int fmt, const void* x, int x_dtype, int64_t M, const uint
     OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
     if (fmt == 0) group = effective_group(group);
-    OJX_RETURN_IF(!gemm_fast_ok(M, N, K, group, x_dtype), OJX_ERR_UNSUPPORTED);
+    int slot = 0;
+    const GemmKernelFn kernel = gemm_kernel_for<false>(fmt, group, &slot);      // sibling formats: groups of 8, 16 or 32
+    OJX_RETURN_IF(kernel == nullptr || !gemm_fast_ok(M, N, K, 32, x_dtype), OJX_ERR_UNSUPPORTED);
     OJX_RETURN_IF(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) |
                     reinterpret_cast<uintptr_t>(scales)) & 15) != 0, OJX_ERR_ALIGN);
     const bool convert = x_dtype == OJX_BF16;
@@ -741,11 +769,8 @@ int32_t gemm_fmt_impl(int fmt, const void* x, int x_dtype, int64_t M, const uint
             }
     }
 
-    static std::atomic<uint64_t> configured[3];                  // per format; one bit per device: the opt-in is per context
-    OJX_RETURN_IF((fmt == 0 ? ensure_dynamic_smem(gemm_tcgen05_kernel<false, 0>, kGemmSmemBytes, configured[0])
-                   : fmt == 2 ? ensure_dynamic_smem(gemm_tcgen05_kernel<false, 2>, kGemmSmemBytes, configured[2])
-                              : ensure_dynamic_smem(gemm_tcgen05_kernel<false, 1>, kGemmSmemBytes, configured[1])) != OJX_OK,
-                  OJX_ERR_LAUNCH);
+    static std::atomic<uint64_t> configured[7];                  // per kernel; one bit per device: the opt-in is per context
+    OJX_RETURN_IF(ensure_dynamic_smem(kernel, kGemmSmemBytes, configured[slot]) != OJX_OK, OJX_ERR_LAUNCH);
     if (convert) {
         if (K <= 4096)
             normalize_rows_bf16_to_f16_kernel<32, 16><<<(unsigned)((M + 7) / 8), 256, 0, s>>>(
@@ -774,7 +799,7 @@ int32_t gemm_fmt_impl(int fmt, const void* x, int x_dtype, int64_t M, const uint
             return OJX_ERR_LAUNCH;
         GemmParams prm;
         prm.packed = packed + (fmt == 0 ? (size_t)n0 * (size_t)K * 3 / 16 : (size_t)n0 * (size_t)K / (fmt == 2 ? 4 : 8));
-        prm.scales = scales + (size_t)n0 * (size_t)K / 32;
+        prm.scales = scales + (size_t)n0 * (size_t)K / (size_t)group;
         prm.bias = bias ? static_cast<const uint8_t*>(bias) + (size_t)n0 * dtype_size(x_dtype) : nullptr;
         prm.y = static_cast<uint8_t*>(y) + ((size_t)m0 * (size_t)N + (size_t)n0) * dtype_size(y_dtype);
         prm.status = static_cast<int32_t*>(workspace);
@@ -789,9 +814,7 @@ int32_t gemm_fmt_impl(int fmt, const void* x, int x_dtype, int64_t M, const uint
         const int64_t all = ((Ns + rows - 1) / rows) * ((Ms + bn - 1) / bn);
         prm.tile_limit = (int)(all < tile_limit ? all : tile_limit);
         const int grid = prm.tile_limit < num_sms() ? prm.tile_limit : num_sms();
-        if (fmt == 0) gemm_tcgen05_kernel<false, 0><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
-        else if (fmt == 2) gemm_tcgen05_kernel<false, 2><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
-        else gemm_tcgen05_kernel<false, 1><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+        kernel<<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
         return launch_status();
     };
 
@@ -837,7 +860,9 @@ int32_t gemm_dx_fmt_impl(int fmt, const void* gy, int gy_dtype, int64_t M, const
     OJX_RETURN_IF(dtype_size(gy_dtype) == 0 || dtype_size(dx_dtype) == 0, OJX_ERR_DTYPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
     if (fmt == 0) group = effective_group(group);
-    OJX_RETURN_IF(!gemm_dx_ok(M, N, K, group, gy_dtype), OJX_ERR_UNSUPPORTED);
+    int slot = 0;
+    const GemmKernelFn kernel = gemm_kernel_for<true>(fmt, group, &slot);
+    OJX_RETURN_IF(kernel == nullptr || !gemm_dx_ok(M, N, K, 32, gy_dtype), OJX_ERR_UNSUPPORTED);
     OJX_RETURN_IF(((reinterpret_cast<uintptr_t>(gy) | reinterpret_cast<uintptr_t>(packed) |
                     reinterpret_cast<uintptr_t>(scales)) & 15) != 0, OJX_ERR_ALIGN);
     const bool convert = gy_dtype == OJX_BF16;
@@ -864,11 +889,8 @@ int32_t gemm_dx_fmt_impl(int fmt, const void* gy, int gy_dtype, int64_t M, const
                 if (cost < best) { best = cost; rows = cand_rows[ri]; bn = cand_bn[bi]; }
             }
     }
-    static std::atomic<uint64_t> configured[3];
-    OJX_RETURN_IF((fmt == 0 ? ensure_dynamic_smem(gemm_tcgen05_kernel<true, 0>, kGemmSmemBytes, configured[0])
-                   : fmt == 2 ? ensure_dynamic_smem(gemm_tcgen05_kernel<true, 2>, kGemmSmemBytes, configured[2])
-                              : ensure_dynamic_smem(gemm_tcgen05_kernel<true, 1>, kGemmSmemBytes, configured[1])) != OJX_OK,
-                  OJX_ERR_LAUNCH);
+    static std::atomic<uint64_t> configured[7];
+    OJX_RETURN_IF(ensure_dynamic_smem(kernel, kGemmSmemBytes, configured[slot]) != OJX_OK, OJX_ERR_LAUNCH);
     if (convert) {
         // per-token power-of-two factors exactly as in the forward launch; rows here are N long (any multiple of 8)
         if (N <= 4096)
@@ -905,9 +927,7 @@ int32_t gemm_dx_fmt_impl(int fmt, const void* gy, int gy_dtype, int64_t M, const
     const int64_t all = ((K + rows - 1) / rows) * ((M + bn - 1) / bn);
     prm.tile_limit = (int)(all < (1 << 30) ? all : (1 << 30));
     const int grid = prm.tile_limit < num_sms() ? prm.tile_limit : num_sms();
-    if (fmt == 0) gemm_tcgen05_kernel<true, 0><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
-    else if (fmt == 2) gemm_tcgen05_kernel<true, 2><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
-    else gemm_tcgen05_kernel<true, 1><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
+    kernel<<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmap, prm);
     return launch_status();
 }
 

@@ -167,14 +167,14 @@ def _linear_lowbit(bits: int, x: torch.Tensor, packed: torch.Tensor, scales: tor
         return y
     b = None if bias is None else bias.detach().to(x2.dtype).contiguous()
     lib = _cabi.lib()
-    if (m > LOWBIT_GEMV_MAX_M and int(group_size) == 32 and k % 256 == 0 and x2.dtype in (torch.bfloat16, torch.float16)
+    if (m > LOWBIT_GEMV_MAX_M and int(group_size) in (8, 16, 32) and k % 256 == 0 and x2.dtype in (torch.bfloat16, torch.float16)
             and packed.numel() * (4 if bits == 2 else 8) == n * k
             and (x2.data_ptr() | packed.data_ptr() | scales.data_ptr()) % 16 == 0):
         # batches of tokens: the tcgen05 prefill kernel with this format's decoder
         with torch.cuda.device(dev):
             ws = _gemm_scratch(dev, lib.ojx_e8t_gemm_workspace_bytes(m, n, k))
             st = lib.ojx_e8t_gemm_lowbit(bits, x2.data_ptr(), _dtype_code(x2.dtype), m, packed.data_ptr(), scales.data_ptr(),
-                                         None if b is None else b.data_ptr(), n, k, 32, y.data_ptr(), _dtype_code(y.dtype),
+                                         None if b is None else b.data_ptr(), n, k, int(group_size), y.data_ptr(), _dtype_code(y.dtype),
                                          ws.data_ptr(), ws.numel(), _stream_ptr(dev))
         _cabi.check(st, "ojx_e8t_gemm_lowbit")
         return y
@@ -204,7 +204,7 @@ def decode_2bit(packed: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, in
 def linear_2bit(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor], n: int, k: int,
                 group_size: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``y = x . W^T (+ bias)`` from 2-bit codes: up to eight rows of x run the decode kernels (int8 tensor cores for
-    groups of 32 and K % 2048 == 0), more rows with 16-bit activations, groups of 32 and K % 256 == 0 the tcgen05
+    groups of 32 and K % 2048 == 0), more rows with 16-bit activations, groups of 8, 16 or 32 and K % 256 == 0 the tcgen05
     prefill kernel (weights rounded to fp16 once, as ``decode_2bit(..., torch.float16)`` gives them), anything else
     a scalar fp32 kernel."""
     return _linear_lowbit(2, x, packed, scales, bias, n, k, group_size, out_dtype)
@@ -466,7 +466,7 @@ def linear_dx_lowbit(bits: int, grad_y2d: torch.Tensor, packed: torch.Tensor, sc
                      in_features: int, group_size: int = 32, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """dX[M, K] = dY[M, N] . W[N, K] for the 2.0-bit (``bits`` 2) or 1.0-bit (``bits`` 1) format straight from the
     packed codes (``ojx_e8t_gemm_dx_lowbit``; the weights enter the tensor cores as fp16).  Shapes the kernel does not
-    take (fp32 gradients, K % 256 != 0, N % 8 != 0, groups other than 32) decode W and multiply."""
+    take (fp32 gradients, K % 256 != 0, N % 8 != 0, groups other than 8, 16 and 32) decode W and multiply."""
     n, k = int(out_features), int(in_features)
     dev = _require_cuda(grad_y2d, packed, scales)
     if grad_y2d.dim() != 2 or grad_y2d.shape[1] != n:
@@ -476,7 +476,7 @@ def linear_dx_lowbit(bits: int, grad_y2d: torch.Tensor, packed: torch.Tensor, sc
     ydt = out_dtype or gy.dtype
     if m == 0:
         return torch.empty((0, k), dtype=ydt, device=dev)
-    fast = (gy.dtype in (torch.bfloat16, torch.float16) and k % 256 == 0 and n % 8 == 0 and int(group_size) == 32
+    fast = (gy.dtype in (torch.bfloat16, torch.float16) and k % 256 == 0 and n % 8 == 0 and int(group_size) in (8, 16, 32)
             and packed.numel() * (4 if bits == 2 else 8) == n * k
             and (gy.data_ptr() | packed.data_ptr() | scales.data_ptr()) % 16 == 0)
     if not fast:
@@ -488,7 +488,7 @@ def linear_dx_lowbit(bits: int, grad_y2d: torch.Tensor, packed: torch.Tensor, sc
     with torch.cuda.device(dev):
         ws = _gemm_scratch(dev, lib.ojx_e8t_gemm_dx_workspace_bytes(m, n, k))
         st = lib.ojx_e8t_gemm_dx_lowbit(bits, gy.data_ptr(), _dtype_code(gy.dtype), m, packed.data_ptr(), scales.data_ptr(), n, k,
-                                        32, dx.data_ptr(), _dtype_code(ydt), ws.data_ptr(), ws.numel(), _stream_ptr(dev))
+                                        int(group_size), dx.data_ptr(), _dtype_code(ydt), ws.data_ptr(), ws.numel(), _stream_ptr(dev))
     _cabi.check(st, "ojx_e8t_gemm_dx_lowbit")
     return dx
 

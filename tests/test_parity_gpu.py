@@ -579,7 +579,7 @@ def test_low_bit_decode_linear_matches_dense_product(P, oracle, bits, m, k, n, g
     pk, sc = enc(w, group)
     # more than eight rows of 16-bit activations with groups of 32 and K % 256 == 0 run the prefill kernel, whose
     # operand is the weight rounded to fp16
-    prefill = m > 8 and group == 32 and k % 256 == 0 and dt != torch.float32
+    prefill = m > 8 and group in (8, 16, 32) and k % 256 == 0 and dt != torch.float32
     wd = dec(pk, sc, (n, k), torch.float16).float() if prefill else dec(pk, sc, (n, k), torch.float32)
     x = torch.from_numpy(oracle.gen_normal(901 + m, m * k, 1.0).reshape(m, k).copy()).to(dt).to(dev)
     bias = torch.from_numpy(oracle.gen_normal(902, n, 0.1).copy()).to(dt).to(dev)
@@ -639,28 +639,30 @@ def test_low_bit_tensor_core_kernels(P, oracle, bits, m, k, n, dt):
 
 
 @pytest.mark.parametrize("bits", [2, 1])
-@pytest.mark.parametrize("m,k,n,dt,with_bias", [(64, 256, 40, torch.float16, False), (17, 512, 256, torch.float16, True),
-                                                (300, 1024, 500, torch.bfloat16, True), (2048, 4096, 4096, torch.bfloat16, False),
-                                                (129, 2048, 8, torch.bfloat16, False)])
-def test_low_bit_prefill_gemm_matches_dense_product(P, oracle, bits, m, k, n, dt, with_bias):
+@pytest.mark.parametrize("m,k,n,dt,with_bias,group", [(64, 256, 40, torch.float16, False, 32), (17, 512, 256, torch.float16, True, 32),
+                                                      (300, 1024, 500, torch.bfloat16, True, 32), (2048, 4096, 4096, torch.bfloat16, False, 32),
+                                                      (129, 2048, 8, torch.bfloat16, False, 32), (300, 1024, 500, torch.bfloat16, True, 8),
+                                                      (70, 512, 264, torch.float16, False, 16), (512, 4096, 1024, torch.bfloat16, False, 8)])
+def test_low_bit_prefill_gemm_matches_dense_product(P, oracle, bits, m, k, n, dt, with_bias, group):
     """ojx_e8t_gemm_lowbit (the tcgen05 prefill kernel with the 2.0-bit / 1.0-bit decoders) against the fp32 product
     with the weights decoded to fp16 - the operand the tensor cores see: fp32 accumulation of exact products, so the
-    error stays within 2e-5 of sum |x||w| per output; tile edges in both directions included."""
+    error stays within 2e-5 of sum |x||w| per output; tile edges in both directions and scale groups of 8, 16 and 32
+    weights (the reference layer's default is 8) included."""
     dev = torch.device(DEV)
     w = torch.from_numpy(oracle.gen_normal(970 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
     enc, dec, lin = ((P.ops.encode_2bit, P.ops.decode_2bit, P.ops.linear_2bit) if bits == 2
                      else (P.ops.encode_1bit, P.ops.decode_1bit, P.ops.linear_1bit))
-    pk, sc = enc(w, 32)
+    pk, sc = enc(w, group)
     wd = dec(pk, sc, (n, k), torch.float16).float()
     x = torch.from_numpy(oracle.gen_normal(971 + m, m * k, 1.0).reshape(m, k).copy()).to(dt).to(dev)
     x[m // 2] *= 64.0                                                    # rows on different scales
     bias = torch.from_numpy(oracle.gen_normal(972, n, 0.1).copy()).to(dt).to(dev) if with_bias else None
-    y = lin(x, pk, sc, bias, n, k, 32, out_dtype=torch.float32)
+    y = lin(x, pk, sc, bias, n, k, group, out_dtype=torch.float32)
     P.ops.gemm_status(dev)
     ref = x.float() @ wd.t() + (bias.float() if with_bias else 0.0)
     budget = x.float().abs() @ wd.abs().t() + (bias.float().abs() if with_bias else 0.0)
     assert float(((y - ref).abs() / budget.clamp_min(1e-30)).max()) < 2e-5
-    y16 = lin(x, pk, sc, bias, n, k, 32)
+    y16 = lin(x, pk, sc, bias, n, k, group)
     assert y16.dtype == dt and float((y16.float() - ref).abs().max()) <= 2.0 ** -7 * float(ref.abs().max()) + 1e-3
     if bits == 2:                                                        # the fp16 rounding of (code - 1.5) * scale is within the tolerance of the path
         exact = x.float() @ dec(pk, sc, (n, k), torch.float32).t() + (bias.float() if with_bias else 0.0)
@@ -674,7 +676,8 @@ def test_low_bit_layer_prefill_runs_on_the_tensor_core_kernel(P):
     torch.manual_seed(11)
     for bitrate in (2.0, 1.0):
         lin = torch.nn.Linear(512, 96, bias=True).to(dev).to(torch.bfloat16)
-        layer = P.E8LatticeLinear.from_linear(lin, rank=0, bitrate=bitrate, group_size=32)
+        layer = P.E8LatticeLinear.from_linear(lin, rank=0, bitrate=bitrate)           # the reference's default group size: 8
+        assert layer.group_size == 8
         wd = layer.unpack_weights(torch.float16).float()
         x = torch.randn(3, 40, 512, device=dev, dtype=torch.bfloat16, requires_grad=True)
         y = layer(x)
@@ -686,24 +689,26 @@ def test_low_bit_layer_prefill_runs_on_the_tensor_core_kernel(P):
 
 
 @pytest.mark.parametrize("bits", [2, 1])
-@pytest.mark.parametrize("m,k,n,dt", [(64, 256, 40, torch.float16), (300, 1024, 504, torch.bfloat16), (2048, 4096, 4096, torch.bfloat16),
-                                      (33, 512, 8, torch.bfloat16)])
-def test_low_bit_backward_dx_matches_dense_product(P, oracle, bits, m, k, n, dt):
+@pytest.mark.parametrize("m,k,n,dt,group", [(64, 256, 40, torch.float16, 32), (300, 1024, 504, torch.bfloat16, 32),
+                                            (2048, 4096, 4096, torch.bfloat16, 32), (33, 512, 8, torch.bfloat16, 32),
+                                            (300, 1024, 504, torch.bfloat16, 8), (64, 512, 72, torch.float16, 16),
+                                            (512, 4096, 1024, torch.bfloat16, 8)])
+def test_low_bit_backward_dx_matches_dense_product(P, oracle, bits, m, k, n, dt, group):
     """ojx_e8t_gemm_dx_lowbit: dX = dY . W for the 2.0-bit / 1.0-bit formats against the fp32 product with the weights
     decoded to fp16 (the tensor cores' operand), within 2e-5 of sum |dy||w| per output; a weight-row count that is not a
     multiple of the 64-row contraction block included."""
     dev = torch.device(DEV)
     w = torch.from_numpy(oracle.gen_normal(980 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
     enc, dec = (P.ops.encode_2bit, P.ops.decode_2bit) if bits == 2 else (P.ops.encode_1bit, P.ops.decode_1bit)
-    pk, sc = enc(w, 32)
+    pk, sc = enc(w, group)
     wd = dec(pk, sc, (n, k), torch.float16).float()
     gy = torch.from_numpy(oracle.gen_normal(981 + m, m * n, 1.0).reshape(m, n).copy()).to(dt).to(dev)
     gy[m // 3] *= 32.0
-    dx = P.ops.linear_dx_lowbit(bits, gy, pk, sc, n, k, 32, out_dtype=torch.float32)
+    dx = P.ops.linear_dx_lowbit(bits, gy, pk, sc, n, k, group, out_dtype=torch.float32)
     P.ops.gemm_status(dev)
     ref = gy.float() @ wd
     budget = gy.float().abs() @ wd.abs()
     assert float(((dx - ref).abs() / budget.clamp_min(1e-30)).max()) < 2e-5
     # fp32 gradients take the decode-and-multiply route
-    dx32 = P.ops.linear_dx_lowbit(bits, gy.float(), pk, sc, n, k, 32)
+    dx32 = P.ops.linear_dx_lowbit(bits, gy.float(), pk, sc, n, k, group)
     assert dx32.dtype == torch.float32 and float((dx32 - gy.float() @ dec(pk, sc, (n, k), torch.float32)).abs().max()) <= 1e-3 * float(ref.abs().max())
