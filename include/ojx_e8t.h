@@ -372,7 +372,8 @@ int32_t ojx_e8t_enable_peer_access(int32_t peer_device);
 /*
  * Prefill-shape linear (large M) on the tcgen05 tensor cores.  Same contract as ojx_e8t_gemv;
  * replaces the reference's TileLang builder (ojasx2/tilelang_kernels.py:277-363) and the
- * unpack + F.linear path (lattice.py:613-624).  Requires K % 256 == 0, group 32, bf16 or fp16 x.
+ * unpack + F.linear path (lattice.py:613-624).  Requires K % 256 == 0, group 32 or 16, bf16 or fp16 x (any M >= 1:
+ * groups of 16, which have no decode-shape kernel of their own, are best sent here at every batch size).
  * `workspace` (256-byte aligned, size from ojx_e8t_gemm_workspace_bytes) holds a status block and,
  * for bf16 activations, one power-of-two factor per token row and the fp16 copy of the activations
  * scaled by it (each row's largest magnitude is brought into [2^14, 2^15); the row's outputs are
@@ -409,7 +410,7 @@ int32_t ojx_e8t_gemm_lowbit(int32_t bits, const void* x, int32_t x_dtype, int64_
  * MN-major operand, so no dense or transposed copy of W ever exists).  Replaces the decode-then-matmul of
  * _FusedE8GEMMFunction.backward (ojasx2/math/lattice.py:642-717) and the reference's native
  * fused_ternary_e8_gemm_backward_dx (ojasx2/math/csrc/ojasx_math_core.hpp:641-702, schema
- * ojasx_math_bindings.cpp:594).  Requires K % 256 == 0, N % 8 == 0, group 32, bf16 or fp16 dY; fp32 accumulation;
+ * ojasx_math_bindings.cpp:594).  Requires K % 256 == 0, N % 8 == 0, group 32 or 16, bf16 or fp16 dY; fp32 accumulation;
  * workspace as for ojx_e8t_gemm (size from ojx_e8t_gemm_dx_workspace_bytes; ojx_e8t_gemm_status reports on it).
  */
 size_t  ojx_e8t_gemm_dx_workspace_bytes(int64_t M, int64_t N, int64_t K);

@@ -598,20 +598,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         const uint8_t* digit_lane = reinterpret_cast<const uint8_t*>(lut) + (lane & (kGemmDigitCopies - 1)) * 8;
         uint32_t it = 0;
         bool ok = true;
-        const int64_t row_bytes = (int64_t)p.K * 3 / 16, row_scales = p.K / 32;
+        constexpr int kSV = 32 / kG;                     // 16-byte vectors of scales per 256 k (groups of 32 or 16)
+        const int64_t row_bytes = (int64_t)p.K * 3 / 16, row_scales = p.K / kG;
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             const int n_blk = tile % n_blocks;
             const int row = min(n_blk * p.rows + r, p.N - 1);
             const uint4* cptr = reinterpret_cast<const uint4*>(p.packed + row * row_bytes);
             const uint4* sptr = reinterpret_cast<const uint4*>(p.scales + row * row_scales);
             const int chunks = p.K / 256;
-            uint4 c0 = __ldg(cptr), c1 = __ldg(cptr + 1), c2 = __ldg(cptr + 2), sc = __ldg(sptr);
+            uint4 c0 = __ldg(cptr), c1 = __ldg(cptr + 1), c2 = __ldg(cptr + 2), sv[kSV];
+#pragma unroll
+            for (int i = 0; i < kSV; ++i) sv[i] = __ldg(sptr + i);
             for (int ch = 0; ch < chunks && ok; ++ch) {
                 uint32_t cw[12] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w, c2.x, c2.y, c2.z, c2.w};
-                uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
+                uint32_t sw[4 * kSV];
+#pragma unroll
+                for (int i = 0; i < kSV; ++i) { sw[4 * i] = sv[i].x; sw[4 * i + 1] = sv[i].y; sw[4 * i + 2] = sv[i].z; sw[4 * i + 3] = sv[i].w; }
                 if (ch + 1 < chunks) {                   // prefetch the next 256 k of this row
                     c0 = __ldg(cptr + 3 * (ch + 1)); c1 = __ldg(cptr + 3 * (ch + 1) + 1);
-                    c2 = __ldg(cptr + 3 * (ch + 1) + 2); sc = __ldg(sptr + ch + 1);
+                    c2 = __ldg(cptr + 3 * (ch + 1) + 2);
+#pragma unroll
+                    for (int i = 0; i < kSV; ++i) sv[i] = __ldg(sptr + kSV * (ch + 1) + i);
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q, ++it) {
@@ -637,12 +644,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
                             lo8[j] = *reinterpret_cast<const uint2*>(digit_lane + u * (kGemmDigitCopies * 8));   // coordinates 0-3
                             hi8[j] = *reinterpret_cast<const uint2*>(digit_lane + v * (kGemmDigitCopies * 8));   // coordinates 4-7
                         }
-                        // the four ranks of a half are one scale group (32 k)
-                        const uint32_t sp = sw[q];
-                        const uint32_t sc2 = prmt(sp, 0u, half == 0 ? 0x1010u : 0x3232u);
+                        // the four ranks of a half are one scale group of 32, or two of 16
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const int jj = half * 4 + j;
+                            const int si = (64 * q + 8 * jj) / kG;
+                            const uint32_t sc2 = prmt(sw[si >> 1], 0u, (si & 1) == 0 ? 0x1010u : 0x3232u);
                             const uint4 v = make_uint4(hmul2_u32(lo8[j].x, sc2), hmul2_u32(lo8[j].y, sc2),
                                                        hmul2_u32(hi8[j].x, sc2), hmul2_u32(hi8[j].y, sc2));
                             *reinterpret_cast<uint4*>(arow + ((jj ^ (r & 7)) << 4)) = v;
@@ -703,6 +710,7 @@ using GemmKernelFn = void (*)(const CUtensorMap, const GemmParams);
 template <bool kDX>
 inline GemmKernelFn gemm_kernel_for(int fmt, int group, int* slot) {
     if (fmt == 0 && group == 32) { *slot = 0; return gemm_tcgen05_kernel<kDX, 0, 32>; }
+    if (fmt == 0 && group == 16) { *slot = 7; return gemm_tcgen05_kernel<kDX, 0, 16>; }
     if (fmt == 2 && group == 32) { *slot = 1; return gemm_tcgen05_kernel<kDX, 2, 32>; }
     if (fmt == 2 && group == 16) { *slot = 2; return gemm_tcgen05_kernel<kDX, 2, 16>; }
     if (fmt == 2 && group == 8) { *slot = 3; return gemm_tcgen05_kernel<kDX, 2, 8>; }
@@ -769,7 +777,7 @@ int32_t gemm_fmt_impl(int fmt, const void* x, int x_dtype, int64_t M, const uint
             }
     }
 
-    static std::atomic<uint64_t> configured[7];                  // per kernel; one bit per device: the opt-in is per context
+    static std::atomic<uint64_t> configured[8];                  // per kernel; one bit per device: the opt-in is per context
     OJX_RETURN_IF(ensure_dynamic_smem(kernel, kGemmSmemBytes, configured[slot]) != OJX_OK, OJX_ERR_LAUNCH);
     if (convert) {
         if (K <= 4096)
@@ -889,7 +897,7 @@ int32_t gemm_dx_fmt_impl(int fmt, const void* gy, int gy_dtype, int64_t M, const
                 if (cost < best) { best = cost; rows = cand_rows[ri]; bn = cand_bn[bi]; }
             }
     }
-    static std::atomic<uint64_t> configured[7];
+    static std::atomic<uint64_t> configured[8];
     OJX_RETURN_IF(ensure_dynamic_smem(kernel, kGemmSmemBytes, configured[slot]) != OJX_OK, OJX_ERR_LAUNCH);
     if (convert) {
         // per-token power-of-two factors exactly as in the forward launch; rows here are N long (any multiple of 8)

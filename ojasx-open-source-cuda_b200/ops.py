@@ -389,9 +389,9 @@ def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: 
            out_dtype: Optional[torch.dtype] = None, force: Optional[str] = None) -> torch.Tensor:
     """y[M, N] = x[M, K] . dequant(W)^T (+ bias), output in x's dtype unless ``out_dtype`` is given.
 
-    Routing: M <= 16 -> decode-shape kernel (``ojx_e8t_gemv``); larger M with K % 256 == 0 and 16-bit
-    activations -> tcgen05 kernel (``ojx_e8t_gemm``); everything else -> the generic kernel inside
-    ``ojx_e8t_gemv``.  ``force`` ("gemv" or "gemm") overrides the routing for tests.
+    Routing: M <= 16 -> decode-shape kernel (``ojx_e8t_gemv``); larger M with K % 256 == 0, 16-bit
+    activations and groups of 32 or 16 -> tcgen05 kernel (``ojx_e8t_gemm``; groups of 16 take it at every M);
+    everything else -> the generic kernel inside ``ojx_e8t_gemv``.  ``force`` ("gemv" or "gemm") overrides the routing for tests.
     """
     n, k = int(out_features), int(in_features)
     dev, x2d, pk, sc, b = _prep_linear(x2d, packed, scales, bias, n, k)
@@ -403,7 +403,9 @@ def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: 
         return y
     g = effective_group(group_size)
     lib = _cabi.lib()
-    use_gemm = (m > GEMV_MAX_M and k % 256 == 0 and g == 32 and x2d.dtype in (torch.bfloat16, torch.float16)
+    # groups of 16 (what the reference layer's default group size of 8 becomes for this format) have no decode-shape
+    # kernel of their own: they take the tensor-core kernel at every batch size rather than the scalar kernel
+    use_gemm = ((m > GEMV_MAX_M or g == 16) and k % 256 == 0 and g in (16, 32) and x2d.dtype in (torch.bfloat16, torch.float16)
                 and (k * 3 // 16) * n == pk.numel())
     if force == "gemm":
         use_gemm = True
@@ -445,7 +447,7 @@ def linear_dx(grad_y2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor
     g = effective_group(group_size)
     if m == 0:
         return torch.empty((0, k), dtype=ydt, device=dev)
-    fast = (gy.dtype in (torch.bfloat16, torch.float16) and k % 256 == 0 and n % 8 == 0 and g == 32
+    fast = (gy.dtype in (torch.bfloat16, torch.float16) and k % 256 == 0 and n % 8 == 0 and g in (16, 32)
             and (k * 3 // 16) * n == packed.numel())
     if not fast:
         w = decode(packed, scales, (n, k), gy.dtype if gy.dtype.is_floating_point else torch.float32)

@@ -712,3 +712,35 @@ def test_low_bit_backward_dx_matches_dense_product(P, oracle, bits, m, k, n, dt,
     # fp32 gradients take the decode-and-multiply route
     dx32 = P.ops.linear_dx_lowbit(bits, gy.float(), pk, sc, n, k, group)
     assert dx32.dtype == torch.float32 and float((dx32 - gy.float() @ dec(pk, sc, (n, k), torch.float32)).abs().max()) <= 1e-3 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("m,k,n,dt", [(1, 512, 40, torch.bfloat16), (5, 4096, 1000, torch.float16), (300, 1024, 520, torch.bfloat16),
+                                      (2048, 4096, 4096, torch.bfloat16)])
+def test_ternary_groups_of_16_run_the_tensor_core_kernels(P, oracle, m, k, n, dt):
+    """Ternary codes with one scale per 16 weights (what the reference layer's default group size of 8 becomes for this
+    format, ojasx2/math/lattice.py:750-751): forward (at every batch size) and backward through the tcgen05 kernels against
+    the fp32 products with the decoded weights, which are exact in fp16 - within 2e-5 of sum |x||w| per output."""
+    dev = torch.device(DEV)
+    w = torch.from_numpy(oracle.gen_normal(990 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
+    pk, sc = P.ops.encode(w, 16)
+    assert sc.numel() == n * k // 16
+    wd = P.ops.decode(pk, sc, (n, k), torch.float32)
+    x = torch.from_numpy(oracle.gen_normal(991 + m, m * k, 1.0).reshape(m, k).copy()).to(dt).to(dev)
+    bias = torch.from_numpy(oracle.gen_normal(992, n, 0.1).copy()).to(dt).to(dev)
+    y = P.ops.linear(x, pk, sc, bias, n, k, 16, out_dtype=torch.float32)
+    P.ops.gemm_status(dev)
+    ref = x.float() @ wd.t() + bias.float()
+    budget = x.float().abs() @ wd.abs().t() + bias.float().abs()
+    assert float(((y - ref).abs() / budget).max()) < 2e-5
+    gy = torch.from_numpy(oracle.gen_normal(993 + m, m * n, 1.0).reshape(m, n).copy()).to(dt).to(dev)
+    dx = P.ops.linear_dx(gy, pk, sc, n, k, 16, out_dtype=torch.float32)
+    P.ops.gemm_status(dev)
+    assert float(((dx - gy.float() @ wd).abs() / (gy.float().abs() @ wd.abs()).clamp_min(1e-30)).max()) < 2e-5
+    # a layer built with the reference's defaults except the bit-rate
+    if m == 5:
+        lin = torch.nn.Linear(k, 64, bias=True).to(dev).to(dt)
+        layer = P.E8LatticeLinear.from_linear(lin, rank=0, bitrate=1.5)
+        assert layer.group_size == 16
+        out = layer(x)
+        refl = x.float() @ layer.unpack_weights(torch.float32).t() + layer.bias.float()
+        assert float((out.float() - refl).abs().max()) <= 2.0 ** -7 * float(refl.abs().max()) + 1e-3
