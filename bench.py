@@ -716,6 +716,8 @@ def run_case(args):
             for pk, sc in mats:
                 lin(x, pk, sc, None, n, k, 32)
         info["bytes_per_launch"] = args.rotation * n * k * ((0.25 if args.case == "linear_2bit" else 0.125) + 2.0 / 32)
+        if m > 8:                                               # batches of tokens run the tcgen05 kernel with this format's decoder
+            info["flops_per_launch"] = args.rotation * 2.0 * m * n * k
     elif args.case == "project":                                # nearest E8 point of N*K/8 fp32 8-vectors: 4 B in + 4 B out per value
         v = ops.generate(n * k, 60, 1.0, torch.float32, dev).view(-1, 8)
         fn = lambda: ops.e8_project(v)
