@@ -567,7 +567,8 @@ def test_one_bit_golden_ties_and_layer(P, golden, oracle):
 @pytest.mark.parametrize("bits", [2, 1])
 @pytest.mark.parametrize("m,k,n,group,dt", [(1, 4096, 4096, 32, torch.bfloat16), (3, 256, 40, 8, torch.float16),
                                              (8, 4096, 96, 64, torch.bfloat16), (1, 14336, 64, 32, torch.float32),
-                                             (2, 1024, 33, 16, torch.bfloat16), (9, 512, 24, 32, torch.bfloat16), (9, 512, 24, 32, torch.float32), (12, 320, 24, 32, torch.bfloat16)])
+                                             (2, 1024, 33, 16, torch.bfloat16), (9, 512, 24, 32, torch.bfloat16), (9, 512, 24, 32, torch.float32), (12, 320, 24, 32, torch.bfloat16),
+                                             (5, 512, 40, 8, torch.bfloat16), (3, 512, 40, 8, torch.bfloat16), (6, 768, 16, 32, torch.float16)])
 def test_low_bit_decode_linear_matches_dense_product(P, oracle, bits, m, k, n, group, dt):
     """ojx_e8t_linear_2bit / _1bit at decode shapes (the tensor-core or the shared-memory kernel for up to eight rows;
     beyond, the prefill kernel or the scalar kernel) against the fp32 product with the decoded weights: fp32
@@ -579,7 +580,7 @@ def test_low_bit_decode_linear_matches_dense_product(P, oracle, bits, m, k, n, g
     pk, sc = enc(w, group)
     # more than eight rows of 16-bit activations with groups of 32 and K % 256 == 0 run the prefill kernel, whose
     # operand is the weight rounded to fp16
-    prefill = m > 8 and group in (8, 16, 32) and k % 256 == 0 and dt != torch.float32
+    prefill = (m > 8 or (m >= 4 and not (group == 32 and k % 2048 == 0))) and group in (8, 16, 32) and k % 256 == 0 and dt != torch.float32
     wd = dec(pk, sc, (n, k), torch.float16).float() if prefill else dec(pk, sc, (n, k), torch.float32)
     x = torch.from_numpy(oracle.gen_normal(901 + m, m * k, 1.0).reshape(m, k).copy()).to(dt).to(dev)
     bias = torch.from_numpy(oracle.gen_normal(902, n, 0.1).copy()).to(dt).to(dev)
