@@ -186,6 +186,9 @@ int32_t ojx_e8t_decode(const uint8_t* packed, const uint16_t* scales, int64_t ro
  * Decode-shape linear (small M): y[M, N] = x[M, K] . W^T (+ bias), W given packed.
  * Replaces _FusedE8GEMMFunction.forward for small batches (ojasx2/math/lattice.py:551-640) and the
  * reference's native fused kernel (ojasx_math_core.hpp:580-634).  fp32 accumulation.
+ * Shapes outside the tensor-core path: up to eight rows with K % 64 == 0, a power-of-two group from 16 and 16-byte
+ * aligned x (any of the three dtypes) run a shared-memory fp32 kernel with exact products; everything else a scalar
+ * fp32 kernel.
  * Numerics of the tensor-core path (M <= 16, K % 256 == 0, group 32, bf16 or fp16 x): the weights enter the
  * MMAs as exact fp16 values coord * scale; fp16 activations are used as they are; bf16 activations are
  * multiplied by a power of two per (row, 256-wide slice of K) so that the slice maximum lies in [2^14, 2^15)

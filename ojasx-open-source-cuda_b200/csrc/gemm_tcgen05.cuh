@@ -461,7 +461,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
 #pragma unroll
                         for (int i = 0; i < kSW; ++i) sw[i] = __ldg(reinterpret_cast<const uint32_t*>(sbase + (int64_t)row * row_scales) + i);
                     } else if (kFmt == 0) {                                      // beyond the matrix: rank of the zero vector, scale 0
-                        cw[0] = 0x68668668u; cw[1] = 0x86686686u; cw[2] = 0x66866866u; sw[0] = 0u;   // rank 1640 eight times
+                        cw[0] = 0x68668668u; cw[1] = 0x86686686u; cw[2] = 0x66866866u;               // rank 1640 eight times
+#pragma unroll
+                        for (int i = 0; i < kSW; ++i) sw[i] = 0u;
                     } else {                                                     // any code, scale 0
                         cw[0] = cw[1] = cw[2] = cw[3] = 0u;
 #pragma unroll

@@ -188,6 +188,30 @@ int32_t gemv_impl(const void* x, int x_dtype, int64_t M, const uint8_t* packed, 
         return launch_status();
     }
     OJX_RETURN_IF(lora_rank > 0, OJX_ERR_UNSUPPORTED);          // the low-rank epilogue exists in the tensor-core kernels only
+    // up to eight rows, any power-of-two group from 16 and any activation dtype: the shared-memory fp32 kernel
+    {
+        int shift = -1;
+        for (int b = 4; b < 20; ++b)
+            if ((1 << b) == group) shift = b;
+        const size_t smem = ternary_small_smem_bytes(M, K);
+        if (shift > 0 && M <= 8 && K % 64 == 0 && K <= (1 << 24) && N < (1 << 30) && smem <= 200 * 1024 &&
+            (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            const int per_sm = (int)((220 * 1024) / (smem + 1024)) < 1 ? 1 : (int)((220 * 1024) / (smem + 1024));
+            int64_t blocks = (N + 31) / 32;                       // at least four weight rows per warp: every CTA stages x once
+            const int64_t cap = (int64_t)num_sms() * (per_sm > 8 ? 8 : per_sm);
+            if (blocks > cap) blocks = cap;
+            auto run = [&](auto kernel, std::atomic<uint64_t>& done) -> int32_t {
+                const int32_t sc = ensure_dynamic_smem(kernel, 200 * 1024, done);
+                OJX_RETURN_IF(sc != OJX_OK, sc);
+                kernel<<<(unsigned)blocks, 256, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, shift, y, y_dtype);
+                return launch_status();
+            };
+            static std::atomic<uint64_t> done1{0}, done4{0}, done8{0};
+            if (M == 1) return run(ternary_small_gemv_kernel<1>, done1);
+            if (M <= 4) return run(ternary_small_gemv_kernel<4>, done4);
+            return run(ternary_small_gemv_kernel<8>, done8);
+        }
+    }
     // generic path
     int64_t warps_needed = N;
     int64_t blocks = (warps_needed * 32 + 255) / 256;

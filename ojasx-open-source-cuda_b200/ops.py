@@ -395,8 +395,9 @@ def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: 
     """y[M, N] = x[M, K] . dequant(W)^T (+ bias), output in x's dtype unless ``out_dtype`` is given.
 
     Routing: M <= 16 -> decode-shape kernel (``ojx_e8t_gemv``); larger M with K % 256 == 0, 16-bit
-    activations and groups of 32 or 16 -> tcgen05 kernel (``ojx_e8t_gemm``; groups of 16 take it at every M);
-    everything else -> the generic kernel inside ``ojx_e8t_gemv``.  ``force`` ("gemv" or "gemm") overrides the routing for tests.
+    activations and groups of 32 or 16 -> tcgen05 kernel (``ojx_e8t_gemm``; groups of 16 take it from three rows on);
+    everything else -> inside ``ojx_e8t_gemv`` the shared-memory fp32 kernel (up to eight rows, K % 64 == 0, groups
+    of 16, 32, 64, ...; any activation dtype) or the scalar kernel.  ``force`` ("gemv" or "gemm") overrides the routing for tests.
     """
     n, k = int(out_features), int(in_features)
     dev, x2d, pk, sc, b = _prep_linear(x2d, packed, scales, bias, n, k)
@@ -408,9 +409,10 @@ def linear(x2d: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: 
         return y
     g = effective_group(group_size)
     lib = _cabi.lib()
-    # groups of 16 (what the reference layer's default group size of 8 becomes for this format) have no decode-shape
-    # kernel of their own: they take the tensor-core kernel at every batch size rather than the scalar kernel
-    use_gemm = ((m > GEMV_MAX_M or g == 16) and k % 256 == 0 and g in (16, 32) and x2d.dtype in (torch.bfloat16, torch.float16)
+    # groups of 16 (what the reference layer's default group size of 8 becomes for this format) have no tensor-core
+    # decode kernel: one or two rows run the shared-memory fp32 kernel inside ojx_e8t_gemv, more rows the prefill kernel
+    # (measured on 14336 x 4096 with the wrapper: 35 against 54 us at one row, 82 against 54 us at four)
+    use_gemm = ((m > GEMV_MAX_M or (g == 16 and m > 2)) and k % 256 == 0 and g in (16, 32) and x2d.dtype in (torch.bfloat16, torch.float16)
                 and (k * 3 // 16) * n == pk.numel())
     if force == "gemm":
         use_gemm = True

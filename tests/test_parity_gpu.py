@@ -716,11 +716,13 @@ def test_low_bit_backward_dx_matches_dense_product(P, oracle, bits, m, k, n, dt,
 
 
 @pytest.mark.parametrize("m,k,n,dt", [(1, 512, 40, torch.bfloat16), (5, 4096, 1000, torch.float16), (300, 1024, 520, torch.bfloat16),
-                                      (2048, 4096, 4096, torch.bfloat16)])
+                                      (2048, 4096, 4096, torch.bfloat16), (2, 14336, 40, torch.bfloat16), (12, 1024, 72, torch.float16),
+                                      (8, 2048, 24, torch.bfloat16)])
 def test_ternary_groups_of_16_run_the_tensor_core_kernels(P, oracle, m, k, n, dt):
     """Ternary codes with one scale per 16 weights (what the reference layer's default group size of 8 becomes for this
-    format, ojasx2/math/lattice.py:750-751): forward (at every batch size) and backward through the tcgen05 kernels against
-    the fp32 products with the decoded weights, which are exact in fp16 - within 2e-5 of sum |x||w| per output."""
+    format, ojasx2/math/lattice.py:750-751): forward (the shared-memory fp32 kernel for one or two rows, the tcgen05 kernel
+    beyond) and backward (tcgen05) against the fp32 products with the decoded weights, which are exact in fp16 -
+    within 2e-5 of sum |x||w| per output."""
     dev = torch.device(DEV)
     w = torch.from_numpy(oracle.gen_normal(990 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
     pk, sc = P.ops.encode(w, 16)
@@ -745,3 +747,21 @@ def test_ternary_groups_of_16_run_the_tensor_core_kernels(P, oracle, m, k, n, dt
         out = layer(x)
         refl = x.float() @ layer.unpack_weights(torch.float32).t() + layer.bias.float()
         assert float((out.float() - refl).abs().max()) <= 2.0 ** -7 * float(refl.abs().max()) + 1e-3
+
+
+@pytest.mark.parametrize("m,k,n,group", [(1, 4096, 4096, 32), (4, 1024, 40, 32), (8, 2048, 17, 64), (2, 320, 24, 32)])
+def test_ternary_fp32_activations_at_decode_shapes(P, oracle, m, k, n, group):
+    """fp32 activations (the dtype of the reference's CPU tests) at decode shapes run the shared-memory fp32 kernel
+    (K % 64 == 0, power-of-two groups from 16) or the scalar one: exact products, fp32 accumulation - within 1e-5 of
+    sum |x||w| per output."""
+    dev = torch.device(DEV)
+    w = torch.from_numpy(oracle.gen_normal(995 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
+    pk, sc = P.ops.encode(w, group)
+    wd = P.ops.decode(pk, sc, (n, k), torch.float32)
+    x = torch.from_numpy(oracle.gen_normal(996 + m, m * k, 1.0).reshape(m, k).copy()).to(dev)
+    x[0, 3::97] *= 1.0e3
+    bias = torch.from_numpy(oracle.gen_normal(997, n, 0.1).copy()).to(dev)
+    y = P.ops.linear(x, pk, sc, bias, n, k, group)
+    ref = x @ wd.t() + bias
+    budget = x.abs() @ wd.abs().t() + bias.abs()
+    assert y.dtype == torch.float32 and float(((y - ref).abs() / budget).max()) < 1e-5
