@@ -218,7 +218,7 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
         for (int slot = 0; slot < kB1Ahead; ++slot) {
             const int64_t it = it0 + slot;
             if (it >= total) break;
-            // this round has landed when at most kB1Ahead - 1 newer groups are pending; the copies were made by other lanes
+            // the slot is complete when at most kB1Ahead - 1 newer groups are pending; the copies were made by other lanes
             asm volatile("cp.async.wait_group %0;" ::"n"(kB1Ahead - 1) : "memory");
             __syncwarp();
             const uint8_t* rs = rings + (cta_warp * kB1Ahead + slot) * kB1RoundBytes;

@@ -258,8 +258,8 @@ def test_activation_outliers_nan_and_inf(P, oracle):
             # per-output bound relative to sum |x_k| |w_k| of that output (what fp32 accumulation of exact
             # products can be held to), not to the outlier
             ref = xo.float() @ wd.t()
-            budget = xo.float().abs() @ wd.abs().t()
-            assert float(((y - ref).abs() / budget).max()) < 1e-5, (m, mag)
+            magnitude = xo.float().abs() @ wd.abs().t()
+            assert float(((y - ref).abs() / magnitude).max()) < 1e-5, (m, mag)
         xn = x.clone()
         xn[0, 100] = float("nan")
         y = P.ops.linear(xn, pk, sc, None, n, k, 32, out_dtype=torch.float32)
@@ -384,8 +384,8 @@ def test_adapter_term_in_the_decode_epilogue(P, m, k, n, dt):
     b = (torch.randn(r, n, device=dev) * 0.5).to(dt)
     y = P.ops.linear_lora(x, pk, sc, bias, n, k, 32, t, b, out_dtype=torch.float32)
     ref = x.float() @ wd.t() + bias.float() + t @ b.float()
-    budget = x.float().abs() @ wd.abs().t() + bias.float().abs() + t.abs() @ b.float().abs()
-    assert float(((y - ref).abs() / budget).max()) < 1e-5
+    magnitude = x.float().abs() @ wd.abs().t() + bias.float().abs() + t.abs() @ b.float().abs()
+    assert float(((y - ref).abs() / magnitude).max()) < 1e-5
     plain = P.ops.linear(x, pk, sc, bias, n, k, 32, out_dtype=torch.float32)
     assert torch.equal(P.ops.linear_lora(x, pk, sc, bias, n, k, 32, torch.zeros_like(t), b, out_dtype=torch.float32), plain)
     y16 = P.ops.linear_lora(x, pk, sc, None, n, k, 32, t, b)

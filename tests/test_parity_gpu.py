@@ -586,8 +586,8 @@ def test_low_bit_decode_linear_matches_dense_product(P, oracle, bits, m, k, n, g
     bias = torch.from_numpy(oracle.gen_normal(902, n, 0.1).copy()).to(dt).to(dev)
     y = lin(x, pk, sc, bias, n, k, group, out_dtype=torch.float32)
     ref = x.float() @ wd.t() + bias.float()
-    budget = x.float().abs() @ wd.abs().t() + bias.float().abs()
-    assert float(((y - ref).abs() / budget).max()) < 1e-5
+    magnitude = x.float().abs() @ wd.abs().t() + bias.float().abs()
+    assert float(((y - ref).abs() / magnitude).max()) < 1e-5
     y16 = lin(x, pk, sc, None, n, k, group)
     assert y16.dtype == dt and float((y16.float() - (ref - bias.float())).abs().max()) <= 2.0 ** -7 * float(ref.abs().max()) + 1e-3
 
@@ -615,8 +615,8 @@ def test_low_bit_tensor_core_kernels(P, oracle, bits, m, k, n, dt):
     bias = torch.from_numpy(oracle.gen_normal(952, n, 0.1).copy()).to(dt).to(dev)
     y = lin(x, pk, sc, bias, n, k, 32, out_dtype=torch.float32)
     ref = x.float() @ wd.t() + bias.float()
-    budget = x.float().abs() @ wd.abs().t() + bias.float().abs()
-    assert float(((y - ref).abs() / budget).max()) < 1e-5
+    magnitude = x.float().abs() @ wd.abs().t() + bias.float().abs()
+    assert float(((y - ref).abs() / magnitude).max()) < 1e-5
     y0 = lin(x, pk, sc, None, n, k, 32, out_dtype=torch.float32)
     for s in (-30, 20):
         if dt == torch.float16:
@@ -632,7 +632,7 @@ def test_low_bit_tensor_core_kernels(P, oracle, bits, m, k, n, dt):
     assert torch.equal(torch.isneginf(yi), torch.isneginf(ri))
     fin = torch.isfinite(ri)
     if bool(fin.any()):
-        assert float((((yi - ri).abs() / (budget - bias.float().abs()))[fin]).max()) < 1e-5
+        assert float((((yi - ri).abs() / (magnitude - bias.float().abs()))[fin]).max()) < 1e-5
     xn = x.clone()
     xn[m // 2, 100] = float("nan")
     yn = lin(xn, pk, sc, None, n, k, 32, out_dtype=torch.float32)
@@ -661,8 +661,8 @@ def test_low_bit_prefill_gemm_matches_dense_product(P, oracle, bits, m, k, n, dt
     y = lin(x, pk, sc, bias, n, k, group, out_dtype=torch.float32)
     P.ops.gemm_status(dev)
     ref = x.float() @ wd.t() + (bias.float() if with_bias else 0.0)
-    budget = x.float().abs() @ wd.abs().t() + (bias.float().abs() if with_bias else 0.0)
-    assert float(((y - ref).abs() / budget.clamp_min(1e-30)).max()) < 2e-5
+    magnitude = x.float().abs() @ wd.abs().t() + (bias.float().abs() if with_bias else 0.0)
+    assert float(((y - ref).abs() / magnitude.clamp_min(1e-30)).max()) < 2e-5
     y16 = lin(x, pk, sc, bias, n, k, group)
     assert y16.dtype == dt and float((y16.float() - ref).abs().max()) <= 2.0 ** -7 * float(ref.abs().max()) + 1e-3
     if bits == 2:                                                        # the fp16 rounding of (code - 1.5) * scale is within the tolerance of the path
@@ -708,8 +708,8 @@ def test_low_bit_backward_dx_matches_dense_product(P, oracle, bits, m, k, n, dt,
     dx = P.ops.linear_dx_lowbit(bits, gy, pk, sc, n, k, group, out_dtype=torch.float32)
     P.ops.gemm_status(dev)
     ref = gy.float() @ wd
-    budget = gy.float().abs() @ wd.abs()
-    assert float(((dx - ref).abs() / budget.clamp_min(1e-30)).max()) < 2e-5
+    magnitude = gy.float().abs() @ wd.abs()
+    assert float(((dx - ref).abs() / magnitude.clamp_min(1e-30)).max()) < 2e-5
     # fp32 gradients take the decode-and-multiply route
     dx32 = P.ops.linear_dx_lowbit(bits, gy.float(), pk, sc, n, k, group)
     assert dx32.dtype == torch.float32 and float((dx32 - gy.float() @ dec(pk, sc, (n, k), torch.float32)).abs().max()) <= 1e-3 * float(ref.abs().max())
@@ -733,8 +733,8 @@ def test_ternary_groups_of_16_run_the_tensor_core_kernels(P, oracle, m, k, n, dt
     y = P.ops.linear(x, pk, sc, bias, n, k, 16, out_dtype=torch.float32)
     P.ops.gemm_status(dev)
     ref = x.float() @ wd.t() + bias.float()
-    budget = x.float().abs() @ wd.abs().t() + bias.float().abs()
-    assert float(((y - ref).abs() / budget).max()) < 2e-5
+    magnitude = x.float().abs() @ wd.abs().t() + bias.float().abs()
+    assert float(((y - ref).abs() / magnitude).max()) < 2e-5
     gy = torch.from_numpy(oracle.gen_normal(993 + m, m * n, 1.0).reshape(m, n).copy()).to(dt).to(dev)
     dx = P.ops.linear_dx(gy, pk, sc, n, k, 16, out_dtype=torch.float32)
     P.ops.gemm_status(dev)
@@ -763,5 +763,5 @@ def test_ternary_fp32_activations_at_decode_shapes(P, oracle, m, k, n, group):
     bias = torch.from_numpy(oracle.gen_normal(997, n, 0.1).copy()).to(dev)
     y = P.ops.linear(x, pk, sc, bias, n, k, group)
     ref = x @ wd.t() + bias
-    budget = x.abs() @ wd.abs().t() + bias.abs()
-    assert y.dtype == torch.float32 and float(((y - ref).abs() / budget).max()) < 1e-5
+    magnitude = x.abs() @ wd.abs().t() + bias.abs()
+    assert y.dtype == torch.float32 and float(((y - ref).abs() / magnitude).max()) < 1e-5
