@@ -157,6 +157,19 @@ int32_t ojx_e8t_linear_1bit(const void* x, int32_t x_dtype, int64_t M, const uin
                             const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype, void* stream);
 
 /*
+ * Decode-shape linear of the 2.0-bit (`bits` 2) or 1.0-bit (`bits` 1) format with the adapter term in the epilogue:
+ * y = x . W^T (+ bias) + lora_t . lora_b, lora_t fp32 [M, lora_rank] = scaling * (x . A) prepared by the caller,
+ * lora_b [lora_rank, N] in x's dtype, accumulated in fp32 before the single rounding (the reference adds the term with
+ * three more tensor operations, ojasx2/math/lattice.py:839-842).  Only the shapes of the int8 tensor-core kernels are
+ * served (1 <= M <= 8, group 32, K % 2048 == 0, 16-byte aligned operands, 1 <= lora_rank <= 64); anything else returns
+ * OJX_ERR_UNSUPPORTED and the caller adds the term itself.
+ */
+int32_t ojx_e8t_linear_lowbit_lora(int32_t bits, const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed,
+                                   const uint16_t* scales, const void* bias, int64_t N, int64_t K, int32_t group,
+                                   const float* lora_t, const void* lora_b, int32_t lora_rank,
+                                   void* y, int32_t y_dtype, void* stream);
+
+/*
  * Nearest point of the E8 lattice (integer vectors with an even sum, or all of them shifted by 1/2) for
  * each of `vectors` consecutive 8-vectors.  Replaces conway_sloane_e8_project (ojasx2/math/lattice.py:162-203;
  * native form ojasx_math_core.hpp:385-425) bit for bit on fp32 input: round-half-even, first index wins the

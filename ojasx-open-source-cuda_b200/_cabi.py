@@ -26,7 +26,7 @@ OJX_ENCODE_HADAMARD = 1
 PEER_SYNC_BYTES = 48        # sizeof(ojx_e8t_peer_sync): epoch, arrived, status, spin_limit, flag[8]
 
 EXPORTED_SYMBOLS = (
-    "ojx_e8t_version", "ojx_e8t_status_string", "ojx_e8t_encode", "ojx_e8t_encode_ex", "ojx_e8t_fwht32", "ojx_e8t_encode_2bit", "ojx_e8t_decode_2bit", "ojx_e8t_linear_2bit", "ojx_e8t_encode_1bit", "ojx_e8t_decode_1bit", "ojx_e8t_linear_1bit", "ojx_e8t_project", "ojx_e8t_ste_quantize", "ojx_e8t_decode",
+    "ojx_e8t_version", "ojx_e8t_status_string", "ojx_e8t_encode", "ojx_e8t_encode_ex", "ojx_e8t_fwht32", "ojx_e8t_encode_2bit", "ojx_e8t_decode_2bit", "ojx_e8t_linear_2bit", "ojx_e8t_encode_1bit", "ojx_e8t_decode_1bit", "ojx_e8t_linear_1bit", "ojx_e8t_linear_lowbit_lora", "ojx_e8t_project", "ojx_e8t_ste_quantize", "ojx_e8t_decode",
     "ojx_e8t_gemv_workspace_bytes", "ojx_e8t_gemv", "ojx_e8t_gemv_lora", "ojx_e8t_gemv_tiles", "ojx_e8t_gemv_kchunks",
     "ojx_e8t_gemv_grouped", "ojx_e8t_gemv_grouped_peers", "ojx_e8t_gemv_grouped_ex", "ojx_e8t_peer_wait", "ojx_e8t_enable_peer_access", "ojx_e8t_gemm_workspace_bytes", "ojx_e8t_gemm", "ojx_e8t_gemm_lowbit", "ojx_e8t_gemm_status", "ojx_e8t_gemm_dx", "ojx_e8t_gemm_dx_lowbit", "ojx_e8t_gemm_dx_workspace_bytes",
     "ojx_e8t_generate", "ojx_e8t_last_cuda_error", "ojx_e8t_device_status", "ojx_e8t_poll_status", "ojx_e8t_set_wait_limit",
@@ -102,6 +102,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ojx_e8t_encode_2bit.argtypes = [vp, i32, i64, i64, i32, vp, vp, vp]
     lib.ojx_e8t_decode_2bit.restype = i32
     lib.ojx_e8t_decode_2bit.argtypes = [vp, vp, i64, i64, i32, i32, vp, vp]
+    lib.ojx_e8t_linear_lowbit_lora.restype = i32
+    lib.ojx_e8t_linear_lowbit_lora.argtypes = [i32, vp, i32, i64, vp, vp, vp, i64, i64, i32, vp, vp, i32, vp, i32, vp]
     lib.ojx_e8t_linear_2bit.restype = i32
     lib.ojx_e8t_linear_2bit.argtypes = [vp, i32, i64, vp, vp, vp, i64, i64, i32, vp, i32, vp]
     lib.ojx_e8t_encode_1bit.restype = i32

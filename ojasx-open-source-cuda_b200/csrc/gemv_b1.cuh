@@ -55,7 +55,8 @@ __device__ __forceinline__ void mma_s8_from_zero(int (&d)[4], uint32_t a0, uint3
 template <int kCB, int kB1Copies, int kB1Groups>  // column blocks (pairs of activation rows); copies of the code table (16 or 8); tile groups of 8 warps
 __global__ void __launch_bounds__(kB1Groups * kB1Warps * 32, 1)
 gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
-               const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype) {
+               const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype,
+               const float* __restrict__ lora_t, const void* __restrict__ lora_b, int lora_rank) {
     extern __shared__ __align__(16) uint8_t b1_smem[];
     const int rounds = K / 256;
     uint2* frag = reinterpret_cast<uint2*>(b1_smem);                                   // [cb][round][group pair][col 0..7][quarter 0..3][group & 1]
@@ -199,6 +200,7 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
                 for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
                 if (lane == 0) {
                     if (bias != nullptr) acc += load_any(bias, x_dtype, n);
+                    if (lora_rank > 0) acc += lowbit_lora_term(lora_t, lora_b, lora_rank, x_dtype, m, n, N);
                     store_any(y, y_dtype, (int64_t)m * N + n, acc);
                 }
             }
@@ -287,6 +289,7 @@ gemv_b1_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
 #pragma unroll
                             for (int w = 0; w < kB1Warps; ++w) sum += b[(size_t)w * 2 * kCB * 16];   // the host only launches with rounds % 8 == 0
                             if (bias != nullptr) sum += load_any(bias, x_dtype, n);
+                            if (lora_rank > 0) sum += lowbit_lora_term(lora_t, lora_b, lora_rank, x_dtype, m, n, N);
                             store_any(y, y_dtype, (int64_t)m * N + n, sum);
                         }
                     }

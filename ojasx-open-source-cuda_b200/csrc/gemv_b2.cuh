@@ -42,15 +42,24 @@ __host__ __device__ inline size_t b2_smem_bytes(int M, int groups, int K) {
     return (size_t)M * rounds * (8 * 32 * 4 + 8 * 4 * 4) + (size_t)groups * M * kB2Warps * 16 * 4 * 2;   // operands, group factors, partial sums
 }
 
+// The optional adapter term of output (activation row m, weight row n): sum_r t[m, r] * B[r, n] in fp32, t = scaling * x . A
+// prepared by the caller, B in the activations' dtype.  Out of line: rare, and the epilogue has no registers to spare.
+__device__ __noinline__ float lowbit_lora_term(const float* t, const void* b, int rank, int dtype, int m, int n, int N) {
+    float acc = 0.f;
+    for (int r = 0; r < rank; ++r) acc = fmaf(t[m * rank + r], load_any(b, dtype, (int64_t)r * N + n), acc);
+    return acc;
+}
+
 struct B2Loads {
     uint4 ca, cb;                                 // 64 codes of rows g and g + 8
     uint32_t sa, sb;                              // their two fp16 scales each
 };
 
-template <int kM, int kB2Groups>                  // rows of x handled by the unrolled loops; tile groups of 8 warps
+template <int kM, int kB2Groups, bool kLora = false>   // rows of x handled by the unrolled loops; tile groups of 8 warps; adapter term in the epilogue
 __global__ void __launch_bounds__(kB2Groups * kB2Warps * 32, 1)
 gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
-               const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype) {
+               const void* __restrict__ bias, int N, int K, void* __restrict__ y, int y_dtype,
+               const float* __restrict__ lora_t, const void* __restrict__ lora_b, int lora_rank) {
     extern __shared__ __align__(16) uint8_t b2_smem[];
     const int rounds = K / 256;
     uint32_t* frag = reinterpret_cast<uint32_t*>(b2_smem);                             // [m][round][digit][word group 0..15][4 words]
@@ -192,6 +201,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
                 for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
                 if (lane == 0) {
                     if (bias != nullptr) acc += load_any(bias, x_dtype, n);
+                    if (kLora && lora_rank > 0) acc += lowbit_lora_term(lora_t, lora_b, lora_rank, x_dtype, m, n, N);
                     store_any(y, y_dtype, (int64_t)m * N + n, acc);
                 }
             }
@@ -280,6 +290,7 @@ gemv_b2_kernel(const void* __restrict__ x, int x_dtype, int M, const uint8_t* __
 #pragma unroll
                             for (int w = 0; w < kB2Warps; ++w) sum += b[(size_t)w * M * 16];   // the host only launches with rounds % 8 == 0
                             if (bias != nullptr) sum += load_any(bias, x_dtype, n);
+                            if (kLora && lora_rank > 0) sum += lowbit_lora_term(lora_t, lora_b, lora_rank, x_dtype, m, n, N);
                             store_any(y, y_dtype, (int64_t)m * N + n, sum);
                         }
                     }

@@ -254,8 +254,10 @@ static bool launch_lowbit_gemv(const void* x, int x_dtype, int64_t M, const uint
 // y = x . W^T (+ bias) for the 2.0-bit (bits == 2) and 1.0-bit (bits == 1) formats: the fused fp32 kernel (one warp per
 // output feature), any shape.
 int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
-                           const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s) {
+                           const void* bias, int64_t N, int64_t K, int group, void* y, int y_dtype, cudaStream_t s,
+                           const float* lora_t, const void* lora_b, int lora_rank) {
     OJX_RETURN_IF(!x || !packed || !scales || !y, OJX_ERR_NULL);
+    OJX_RETURN_IF(lora_rank < 0 || lora_rank > 64 || (lora_rank > 0 && (!lora_t || !lora_b)), OJX_ERR_SHAPE);
     OJX_RETURN_IF(M <= 0 || N <= 0 || K <= 0 || group <= 0 || group % 8 != 0, OJX_ERR_SHAPE);
     OJX_RETURN_IF(dtype_size(x_dtype) == 0 || dtype_size(y_dtype) == 0, OJX_ERR_DTYPE);
     OJX_RETURN_IF(check_arch() != OJX_OK, OJX_ERR_ARCH);
@@ -273,10 +275,17 @@ int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, cons
         auto run = [&](auto kernel, std::atomic<uint64_t>& done) -> int32_t {
             const int32_t sc = ensure_dynamic_smem(kernel, 227 * 1024, done);
             OJX_RETURN_IF(sc != OJX_OK, sc);
-            kernel<<<grid, groups * kB2Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
+            kernel<<<grid, groups * kB2Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype,
+                                                              lora_t, lora_b, lora_rank);
             return launch_status();
         };
-        static std::atomic<uint64_t> d1{0}, d2{0}, d4{0}, d8{0};
+        static std::atomic<uint64_t> d1{0}, d2{0}, d4{0}, d8{0}, l1{0}, l2{0}, l4{0}, l8{0};
+        if (lora_rank > 0) {                                  // the variants that carry the adapter term are kept apart
+            if (M == 1) return run(gemv_b2_kernel<1, 2, true>, l1);
+            if (M == 2) return run(gemv_b2_kernel<2, 2, true>, l2);
+            if (M <= 4) return run(gemv_b2_kernel<4, 2, true>, l4);
+            return run(gemv_b2_kernel<8, 2, true>, l8);
+        }
         if (M == 1) return run(gemv_b2_kernel<1, 2>, d1);
         if (M == 2) return run(gemv_b2_kernel<2, 2>, d2);
         if (M <= 4) return run(gemv_b2_kernel<4, 2>, d4);
@@ -295,7 +304,8 @@ int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, cons
         auto run = [&](auto kernel, std::atomic<uint64_t>& done) -> int32_t {
             const int32_t sc = ensure_dynamic_smem(kernel, 227 * 1024, done);
             OJX_RETURN_IF(sc != OJX_OK, sc);
-            kernel<<<grid, groups * kB1Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype);
+            kernel<<<grid, groups * kB1Warps * 32, smem, s>>>(x, x_dtype, (int)M, packed, scales, bias, (int)N, (int)K, y, y_dtype,
+                                                              lora_t, lora_b, lora_rank);
             return launch_status();
         };
         static std::atomic<uint64_t> d1{0}, d2{0}, d4{0}, d1n{0}, d2n{0}, d4n{0};
@@ -303,6 +313,7 @@ int32_t linear_lowbit_impl(int bits, const void* x, int x_dtype, int64_t M, cons
         if (cbs == 2) return narrow ? run(gemv_b1_kernel<2, 8, 2>, d2n) : run(gemv_b1_kernel<2, 16, 2>, d2);
         return narrow ? run(gemv_b1_kernel<4, 8, 2>, d4n) : run(gemv_b1_kernel<4, 16, 2>, d4);
     }
+    OJX_RETURN_IF(lora_rank > 0, OJX_ERR_UNSUPPORTED);          // the adapter epilogue exists in the tensor-core kernels only
     int32_t st = OJX_OK;                                      // small batches: the shared-memory kernel when x fits
     if (bits == 2 ? launch_lowbit_gemv<2>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, s, &st)
                   : launch_lowbit_gemv<1>(x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, s, &st))

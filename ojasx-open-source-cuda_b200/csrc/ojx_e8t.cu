@@ -123,7 +123,7 @@ int32_t ojx_e8t_decode_2bit(const uint8_t* packed, const uint16_t* scales, int64
 
 int32_t ojx_e8t_linear_2bit(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                             const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype, void* stream) {
-    return ojx::linear_lowbit_impl(2, x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream);
+    return ojx::linear_lowbit_impl(2, x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream, nullptr, nullptr, 0);
 }
 
 int32_t ojx_e8t_encode_1bit(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t group,
@@ -138,7 +138,17 @@ int32_t ojx_e8t_decode_1bit(const uint8_t* packed, const uint16_t* scales, int64
 
 int32_t ojx_e8t_linear_1bit(const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed, const uint16_t* scales,
                             const void* bias, int64_t N, int64_t K, int32_t group, void* y, int32_t y_dtype, void* stream) {
-    return ojx::linear_lowbit_impl(1, x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream);
+    return ojx::linear_lowbit_impl(1, x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream, nullptr, nullptr, 0);
+}
+
+int32_t ojx_e8t_linear_lowbit_lora(int32_t bits, const void* x, int32_t x_dtype, int64_t M, const uint8_t* packed,
+                                   const uint16_t* scales, const void* bias, int64_t N, int64_t K, int32_t group,
+                                   const float* lora_t, const void* lora_b, int32_t lora_rank,
+                                   void* y, int32_t y_dtype, void* stream) {
+    if (bits != 1 && bits != 2) return OJX_ERR_UNSUPPORTED;
+    if (lora_rank <= 0) return OJX_ERR_SHAPE;
+    return ojx::linear_lowbit_impl(bits, x, x_dtype, M, packed, scales, bias, N, K, group, y, y_dtype, (cudaStream_t)stream,
+                                   lora_t, lora_b, lora_rank);
 }
 
 int32_t ojx_e8t_project(const float* x, int64_t vectors, float* out, void* stream) {

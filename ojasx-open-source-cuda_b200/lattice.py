@@ -350,12 +350,20 @@ class E8LatticeLinear(nn.Module):
     def _forward_decode_with_adapter(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """Inference at decode shapes with an adapter: the low-rank term rides in the GEMV's epilogue (one launch for
         the packed product, the adapter's second factor, the scaling and the addition); ``None`` when it does not apply."""
-        if self.rank <= 0 or self.lora_A is None or self.bitrate != 1.5 or not x.is_cuda or torch.compiler.is_compiling():
+        if self.rank <= 0 or self.lora_A is None or not x.is_cuda or torch.compiler.is_compiling():
             return None
         if torch.is_grad_enabled() and (x.requires_grad or self.lora_A.requires_grad or self.lora_B.requires_grad
                                         or (self.bias is not None and self.bias.requires_grad)):
             return None
         x_2d = x.reshape(-1, self.in_features)
+        if self.bitrate != 1.5:                          # the sibling formats: their int8 tensor-core decode kernels
+            if not ops.lowbit_lora_fusable(int(x_2d.shape[0]), self.in_features, self.group_size, self.rank):
+                return None
+            t = (x_2d @ self.lora_A.to(x.dtype)).float() * self.scaling
+            x_rot = fwht_block32(x_2d) if (self.use_hadamard and self.in_features % 32 == 0) else x_2d
+            y = ops.linear_lowbit_lora(_lowbit(self.bitrate), x_rot, self.packed_weight, self.block_scales, self.bias,
+                                       self.out_features, self.in_features, self.group_size, t, self.lora_B)
+            return y.reshape(*x.shape[:-1], self.out_features)
         if not ops.lora_fusable(int(x_2d.shape[0]), self.in_features, self.group_size, x.dtype, self.rank):
             return None
         t = (x_2d @ self.lora_A.to(x.dtype)).float() * self.scaling

@@ -192,6 +192,36 @@ def _linear_lowbit(bits: int, x: torch.Tensor, packed: torch.Tensor, scales: tor
     return y
 
 
+def lowbit_lora_fusable(m: int, k: int, group_size: int, rank: int) -> bool:
+    """Shapes for which the adapter term can ride in the epilogue of the 2.0-bit / 1.0-bit decode kernels
+    (``ojx_e8t_linear_lowbit_lora``)."""
+    return 1 <= m <= 8 and int(group_size) == 32 and k % 2048 == 0 and m * k <= 32768 and 0 < rank <= 64
+
+
+def linear_lowbit_lora(bits: int, x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
+                       n: int, k: int, group_size: int, lora_t: torch.Tensor, lora_b: torch.Tensor,
+                       out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``y = x . W^T (+ bias) + lora_t . lora_b`` for the 2.0-bit (``bits`` 2) or 1.0-bit (``bits`` 1) format in ONE
+    decode-shape launch; ``lora_t`` [M, r] fp32 is ``scaling * (x . A)``, ``lora_b`` [r, N]."""
+    dev = _require_cuda(x, packed, scales)
+    x2 = x.detach().reshape(-1, k).contiguous()
+    m, r = int(x2.shape[0]), int(lora_b.shape[0])
+    if not lowbit_lora_fusable(m, k, group_size, r):
+        raise ValueError("this shape cannot take the fused adapter term; add it separately")
+    if tuple(lora_t.shape) != (m, r) or tuple(lora_b.shape) != (r, n):
+        raise ValueError("lora_t must be [M, r] and lora_b [r, N]")
+    t = lora_t.detach().to(torch.float32).contiguous()
+    bb = lora_b.detach().to(x2.dtype).contiguous()
+    b = None if bias is None else bias.detach().to(x2.dtype).contiguous()
+    y = torch.empty((m, n), dtype=out_dtype or x2.dtype, device=dev)
+    with torch.cuda.device(dev):
+        st = _cabi.lib().ojx_e8t_linear_lowbit_lora(bits, x2.data_ptr(), _dtype_code(x2.dtype), m, packed.data_ptr(), scales.data_ptr(),
+                                                    None if b is None else b.data_ptr(), n, k, 32, t.data_ptr(), bb.data_ptr(), r,
+                                                    y.data_ptr(), _dtype_code(y.dtype), _stream_ptr(dev))
+    _cabi.check(st, "ojx_e8t_linear_lowbit_lora")
+    return y
+
+
 def encode_2bit(w: torch.Tensor, group_size: int = 8, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                 hadamard: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """``w`` [rows, cols] -> (packed uint8[P/4], scales fp16[P/g]) in the 2.0-bit format; bit-exact with the

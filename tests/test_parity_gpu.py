@@ -765,3 +765,37 @@ def test_ternary_fp32_activations_at_decode_shapes(P, oracle, m, k, n, group):
     ref = x @ wd.t() + bias
     magnitude = x.abs() @ wd.abs().t() + bias.abs()
     assert y.dtype == torch.float32 and float(((y - ref).abs() / magnitude).max()) < 1e-5
+
+
+@pytest.mark.parametrize("bits", [2, 1])
+@pytest.mark.parametrize("m,k,n,r,dt", [(1, 4096, 100, 8, torch.bfloat16), (4, 2048, 48, 16, torch.float16), (8, 4096, 33, 3, torch.float32)])
+def test_low_bit_adapter_epilogue(P, oracle, bits, m, k, n, r, dt):
+    """ojx_e8t_linear_lowbit_lora: the packed product, bias and the low-rank term in one launch of the int8 tensor-core
+    decode kernels, against the fp32 sum of the three - within 1e-5 of sum |x||w| + |bias| + sum |t||B| per output;
+    then a layer with an adapter at decode shapes against the reference's formula (lattice.py:839-842)."""
+    dev = torch.device(DEV)
+    w = torch.from_numpy(oracle.gen_normal(1000 + n, n * k, 0.02).reshape(n, k).copy()).to(dev)
+    enc, dec = (P.ops.encode_2bit, P.ops.decode_2bit) if bits == 2 else (P.ops.encode_1bit, P.ops.decode_1bit)
+    pk, sc = enc(w, 32)
+    wd = dec(pk, sc, (n, k), torch.float32)
+    x = torch.from_numpy(oracle.gen_normal(1001 + m, m * k, 1.0).reshape(m, k).copy()).to(dt).to(dev)
+    bias = torch.from_numpy(oracle.gen_normal(1002, n, 0.1).copy()).to(dt).to(dev)
+    t = torch.from_numpy(oracle.gen_normal(1003, m * r, 1.0).reshape(m, r).copy()).to(dev)
+    b = torch.from_numpy(oracle.gen_normal(1004, r * n, 0.05).reshape(r, n).copy()).to(dt).to(dev)
+    y = P.ops.linear_lowbit_lora(bits, x, pk, sc, bias, n, k, 32, t, b, out_dtype=torch.float32)
+    ref = x.float() @ wd.t() + bias.float() + t @ b.float()
+    magnitude = x.float().abs() @ wd.abs().t() + bias.float().abs() + t.abs() @ b.float().abs()
+    assert float(((y - ref).abs() / magnitude).max()) < 1e-5
+    with pytest.raises(ValueError):
+        P.ops.linear_lowbit_lora(bits, x[:1].repeat(9, 1), pk, sc, bias, n, k, 32, t[:1].repeat(9, 1), b)
+    if dt == torch.bfloat16:
+        torch.manual_seed(5)
+        lin = torch.nn.Linear(k, 64, bias=True).to(dev).to(dt)
+        layer = P.E8LatticeLinear.from_linear(lin, rank=r, bitrate=float(bits), group_size=32)
+        with torch.no_grad():
+            layer.lora_B.copy_(torch.randn_like(layer.lora_B) * 0.05)
+            out = layer(x)
+            wl = layer.unpack_weights(torch.float32)
+            refl = (x.float() @ wl.t() + layer.bias.float()
+                    + layer.scaling * ((x.float() @ layer.lora_A.float()) @ layer.lora_B.float()))
+        assert float((out.float() - refl).abs().max()) <= 2.0 ** -6 * float(refl.abs().max()) + 1e-3
