@@ -274,3 +274,20 @@ def test_checkpoint_file_discovery_and_layout_rules(P, tmp_path):
         P.load_hf_checkpoint_e8(str(tmp_path), row_block=0)
     with pytest.raises(NotADirectoryError):
         P.load_hf_checkpoint_e8(str(tmp_path / "nowhere"))
+
+
+def test_adapter_epilogue_shape_rules(P):
+    """Which decode shapes may carry the adapter term in the kernels' epilogue (host-side predicates only): the ternary
+    kernels take 1-8 rows of 16-bit activations with K % 256 == 0 and groups of 32; the 2.0-bit / 1.0-bit kernels 1-8
+    rows with groups of 32, K % 2048 == 0 and operands of x that fit shared memory; ranks 1-64."""
+    import torch
+    ops = P.ops
+    assert ops.lora_fusable(1, 4096, 32, torch.bfloat16, 8) and ops.lora_fusable(8, 256, 32, torch.float16, 64)
+    assert not ops.lora_fusable(9, 4096, 32, torch.bfloat16, 8)          # the 9-16 row kernels have no registers for it
+    assert not ops.lora_fusable(1, 4096, 32, torch.float32, 8)           # fp32 activations do not reach those kernels
+    assert not ops.lora_fusable(1, 4000, 32, torch.bfloat16, 8) and not ops.lora_fusable(1, 4096, 32, torch.bfloat16, 65)
+    assert not ops.lora_fusable(1, 4096, 32, torch.bfloat16, 0)
+    assert ops.lowbit_lora_fusable(1, 4096, 32, 8) and ops.lowbit_lora_fusable(8, 4096, 32, 64) and ops.lowbit_lora_fusable(4, 8192, 32, 1)
+    assert not ops.lowbit_lora_fusable(8, 8192, 32, 8)                   # eight rows of 8192 activations do not fit shared memory
+    assert not ops.lowbit_lora_fusable(1, 4096, 8, 8) and not ops.lowbit_lora_fusable(1, 4352, 32, 8)
+    assert not ops.lowbit_lora_fusable(9, 2048, 32, 8) and not ops.lowbit_lora_fusable(0, 2048, 32, 8)
